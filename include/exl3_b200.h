@@ -1,0 +1,134 @@
+/*
+ * exl3_b200 -- C ABI of the sm_100a kernels for the EXL3 trellis-quantized linear layer.
+ *
+ * This is the boundary a host runtime binds instead of the pybind11 module
+ * `exllamav3.ext.exllamav3_ext` that the orcasaq2 plugin calls.  Every function takes plain
+ * device pointers, integer sizes and a CUDA stream (a `cudaStream_t` passed as `void*`,
+ * NULL = the legacy default stream), launches asynchronously on that stream, and returns 0
+ * or a negative EXL3_E_* code.  Unless a function says otherwise the library allocates
+ * nothing, never synchronises the device and keeps no reference to any buffer: the caller
+ * owns inputs, outputs and scratch.  There is no CPU fallback.
+ *
+ * Common conventions
+ *   trellis   [ic/16][oc/16][16*K] uint16 words (int16 storage is the same bits), contiguous,
+ *             16-byte aligned.  K = bits per weight; passed as k_times_2 (= 2*K) because the
+ *             reference API lets K be x.5 (orcasaq2/ops.py:28-34).  Supported here: integer
+ *             K in 1..8.  Half rates return EXL3_E_UNSUPPORTED.
+ *   fp16      IEEE binary16 bit patterns; activations row-major, contiguous.
+ *   mcg, mul1 alternative codebooks selected by flag in the reference
+ *             (orcasaq2/ops.py:38, orcasaq2/config.py:218); only the default "3INST"
+ *             codebook is defined here, so a non-zero flag returns EXL3_E_UNSUPPORTED.
+ *   ic, oc    multiples of 128 wherever a Hadamard is involved (orcasaq2/__init__.py:29,46),
+ *             multiples of 16 for exl3_reconstruct.
+ */
+#ifndef EXL3_B200_H
+#define EXL3_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define EXL3_ABI_VERSION 1
+
+enum {
+    EXL3_OK = 0,
+    EXL3_E_SHAPE = -1,       /* bad dimension, row count or packed size */
+    EXL3_E_ALIGN = -2,       /* pointer not aligned as required */
+    EXL3_E_UNSUPPORTED = -3, /* K, codebook flag or mode not implemented */
+    EXL3_E_LAUNCH = -4,      /* CUDA reported an error on launch */
+    EXL3_E_WORKSPACE = -5,   /* scratch buffer missing or too small */
+    EXL3_E_NULL = -6         /* required pointer is NULL */
+};
+
+int exl3_abi_version(void);
+const char *exl3_strerror(int code);
+
+/*
+ * Trellis -> dense fp16 inner weight  w[ic][oc]  (before Hadamard and sign vectors).
+ * Replaces ext.reconstruct(w, trellis, k, mcg, mul1): orcasaq2/ops.py:56,
+ * orcasaq2/__init__.py:57.  Bit-exact against the CPU oracle.
+ */
+int exl3_reconstruct(void *w, const void *trellis, int ic, int oc, int k_times_2, int mcg,
+                     int mul1, void *stream);
+
+/*
+ * out = H128(in * pre) * post * scale, blockwise over the last dimension n (a multiple of
+ * 128), rows x n fp16, one rounding.  pre / post are fp16 [n] or NULL; in == out is allowed.
+ * Replaces ext.had_r_128(in, out, pre, post, scale): orcasaq2/ops.py:54,59.
+ */
+int exl3_had_r_128(const void *in, void *out, const void *pre, const void *post, float scale,
+                   int rows, int n, void *stream);
+
+/* One shard of a (possibly fused) layer for exl3_gemv_grouped. */
+typedef struct exl3_shard {
+    const void *trellis; /* [ic/16][oc/16][16K] uint16 */
+    const void *suh;     /* [ic] fp16 */
+    const void *svh;     /* [oc] fp16 */
+    int oc;              /* output features of this shard (multiple of 128) */
+    int k_times_2;       /* 2 * bits per weight */
+    int mcg, mul1;       /* codebook flags; must be 0 */
+    int out_col;         /* first column of this shard inside y */
+} exl3_shard;
+
+#define EXL3_MAX_SHARDS 8
+#define EXL3_GEMV_MAX_ROWS 16
+
+/*
+ * Fused decode GEMV for 1..16 rows:   y[:, out_col : out_col+oc] = H(H(x*suh) W) * svh
+ * for every shard, in ONE launch.  All shards read the same x [rows][ic]; y is [rows][ldy]
+ * fp16 (ldy >= the widest out_col+oc), so a fused qkv_proj / gate_up_proj needs no
+ * concatenation.  Replaces ext.exl3_gemm(A, trellis, C, suh, A_had, svh, kernel, mcg, mul1,
+ * acc_mode) for small row counts (orcasaq2/ops.py:46-49) and the per-shard loop plus
+ * torch.cat of orcasaq2/config.py:236-243.
+ *
+ * workspace: device scratch of at least exl3_gemv_workspace_bytes(...) bytes, 256-byte
+ * aligned, ZERO-FILLED ONCE by the caller before its first use; the kernel leaves the part
+ * that must stay zero at zero on exit, so it can be reused by later calls on the same
+ * stream.  Calls that share a workspace must not overlap on the device.
+ */
+size_t exl3_gemv_workspace_bytes(const exl3_shard *shards, int nshards, int rows, int ic);
+int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                      int ic, int ldy, void *workspace, size_t workspace_bytes, void *stream);
+
+/* Single-shard convenience form of exl3_gemv_grouped (y is [rows][oc]). */
+int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
+              int rows, int ic, int oc, int k_times_2, int mcg, int mul1, void *workspace,
+              size_t workspace_bytes, void *stream);
+
+/*
+ * The word at byte offset 0 of a GEMV workspace is a sticky device-side status: 0, or
+ * non-zero after a bounded wait inside a kernel ran out.  Read it with a device-to-host copy
+ * when diagnosing; it is never set in normal operation.
+ */
+#define EXL3_WS_STATUS_OFFSET 0
+
+/*
+ * int8 embedding gather:  out[t][:] = dt(q[ids[t]][:]) * scales[ids[t]], one rounding to dt
+ * (dt = fp16, or bf16 when is_bf16).  qweight [vocab][hidden] int8 (hidden a multiple of 16),
+ * scales [vocab] dt, ids [tokens] int64 (int32 when ids_are_i32), out [tokens][hidden] dt.
+ * An id outside [0, vocab) yields a zero row and, if bad_id_flag (a device uint32) is not
+ * NULL, sets it to 1.  Replaces Exl3EmbeddingMethod.embedding (orcasaq2/heads.py:61-67) and
+ * Int8EmbeddingTable.forward (orcasaq2/patches/int8_embedding.py:40-43).  Bit-exact.
+ */
+int exl3_int8_embed(const void *qweight, const void *scales, const void *ids, void *out, int tokens,
+                    int vocab, int hidden, int is_bf16, int ids_are_i32, void *bad_id_flag,
+                    void *stream);
+
+/*
+ * int8 head:  logits[r][v] = scales[v] * sum_h x[r][h] * q[v][h]  for 1..16 rows, written as dt
+ * with leading dimension ld_logits.  hidden must be a multiple of 64.  The table is streamed
+ * once as int8 and never dequantised into memory.  Replaces Exl3EmbeddingMethod.apply
+ * (orcasaq2/heads.py:69-75), which materialises the dt table on every call; that version
+ * rounds q*s to dt before the product, this one scales the exact integer dot product, so the
+ * two agree within the layer tolerance, not bit for bit.
+ */
+int exl3_int8_head(const void *qweight, const void *scales, const void *x, void *logits, int rows,
+                   int vocab, int hidden, long long ld_logits, int is_bf16, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* EXL3_B200_H */

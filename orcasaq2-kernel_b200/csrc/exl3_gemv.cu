@@ -1,0 +1,486 @@
+// Fused trellis-decode GEMV for 1..16 rows, grouped over the shards of a fused layer:
+//     y[:, out_col : out_col+oc] = H128( H128(x * suh) . W(trellis) ) * svh
+// in one launch, with no intermediate tensor in global memory except split-K partial sums.
+//
+// Work unit: one 128-wide block of output channels (the width of the output Hadamard) times one
+// slice of the input channels.  A CTA of eight warps owns one unit:
+//   prologue  H128(x*suh) for its input slice is computed with warp shuffles and left in
+//             shared memory in mma B-fragment order; meanwhile the first trellis stages are
+//             already in flight.
+//   main loop each warp streams [4 tiles x 32K bytes] pieces of the packed trellis with 1-D bulk
+//             async copies (TMA) into its private shared-memory ring (mbarrier completion, no
+//             block-wide synchronisation), decodes 32 weights per lane in registers and feeds
+//             the raw codewords to mma.m16n8k16: a codeword's two fp16 halves occupy two
+//             consecutive K slots that see the same activation, so their sum -- the weight --
+//             is formed inside the fp32 accumulator and never rounded to fp16.
+//   epilogue  warps are reduced through shared memory, slices through a global scratch with an
+//             arrival ticket; the last CTA of a unit sums the partials in slice order (bitwise
+//             reproducible), applies H128 and svh and writes fp16.
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "exl3_codec.cuh"
+#include "exl3_common.cuh"
+#include "exl3_hadamard.cuh"
+
+namespace exl3 {
+
+constexpr int kWarps = 8;
+constexpr int kThreads = kWarps * 32;
+constexpr int kRowGroups = 4;          // warps along the input dimension
+constexpr int kDepth = 8;              // ring slots per warp
+constexpr int kTargetCtas = 296;       // two resident CTAs on each of 148 SMs
+constexpr int kXfMaxBytes = 48 * 1024; // activation fragments
+constexpr int kBarBytes = 1024;
+constexpr int kSpinLimit = 1 << 22;
+constexpr unsigned kStatusTimeout = 1u;
+
+constexpr int kWsStatusBytes = 256;
+
+struct GemvShardDev {
+    const uint32_t *trellis;
+    const __half *suh;
+    const __half *svh;
+    long long partial_off;  // in floats
+    int tiles_j;            // oc / 16
+    int K;
+    int out_col;
+    int cta_begin;
+    int splitk;
+    int unit_begin;
+};
+
+struct GemvParams {
+    const __half *x;
+    __half *y;
+    float *partial;
+    unsigned *tickets;
+    unsigned *status;
+    int rows, ic, ldy, kblocks;
+    int nb;         // rows held per group of eight (1, 2, 4 or 8)
+    int xf_bytes;   // bytes reserved for activation fragments
+    int nshards;
+    GemvShardDev sh[EXL3_MAX_SHARDS];
+};
+
+// ---------------------------------------------------------------------------------------------
+// PTX wrappers
+__device__ __forceinline__ uint32_t smem_u32(const void *p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait: gives up after kSpinLimit polls and reports through the status word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status) {
+    for (int it = 0; it < kSpinLimit; ++it)
+        if (mbar_try_wait(bar, parity)) return true;
+    atomicOr(status, kStatusTimeout);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t *a, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+        "{%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+// K consecutive 32-bit words from shared memory, widest loads the alignment allows.
+template <int K>
+__device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&w)[K + 1]) {
+    if constexpr (K % 4 == 0) {
+#pragma unroll
+        for (int k = 0; k < K; k += 4) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(src + k);
+            w[k] = v.x; w[k + 1] = v.y; w[k + 2] = v.z; w[k + 3] = v.w;
+        }
+    } else if constexpr (K % 2 == 0) {
+#pragma unroll
+        for (int k = 0; k < K; k += 2) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(src + k);
+            w[k] = v.x; w[k + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < K; ++k) w[k] = src[k];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+template <int K, int NT>
+__device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev &S, int local,
+                                         unsigned char *smem) {
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const int wc = warp & 1;        // which half of the 128 output channels
+    const int wr = warp >> 1;       // interleave over input tiles
+    const int g = lane >> 2, q = lane & 3;
+    const int NB = P.nb;
+
+    const int ob = local / S.splitk, ks = local - ob * S.splitk;
+    const int kb0 = (int)((long long)ks * P.kblocks / S.splitk);
+    const int kb1 = (int)((long long)(ks + 1) * P.kblocks / S.splitk);
+    const int nblk = kb1 - kb0;
+    const int nsteps = nblk * 2;    // 8 tiles per block / 4 row groups
+
+    uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
+    uint32_t *xf = reinterpret_cast<uint32_t *>(smem + kBarBytes);
+    unsigned char *region = smem + kBarBytes + P.xf_bytes;
+    constexpr int kStageWords = 4 * 8 * K;          // four tiles
+    constexpr uint32_t kStageBytes = kStageWords * 4;
+    uint32_t *ring = reinterpret_cast<uint32_t *>(region) + warp * (kDepth * kStageWords);
+    const uint32_t bar0 = smem_u32(bars + warp * kDepth);
+    const uint32_t ring0 = smem_u32(ring);
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < kDepth; ++s) mbar_init(bar0 + 8 * s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    __syncwarp();
+
+    const uint32_t *src0 =
+        S.trellis + ((size_t)(kb0 * 8 + wr) * S.tiles_j + (size_t)(ob * 8 + wc * 4)) * (size_t)(8 * K);
+    const size_t src_step = (size_t)4 * S.tiles_j * (8 * K);   // four tile rows further
+    if (lane == 0) {
+        const int pre = nsteps < kDepth ? nsteps : kDepth;
+        for (int s = 0; s < pre; ++s) {
+            mbar_expect_tx(bar0 + 8 * s, kStageBytes);
+            bulk_g2s(ring0 + s * kStageBytes, src0 + s * src_step, kStageBytes, bar0 + 8 * s);
+        }
+    }
+
+    // ---- prologue: H128(x * suh) for the slice, in B-fragment order, both halves equal
+    {
+        const int nrow = NT * NB;
+        const int tasks = nrow * nblk;
+        for (int task = warp; task < tasks; task += kWarps) {
+            const int blk = task / nrow, n = task - blk * nrow;
+            float v[4] = {0.f, 0.f, 0.f, 0.f};
+            if (n < P.rows) {
+                const int col = (kb0 + blk) * 128 + 4 * lane;
+                const uint2 xr = *reinterpret_cast<const uint2 *>(P.x + (size_t)n * P.ic + col);
+                const uint2 sr = __ldg(reinterpret_cast<const uint2 *>(S.suh + col));
+                const __half2 x01 = *reinterpret_cast<const __half2 *>(&xr.x);
+                const __half2 x23 = *reinterpret_cast<const __half2 *>(&xr.y);
+                const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x);
+                const __half2 s23 = *reinterpret_cast<const __half2 *>(&sr.y);
+                v[0] = __low2float(x01) * __low2float(s01);
+                v[1] = __high2float(x01) * __high2float(s01);
+                v[2] = __low2float(x23) * __low2float(s23);
+                v[3] = __high2float(x23) * __high2float(s23);
+                fwht128_warp(v, lane);
+            }
+            const int tile_local = blk * 8 + (lane >> 2);
+            const int t = (NT == 2) ? (n >> 3) : 0;
+            const int nn = (NT == 2) ? (n & 7) : n;
+            uint32_t *dst = xf + (((size_t)(tile_local * NT + t) * NB + nn) * 4) * 4 + (lane & 3);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const __half2 d = __float2half2_rn(v[k] * kHadScale);
+                dst[k * 4] = *reinterpret_cast<const uint32_t *>(&d);
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- main loop
+    float acc[NT][4][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[t][a][e] = 0.f;
+
+    const int nsel = g & (NB - 1);
+    const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
+    bool ok = true;
+    for (int s = 0; s < nsteps && ok; ++s) {
+        const int slot = s & (kDepth - 1);
+        ok = mbar_wait(bar0 + 8 * slot, (s / kDepth) & 1, P.status);
+        uint32_t wd[K + 1];
+        load_words<K>(ring + slot * kStageWords + lane * K, wd);
+        const int tile_local = wr + 4 * s;
+        uint4 xa[NT];
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+            xa[t] = *reinterpret_cast<const uint4 *>(xf + (((size_t)(tile_local * NT + t) * NB + nsel) * 4 + q) * 4);
+        wd[K] = __shfl_sync(0xffffffffu, wd[0], nxt_lane);
+        __syncwarp();
+        if (lane == 0 && s + kDepth < nsteps) {
+            // the slot has been read by every lane; hand it back to the async proxy
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            mbar_expect_tx(bar0 + 8 * slot, kStageBytes);
+            bulk_g2s(ring0 + slot * kStageBytes, src0 + (size_t)(s + kDepth) * src_step, kStageBytes,
+                     bar0 + 8 * slot);
+        }
+        uint32_t z[32];
+        decode_chunk<K>(wd, z);
+#pragma unroll
+        for (int a = 0; a < 4; ++a) {
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                mma16816(acc[t][a], &z[8 * a], xa[t].x, xa[t].y);
+                mma16816(acc[t][a], &z[8 * a + 4], xa[t].z, xa[t].w);
+            }
+        }
+    }
+    __syncthreads();   // every warp is done with its ring: the region is reused below
+
+    // ---- reduce the four row-group warps
+    float *red = reinterpret_cast<float *>(region);                  // [4][NT*8][128]
+    float *fin = red + kRowGroups * (NT * 8) * 128;                  // [NT*8][128]
+    {
+        const int u = g >> 1, p = g & 1;
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+                const int oc_lo = 64 * wc + 16 * u + 4 * a + p;
+                const int n0 = 8 * t + 2 * q;
+                float *r0 = red + ((size_t)(wr * (NT * 8) + n0)) * 128 + oc_lo;
+                if (n0 < P.rows) { r0[0] = acc[t][a][0]; r0[2] = acc[t][a][2]; }
+                if (n0 + 1 < P.rows) { r0[128] = acc[t][a][1]; r0[130] = acc[t][a][3]; }
+            }
+    }
+    __syncthreads();
+
+    const int unit = S.unit_begin + ob;
+    const int ocl = tid & 127;
+    float *part = P.partial + S.partial_off + (size_t)ob * S.splitk * P.rows * 128;
+    for (int n = tid >> 7; n < P.rows; n += 2) {
+        float v = 0.f;
+#pragma unroll
+        for (int r = 0; r < kRowGroups; ++r) v += red[((size_t)(r * (NT * 8) + n)) * 128 + ocl];
+        if (S.splitk == 1) fin[n * 128 + ocl] = v;
+        else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
+    }
+
+    if (S.splitk > 1) {
+        __shared__ unsigned s_last;
+        __threadfence();
+        __syncthreads();
+        if (tid == 0) {
+            const unsigned prev = atomicAdd(P.tickets + unit, 1u);
+            s_last = (prev == (unsigned)(S.splitk - 1));
+            if (s_last) P.tickets[unit] = 0u;   // ready for the next launch
+        }
+        __syncthreads();
+        if (!s_last) return;
+        __threadfence();
+        for (int n = tid >> 7; n < P.rows; n += 2) {
+            float v = 0.f;
+            for (int k2 = 0; k2 < S.splitk; ++k2) v += __ldcg(part + ((size_t)k2 * P.rows + n) * 128 + ocl);
+            fin[n * 128 + ocl] = v;
+        }
+    }
+    __syncthreads();
+
+    // ---- output Hadamard, svh, fp16
+    const int ocol = S.out_col + ob * 128 + 4 * lane;
+    const uint2 sv = __ldg(reinterpret_cast<const uint2 *>(S.svh + ob * 128 + 4 * lane));
+    const __half2 sv01 = *reinterpret_cast<const __half2 *>(&sv.x);
+    const __half2 sv23 = *reinterpret_cast<const __half2 *>(&sv.y);
+    for (int n = warp; n < P.rows; n += kWarps) {
+        const float4 f = *reinterpret_cast<const float4 *>(fin + n * 128 + 4 * lane);
+        float v[4] = {f.x, f.y, f.z, f.w};
+        fwht128_warp(v, lane);
+        const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * __low2float(sv01),
+                                              v[1] * kHadScale * __high2float(sv01));
+        const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * __low2float(sv23),
+                                              v[3] * kHadScale * __high2float(sv23));
+        uint2 o;
+        o.x = *reinterpret_cast<const uint32_t *>(&o01);
+        o.y = *reinterpret_cast<const uint32_t *>(&o23);
+        *reinterpret_cast<uint2 *>(P.y + (size_t)n * P.ldy + ocol) = o;
+    }
+}
+
+template <int NT>
+__global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const __grid_constant__ GemvParams P) {
+    extern __shared__ __align__(128) unsigned char smem[];
+    int s = 0;
+    while (s + 1 < P.nshards && (int)blockIdx.x >= P.sh[s + 1].cta_begin) ++s;
+    const GemvShardDev &S = P.sh[s];
+    const int local = blockIdx.x - S.cta_begin;
+    switch (S.K) {
+        case 1: gemv_cta<1, NT>(P, S, local, smem); break;
+        case 2: gemv_cta<2, NT>(P, S, local, smem); break;
+        case 3: gemv_cta<3, NT>(P, S, local, smem); break;
+        case 4: gemv_cta<4, NT>(P, S, local, smem); break;
+        case 5: gemv_cta<5, NT>(P, S, local, smem); break;
+        case 6: gemv_cta<6, NT>(P, S, local, smem); break;
+        case 7: gemv_cta<7, NT>(P, S, local, smem); break;
+        case 8: gemv_cta<8, NT>(P, S, local, smem); break;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// host-side plan: how the shards are cut into CTAs and how the scratch is laid out
+struct GemvPlan {
+    int nt, nb, xf_bytes, region_bytes, total_ctas, total_units, kblocks;
+    long long partial_floats;
+    int splitk[EXL3_MAX_SHARDS], cta_begin[EXL3_MAX_SHARDS], unit_begin[EXL3_MAX_SHARDS], K[EXL3_MAX_SHARDS];
+    long long partial_off[EXL3_MAX_SHARDS];
+};
+
+static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl) {
+    if (!sh) return EXL3_E_NULL;
+    if (n < 1 || n > EXL3_MAX_SHARDS || rows < 1 || rows > EXL3_GEMV_MAX_ROWS || ic <= 0 || (ic & 127))
+        return EXL3_E_SHAPE;
+    pl.kblocks = ic / 128;
+    pl.nt = rows > 8 ? 2 : 1;
+    pl.nb = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
+    const int frag_bytes_per_block = 8 * pl.nt * pl.nb * 64;
+    const int max_slice = kXfMaxBytes / frag_bytes_per_block;
+    double total_bytes = 0;
+    int maxK = 0;
+    for (int i = 0; i < n; ++i) {
+        if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
+        if (sh[i].mcg || sh[i].mul1) return EXL3_E_UNSUPPORTED;
+        const int K = integer_k(sh[i].k_times_2);
+        if (!K) return EXL3_E_UNSUPPORTED;
+        if (!sh[i].trellis || !sh[i].suh || !sh[i].svh) return EXL3_E_NULL;
+        if (!aligned(sh[i].trellis, 16) || !aligned(sh[i].suh, 8) || !aligned(sh[i].svh, 8)) return EXL3_E_ALIGN;
+        pl.K[i] = K;
+        maxK = K > maxK ? K : maxK;
+        total_bytes += (double)ic * sh[i].oc * K / 8.0;
+    }
+    int ctas = 0, units = 0, max_nblk = 0;
+    long long pf = 0;
+    for (int i = 0; i < n; ++i) {
+        const int ocb = sh[i].oc / 128;
+        const double share = (double)ic * sh[i].oc * pl.K[i] / 8.0 / total_bytes;
+        int sk = (int)(kTargetCtas * share / ocb + 0.5);
+        const int min_sk = (pl.kblocks + max_slice - 1) / max_slice;
+        if (sk < min_sk) sk = min_sk;
+        if (sk < 1) sk = 1;
+        if (sk > pl.kblocks) sk = pl.kblocks;
+        pl.splitk[i] = sk;
+        pl.cta_begin[i] = ctas;
+        pl.unit_begin[i] = units;
+        pl.partial_off[i] = pf;
+        ctas += ocb * sk;
+        units += ocb;
+        if (sk > 1) pf += (long long)ocb * sk * rows * 128;
+        const int nblk = (pl.kblocks + sk - 1) / sk;
+        max_nblk = nblk > max_nblk ? nblk : max_nblk;
+    }
+    pl.total_ctas = ctas;
+    pl.total_units = units;
+    pl.partial_floats = pf;
+    pl.xf_bytes = ((max_nblk * frag_bytes_per_block) + 127) & ~127;
+    const int ring = kWarps * kDepth * 4 * 8 * maxK * 4;
+    const int red = (kRowGroups + 1) * pl.nt * 8 * 128 * 4;
+    pl.region_bytes = ring > red ? ring : red;
+    return EXL3_OK;
+}
+
+static size_t plan_workspace_bytes(const GemvPlan &pl) {
+    size_t b = kWsStatusBytes + (size_t)pl.total_units * 4;
+    b = (b + 255) & ~(size_t)255;
+    return b + (size_t)pl.partial_floats * 4;
+}
+
+}  // namespace exl3
+
+extern "C" size_t exl3_gemv_workspace_bytes(const exl3_shard *shards, int nshards, int rows, int ic) {
+    exl3::GemvPlan pl;
+    if (exl3::make_plan(shards, nshards, rows, ic, pl) != EXL3_OK) return 0;
+    return exl3::plan_workspace_bytes(pl);
+}
+
+extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                                 int ic, int ldy, void *workspace, size_t workspace_bytes, void *stream) {
+    using namespace exl3;
+    GemvPlan pl;
+    const int rc = make_plan(shards, nshards, rows, ic, pl);
+    if (rc != EXL3_OK) return rc;
+    if (!x || !y) return EXL3_E_NULL;
+    if (!aligned(x, 8) || !aligned(y, 8) || (ldy & 3)) return EXL3_E_ALIGN;
+    for (int i = 0; i < nshards; ++i)
+        if (shards[i].out_col + shards[i].oc > ldy) return EXL3_E_SHAPE;
+    if (!workspace || workspace_bytes < plan_workspace_bytes(pl)) return EXL3_E_WORKSPACE;
+    if (!aligned(workspace, 256)) return EXL3_E_ALIGN;
+
+    GemvParams P;
+    P.x = static_cast<const __half *>(x);
+    P.y = static_cast<__half *>(y);
+    unsigned char *ws = static_cast<unsigned char *>(workspace);
+    P.status = reinterpret_cast<unsigned *>(ws);
+    P.tickets = reinterpret_cast<unsigned *>(ws + kWsStatusBytes);
+    const size_t head = ((size_t)kWsStatusBytes + (size_t)pl.total_units * 4 + 255) & ~(size_t)255;
+    P.partial = reinterpret_cast<float *>(ws + head);
+    P.rows = rows;
+    P.ic = ic;
+    P.ldy = ldy;
+    P.kblocks = pl.kblocks;
+    P.nb = pl.nb;
+    P.xf_bytes = pl.xf_bytes;
+    P.nshards = nshards;
+    for (int i = 0; i < nshards; ++i) {
+        GemvShardDev &d = P.sh[i];
+        d.trellis = static_cast<const uint32_t *>(shards[i].trellis);
+        d.suh = static_cast<const __half *>(shards[i].suh);
+        d.svh = static_cast<const __half *>(shards[i].svh);
+        d.partial_off = pl.partial_off[i];
+        d.tiles_j = shards[i].oc / 16;
+        d.K = pl.K[i];
+        d.out_col = shards[i].out_col;
+        d.cta_begin = pl.cta_begin[i];
+        d.splitk = pl.splitk[i];
+        d.unit_begin = pl.unit_begin[i];
+    }
+    const size_t smem = (size_t)kBarBytes + pl.xf_bytes + pl.region_bytes;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t e;
+    if (pl.nt == 1) {
+        e = cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+        gemv_kernel<1><<<pl.total_ctas, kThreads, smem, st>>>(P);
+    } else {
+        e = cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+        gemv_kernel<2><<<pl.total_ctas, kThreads, smem, st>>>(P);
+    }
+    return launch_status();
+}
+
+extern "C" int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
+                         int rows, int ic, int oc, int k_times_2, int mcg, int mul1, void *workspace,
+                         size_t workspace_bytes, void *stream) {
+    exl3_shard s;
+    s.trellis = trellis;
+    s.suh = suh;
+    s.svh = svh;
+    s.oc = oc;
+    s.k_times_2 = k_times_2;
+    s.mcg = mcg;
+    s.mul1 = mul1;
+    s.out_col = 0;
+    return exl3_gemv_grouped(&s, 1, x, y, rows, ic, oc, workspace, workspace_bytes, stream);
+}

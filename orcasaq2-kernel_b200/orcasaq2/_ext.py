@@ -1,0 +1,255 @@
+"""Stand-in for `exllamav3.ext.exllamav3_ext`: the same positional entry points the plugin
+calls (orcasaq2/ops.py:47-59 and orcasaq2/__init__.py:57 of the reference), bound with ctypes
+to this package's sm_100a library `libexl3_b200.so` (C ABI in include/exl3_b200.h).
+
+There is no CPU path and no fallback: a missing library or a non-CUDA tensor raises.
+PyTorch is used only for device memory and the current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(_HERE, "libexl3_b200.so")
+_lib = None
+_lock = threading.Lock()
+
+MAX_SHARDS = 8
+GEMV_MAX_ROWS = 16
+
+
+class Exl3Shard(ctypes.Structure):
+    _fields_ = [("trellis", ctypes.c_void_p), ("suh", ctypes.c_void_p), ("svh", ctypes.c_void_p),
+                ("oc", ctypes.c_int), ("k_times_2", ctypes.c_int), ("mcg", ctypes.c_int),
+                ("mul1", ctypes.c_int), ("out_col", ctypes.c_int)]
+
+
+def library_path() -> str:
+    return _LIB_PATH
+
+
+def lib():
+    """Load the CUDA library once; raise if it has not been built."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                if not os.path.exists(_LIB_PATH):
+                    raise RuntimeError(
+                        f"{_LIB_PATH} is missing: build it with `python build.py` in "
+                        f"{os.path.dirname(_HERE)} (needs nvcc, sm_100a). There is no CPU fallback.")
+                L = ctypes.CDLL(_LIB_PATH)
+                vp, ci, cf, sz = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_size_t
+                L.exl3_abi_version.restype = ci
+                L.exl3_strerror.restype = ctypes.c_char_p
+                L.exl3_strerror.argtypes = [ci]
+                L.exl3_reconstruct.argtypes = [vp, vp, ci, ci, ci, ci, ci, vp]
+                L.exl3_had_r_128.argtypes = [vp, vp, vp, vp, cf, ci, ci, vp]
+                L.exl3_gemv_workspace_bytes.restype = sz
+                L.exl3_gemv_workspace_bytes.argtypes = [ctypes.POINTER(Exl3Shard), ci, ci, ci]
+                L.exl3_gemv_grouped.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp, sz, vp]
+                L.exl3_gemv.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, sz, vp]
+                ll = ctypes.c_longlong
+                L.exl3_int8_embed.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp]
+                L.exl3_int8_head.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ci, vp]
+                for name in ("exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
+                             "exl3_int8_embed", "exl3_int8_head"):
+                    getattr(L, name).restype = ci
+                _lib = L
+    return _lib
+
+
+def _check(rc: int, what: str):
+    if rc != 0:
+        raise RuntimeError(f"{what}: {lib().exl3_strerror(rc).decode()} ({rc})")
+
+
+def _cuda(t: torch.Tensor, name: str, dtype=None):
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        raise RuntimeError(f"{name} must be a CUDA tensor (this build has no CPU path)")
+    if dtype is not None and t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise RuntimeError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    return t
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _k2(k) -> int:
+    k2 = float(k) * 2.0
+    if not k2.is_integer():
+        raise RuntimeError(f"unsupported bitrate K={k}")
+    return int(k2)
+
+
+def _trellis_dims(trellis: torch.Tensor):
+    if trellis.dim() != 3 or trellis.dtype not in (torch.int16, torch.uint16):
+        raise RuntimeError("trellis must be a 3-D int16 tensor [ic/16, oc/16, 16*K]")
+    return trellis.shape[0] * 16, trellis.shape[1] * 16, trellis.shape[2] / 16
+
+
+# --------------------------------------------------------------------------- workspaces
+# Scratch for the fused GEMV: split-K partial sums, arrival tickets, a status word.  One buffer
+# per (device, stream), grown on demand and zero-filled when (re)allocated; the kernels leave
+# the tickets at zero.  Allocation happens outside of CUDA-graph capture only if the first call
+# of a given size is made before capture (warm-up), as vLLM does.
+_workspaces: dict = {}
+
+
+def gemv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        size = max(nbytes, 8 << 20)
+        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
+
+
+def workspace_status(device: torch.device) -> int:
+    """OR of the sticky device-side status words of this device's workspaces (0 = healthy)."""
+    st = 0
+    for (idx, _), ws in _workspaces.items():
+        if idx == device.index:
+            st |= int(ws[:4].view(torch.int32).item())
+    return st
+
+
+# --------------------------------------------------------------------------- entry points
+def reconstruct(w: torch.Tensor, trellis: torch.Tensor, k, mcg: bool, mul1: bool) -> None:
+    """w[ic, oc] (fp16, out) <- decoded trellis.  ext.reconstruct, ops.py:56 of the reference."""
+    _cuda(w, "w", torch.float16)
+    _cuda(trellis, "trellis")
+    ic, oc, kk = _trellis_dims(trellis)
+    if float(k) != kk:
+        raise RuntimeError("packed dimension 2 is incorrect size")
+    if tuple(w.shape) != (ic, oc):
+        raise RuntimeError(f"w has shape {tuple(w.shape)}, trellis implies {(ic, oc)}")
+    _check(lib().exl3_reconstruct(w.data_ptr(), trellis.data_ptr(), ic, oc, _k2(k), int(bool(mcg)),
+                                  int(bool(mul1)), _stream(w)), "exl3_reconstruct")
+
+
+def had_r_128(inp: torch.Tensor, out: torch.Tensor, pre_scale, post_scale, scale: float) -> None:
+    """out <- H128(inp * pre) * post * scale along the last dim.  ext.had_r_128, ops.py:54,59."""
+    _cuda(inp, "in", torch.float16)
+    _cuda(out, "out", torch.float16)
+    if inp.shape != out.shape:
+        raise RuntimeError("had_r_128: in and out differ in shape")
+    n = inp.shape[-1]
+    rows = inp.numel() // n if n else 0
+    for nm, v in (("pre_scale", pre_scale), ("post_scale", post_scale)):
+        if v is not None:
+            _cuda(v, nm, torch.float16)
+            if v.numel() != n:
+                raise RuntimeError(f"{nm} has {v.numel()} elements, expected {n}")
+    _check(lib().exl3_had_r_128(inp.data_ptr(), out.data_ptr(),
+                                None if pre_scale is None else pre_scale.data_ptr(),
+                                None if post_scale is None else post_scale.data_ptr(),
+                                float(scale), rows, n, _stream(inp)), "exl3_had_r_128")
+
+
+def gemv_grouped(x: torch.Tensor, shards, y: torch.Tensor) -> None:
+    """y[:, cols of shard s] <- H(H(x*suh_s) W_s) * svh_s for every shard, one launch.
+    `shards` is a sequence of dicts with trellis, suh, svh, mcg, mul1 and (optionally)
+    out_col; columns default to the running sum of the shard widths."""
+    _cuda(x, "x", torch.float16)
+    _cuda(y, "y", torch.float16)
+    rows, ic = x.shape
+    arr = (Exl3Shard * len(shards))()
+    col = 0
+    for i, s in enumerate(shards):
+        tr = _cuda(s["trellis"], "trellis")
+        tic, toc, kk = _trellis_dims(tr)
+        if tic != ic:
+            raise RuntimeError(f"shard {i}: trellis has {tic} input channels, x has {ic}")
+        _cuda(s["suh"], "suh", torch.float16)
+        _cuda(s["svh"], "svh", torch.float16)
+        if s["suh"].numel() != ic or s["svh"].numel() != toc:
+            raise RuntimeError(f"shard {i}: suh/svh sizes do not match the trellis")
+        oc_col = s.get("out_col", col)
+        arr[i] = Exl3Shard(tr.data_ptr(), s["suh"].data_ptr(), s["svh"].data_ptr(), toc, _k2(kk),
+                           int(bool(s.get("mcg"))), int(bool(s.get("mul1"))), oc_col)
+        col = oc_col + toc
+    L = lib()
+    need = L.exl3_gemv_workspace_bytes(arr, len(shards), rows, ic)
+    ws = gemv_workspace(x.device, need) if need else None
+    _check(L.exl3_gemv_grouped(arr, len(shards), x.data_ptr(), y.data_ptr(), rows, ic, y.stride(0),
+                               None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
+                               _stream(x)), "exl3_gemv_grouped")
+
+
+def exl3_gemm(A, trellis, C, suh, A_had, svh, kernel: int, mcg: bool, mul1: bool, acc_mode: int) -> None:
+    """C[rows, oc] <- H(H(A*suh) W) * svh, fused.  ext.exl3_gemm, ops.py:47-49 of the reference.
+    A_had is the reference's scratch operand; this implementation keeps the rotated
+    activations on chip and leaves it untouched.  kernel: -1 = automatic."""
+    if acc_mode != 0:
+        raise RuntimeError("exl3_gemm: only acc_mode 0 is implemented")
+    rows = A.shape[0]
+    if rows <= GEMV_MAX_ROWS:
+        gemv_grouped(A, [dict(trellis=trellis, suh=suh, svh=svh, mcg=mcg, mul1=mul1)], C)
+        return
+    # more rows than one decode pass holds: walk the batch in passes of 16 rows
+    for r0 in range(0, rows, GEMV_MAX_ROWS):
+        r1 = min(rows, r0 + GEMV_MAX_ROWS)
+        gemv_grouped(A[r0:r1], [dict(trellis=trellis, suh=suh, svh=svh, mcg=mcg, mul1=mul1)], C[r0:r1])
+
+
+def hgemm_recon(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
+    """y[rows, oc] <- a[rows, ic] @ w[ic, oc], fp16.  ext.hgemm_recon, ops.py:57: a plain
+    dense GEMM, which the reference leaves to cuBLAS; so does this (torch.matmul)."""
+    _cuda(a, "a", torch.float16)
+    _cuda(w, "w", torch.float16)
+    _cuda(y, "y", torch.float16)
+    torch.matmul(a, w, out=y)
+
+
+_DT = (torch.float16, torch.bfloat16)
+HEAD_MAX_ROWS = 16
+
+
+def int8_embed(qweight: torch.Tensor, scales: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
+    """Gather int8 rows and scale them: [*ids.shape, hidden] in scales.dtype."""
+    _cuda(qweight, "qweight", torch.int8)
+    _cuda(scales, "scales", _DT)
+    if not isinstance(ids, torch.Tensor) or ids.device.type != "cuda":
+        raise RuntimeError("ids must be a CUDA tensor")
+    if ids.dtype not in (torch.int64, torch.int32):
+        raise RuntimeError(f"ids has dtype {ids.dtype}, expected int64 or int32")
+    vocab, hidden = qweight.shape
+    if scales.numel() != vocab:
+        raise RuntimeError("scales must hold one value per table row")
+    flat = ids.reshape(-1).contiguous()
+    out = torch.empty((flat.numel(), hidden), dtype=scales.dtype, device=qweight.device)
+    _check(lib().exl3_int8_embed(qweight.data_ptr(), scales.data_ptr(), flat.data_ptr(), out.data_ptr(),
+                                 flat.numel(), vocab, hidden, int(scales.dtype == torch.bfloat16),
+                                 int(flat.dtype == torch.int32), None, _stream(qweight)),
+           "exl3_int8_embed")
+    return out.reshape(*ids.shape, hidden)
+
+
+def int8_head(qweight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    """logits [rows, vocab] in x.dtype = x @ (q * s)^T without dequantising the table."""
+    _cuda(qweight, "qweight", torch.int8)
+    _cuda(x, "x", _DT)
+    _cuda(scales, "scales", _DT)
+    if scales.dtype != x.dtype:
+        scales = scales.to(x.dtype)
+    vocab, hidden = qweight.shape
+    rows = x.shape[0]
+    if x.shape[1] != hidden or scales.numel() != vocab:
+        raise RuntimeError("int8_head: shapes of x, qweight and scales do not agree")
+    out = torch.empty((rows, vocab), dtype=x.dtype, device=x.device)
+    L = lib()
+    for r0 in range(0, rows, HEAD_MAX_ROWS):
+        r1 = min(rows, r0 + HEAD_MAX_ROWS)
+        _check(L.exl3_int8_head(qweight.data_ptr(), scales.data_ptr(), x[r0:r1].data_ptr(),
+                                out[r0:r1].data_ptr(), r1 - r0, vocab, hidden, vocab,
+                                int(x.dtype == torch.bfloat16), _stream(x)), "exl3_int8_head")
+    return out

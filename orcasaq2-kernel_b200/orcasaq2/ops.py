@@ -1,0 +1,104 @@
+"""The EXL3 shard GEMM as PyTorch custom ops, so the layer stays one opaque node under
+torch.compile and replays inside CUDA graphs (reference orcasaq2/ops.py:1-66).
+
+`orcasaq2::shard_gemm` keeps the reference schema.  `orcasaq2::layer_gemm` is the grouped form
+used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, written straight
+into the concatenated output.
+
+Row-count dispatch (reference ops.py:25,46): at or below GEMM_MAX_ROWS the fused decode kernel
+reads the packed trellis directly (in passes of 16 rows); above it the weight is rebuilt once
+into a scratch buffer and handed to a dense GEMM, bracketed by the two Hadamard passes.
+"""
+import os
+from typing import List
+
+import torch
+from torch import Tensor
+
+from . import _ext
+
+GEMM_MAX_ROWS = int(os.environ.get("ORCA_EXL3_GEMM_MAX_ROWS", "144"))
+
+
+def exl3_K(trellis: Tensor):
+    """Bits per weight from the packed width: last dim / 16.  The half rates (1.5/2.5/3.5) are
+    kept as floats -- a 3.5-bit tile packs 56 words, and flooring would silently give 3
+    (reference ops.py:28-34)."""
+    k = trellis.shape[-1] / 16
+    return int(k) if float(k).is_integer() else k
+
+
+def _narrow_k(k: float):
+    return int(k) if float(k).is_integer() else k
+
+
+def _dense_path(x: Tensor, trellis: Tensor, suh: Tensor, svh: Tensor, k, mcg: bool, mul1: bool,
+                y: Tensor) -> None:
+    """rows > GEMM_MAX_ROWS: rotate, rebuild the weight into scratch, dense GEMM, rotate back."""
+    xh = torch.empty_like(x)
+    _ext.had_r_128(x, xh, suh, None, 1.0)
+    w = torch.empty((x.shape[1], y.shape[1]), dtype=torch.half, device=x.device)
+    _ext.reconstruct(w, trellis, k, mcg, mul1)
+    _ext.hgemm_recon(xh, w, y)
+    del w, xh                        # scratch only: keeping it would undo the compression
+    _ext.had_r_128(y, y, None, svh, 1.0)
+
+
+@torch.library.custom_op("orcasaq2::shard_gemm", mutates_args=())
+def shard_gemm(x: Tensor, trellis: Tensor, suh: Tensor, svh: Tensor,
+               oc: int, k: float, mcg: bool, mul1: bool) -> Tensor:
+    k = _narrow_k(k)
+    rows = x.shape[0]
+    y = torch.empty((rows, oc), dtype=torch.half, device=x.device)
+    if rows == 0:
+        return y
+    if rows <= GEMM_MAX_ROWS:
+        _ext.exl3_gemm(x, trellis, y, suh, x, svh, -1, mcg, mul1, 0)
+    else:
+        _dense_path(x, trellis, suh, svh, k, mcg, mul1, y)
+    return y
+
+
+@shard_gemm.register_fake
+def _shard_gemm_fake(x: Tensor, trellis: Tensor, suh: Tensor, svh: Tensor,
+                     oc: int, k: float, mcg: bool, mul1: bool) -> Tensor:
+    return x.new_empty((x.shape[0], oc), dtype=torch.half)
+
+
+@torch.library.custom_op("orcasaq2::layer_gemm", mutates_args=())
+def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Tensor],
+               ocs: List[int], ks: List[float], mcg: List[bool], mul1: List[bool]) -> Tensor:
+    """All shards of one layer: returns [rows, sum(ocs)] fp16, shard outputs side by side."""
+    rows = x.shape[0]
+    total = sum(ocs)
+    y = torch.empty((rows, total), dtype=torch.half, device=x.device)
+    if rows == 0:
+        return y
+    n = len(trellis)
+    if rows <= GEMM_MAX_ROWS:
+        shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i])
+                  for i in range(n)]
+        for g0 in range(0, n, _ext.MAX_SHARDS):
+            grp = shards[g0:g0 + _ext.MAX_SHARDS]
+            col0 = sum(ocs[:g0])
+            c = col0
+            for s, oc in zip(grp, ocs[g0:g0 + _ext.MAX_SHARDS]):
+                s["out_col"] = c
+                c += oc
+            for r0 in range(0, rows, _ext.GEMV_MAX_ROWS):
+                r1 = min(rows, r0 + _ext.GEMV_MAX_ROWS)
+                _ext.gemv_grouped(x[r0:r1], grp, y[r0:r1])
+    else:
+        col = 0
+        for i in range(n):
+            yi = torch.empty((rows, ocs[i]), dtype=torch.half, device=x.device)
+            _dense_path(x, trellis[i], suh[i], svh[i], _narrow_k(ks[i]), mcg[i], mul1[i], yi)
+            y[:, col:col + ocs[i]] = yi
+            col += ocs[i]
+    return y
+
+
+@layer_gemm.register_fake
+def _layer_gemm_fake(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Tensor],
+                     ocs: List[int], ks: List[float], mcg: List[bool], mul1: List[bool]) -> Tensor:
+    return x.new_empty((x.shape[0], sum(ocs)), dtype=torch.half)

@@ -1,0 +1,78 @@
+"""The C-ABI library loads and exports every function declared in include/exl3_b200.h; argument
+checks that run before any CUDA call are exercised here without a GPU."""
+import ctypes
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+HEADER = os.path.join(ROOT, "include", "exl3_b200.h")
+LIB = os.path.join(ROOT, "orcasaq2-kernel_b200", "orcasaq2", "libexl3_b200.so")
+
+
+@pytest.fixture(scope="module")
+def lib():
+    if not os.path.exists(LIB):
+        import __graft_entry__
+        __graft_entry__.build()
+    return ctypes.CDLL(LIB)
+
+
+def declared_functions():
+    src = open(HEADER).read()
+    src = re.sub(r"/\*.*?\*/", "", src, flags=re.S)
+    return sorted(set(re.findall(r"\b(exl3_[a-z0-9_]+)\s*\(", src)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_functions()
+    assert {"exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
+            "exl3_int8_embed", "exl3_int8_head", "exl3_strerror"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), n
+
+
+def test_version_and_strerror(lib):
+    lib.exl3_strerror.restype = ctypes.c_char_p
+    assert lib.exl3_abi_version() >= 1
+    for code in range(0, -7, -1):
+        assert lib.exl3_strerror(code)
+    assert b"unknown" in lib.exl3_strerror(-99)
+
+
+def test_argument_checks_without_gpu(lib):
+    vp = ctypes.c_void_p
+    lib.exl3_reconstruct.argtypes = [vp, vp] + [ctypes.c_int] * 5 + [vp]
+    assert lib.exl3_reconstruct(None, None, 128, 128, 8, 0, 0, None) == -6          # NULL
+    fake = vp(4096)     # never dereferenced: these calls fail validation first
+    assert lib.exl3_reconstruct(fake, fake, 100, 128, 8, 0, 0, None) == -1           # shape
+    assert lib.exl3_reconstruct(fake, fake, 128, 128, 7, 0, 0, None) == -3           # K = 3.5
+    assert lib.exl3_reconstruct(fake, fake, 128, 128, 8, 1, 0, None) == -3           # mcg
+    assert lib.exl3_reconstruct(vp(4100), fake, 128, 128, 8, 0, 0, None) == -2       # alignment
+    lib.exl3_had_r_128.argtypes = [vp, vp, vp, vp, ctypes.c_float, ctypes.c_int, ctypes.c_int, vp]
+    assert lib.exl3_had_r_128(fake, fake, None, None, 1.0, 1, 100, None) == -1
+    assert lib.exl3_had_r_128(fake, fake, None, None, 1.0, 0, 128, None) == 0         # empty input
+
+
+def test_gemv_plan_and_workspace(lib):
+    class Shard(ctypes.Structure):
+        _fields_ = [("trellis", ctypes.c_void_p), ("suh", ctypes.c_void_p), ("svh", ctypes.c_void_p),
+                    ("oc", ctypes.c_int), ("k2", ctypes.c_int), ("mcg", ctypes.c_int),
+                    ("mul1", ctypes.c_int), ("out_col", ctypes.c_int)]
+    lib.exl3_gemv_workspace_bytes.restype = ctypes.c_size_t
+    lib.exl3_gemv_workspace_bytes.argtypes = [ctypes.POINTER(Shard), ctypes.c_int, ctypes.c_int, ctypes.c_int]
+    vp = ctypes.c_void_p
+    lib.exl3_gemv_grouped.argtypes = [ctypes.POINTER(Shard), ctypes.c_int, vp, vp, ctypes.c_int, ctypes.c_int,
+                                      ctypes.c_int, vp, ctypes.c_size_t, vp]
+    arr = (Shard * 3)(Shard(4096, 4096, 4096, 6144, 8, 0, 0, 0), Shard(4096, 4096, 4096, 1024, 10, 0, 0, 6144),
+                      Shard(4096, 4096, 4096, 1024, 12, 0, 0, 7168))
+    need = lib.exl3_gemv_workspace_bytes(arr, 3, 16, 5120)
+    assert 256 < need < 64 << 20 and need % 4 == 0
+    assert lib.exl3_gemv_workspace_bytes(arr, 3, 17, 5120) == 0      # too many rows
+    assert lib.exl3_gemv_workspace_bytes(arr, 3, 1, 5000) == 0       # ic not a multiple of 128
+    fake = vp(4096)
+    assert lib.exl3_gemv_grouped(arr, 3, fake, fake, 1, 5120, 8192, None, 0, None) == -5    # no workspace
+    assert lib.exl3_gemv_grouped(arr, 3, fake, fake, 1, 5120, 4096, fake, 1 << 30, None) == -1  # ldy too small
+    arr[1].mul1 = 1
+    assert lib.exl3_gemv_grouped(arr, 3, fake, fake, 1, 5120, 8192, fake, 1 << 30, None) == -3
