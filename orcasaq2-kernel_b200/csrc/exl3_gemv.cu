@@ -22,21 +22,28 @@
 
 #include "exl3_codec.cuh"
 #include "exl3_common.cuh"
+#include "exl3_decode_fast.cuh"
 #include "exl3_hadamard.cuh"
 
 namespace exl3 {
 
 constexpr int kWarps = 8;
 constexpr int kThreads = kWarps * 32;
-constexpr int kRowGroups = 4;          // warps along the input dimension
-constexpr int kDepth = 8;              // ring slots per warp
+// Ring slots per warp.  About 48-64 KB of trellis in flight per SM keeps HBM busy; measured on
+// B200, deeper rings LOSE bandwidth again (1 KB pieces: 7.2 TB/s at depth 4, 3.0 TB/s at depth 8).
+__host__ __device__ constexpr int ring_depth(int K) { return K <= 4 ? 4 : 3; }
 constexpr int kTargetCtas = 296;       // two resident CTAs on each of 148 SMs
 constexpr int kXfMaxBytes = 48 * 1024; // activation fragments
 constexpr int kBarBytes = 1024;
 constexpr int kSpinLimit = 1 << 22;
 constexpr unsigned kStatusTimeout = 1u;
 
+// Workspace layout: [status word, 256 B][arrival tickets, fixed capacity][split-K partial sums].
+// The ticket area has a FIXED size so that the partial sums of one launch can never land on the
+// tickets of a later launch with a different shape (tickets must stay zero between launches).
 constexpr int kWsStatusBytes = 256;
+constexpr int kWsMaxUnits = 8192;                 // 128-column blocks per launch (oc total <= 1M)
+constexpr size_t kWsHeadBytes = kWsStatusBytes + (size_t)kWsMaxUnits * 4;
 
 struct GemvShardDev {
     const uint32_t *trellis;
@@ -60,6 +67,8 @@ struct GemvParams {
     int rows, ic, ldy, kblocks;
     int nb;         // rows held per group of eight (1, 2, 4 or 8)
     int xf_bytes;   // bytes reserved for activation fragments
+    int xf_blocks;  // 128-blocks of fragments those bytes hold
+    uint32_t one;   // the value 1, opaque to the compiler (keeps multiplies on the multiply pipe)
     int nshards;
     GemvShardDev sh[EXL3_MAX_SHARDS];
 };
@@ -132,26 +141,27 @@ __device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&w)[K 
 template <int K, int NT>
 __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev &S, int local,
                                          unsigned char *smem) {
+    constexpr int kDepth = ring_depth(K);
+    constexpr int kHalfWords = 4 * 8 * K;            // four tiles
+    constexpr int kStageWords = 2 * kHalfWords;      // one tile row of the 128-column block
+    constexpr uint32_t kStageBytes = kStageWords * 4;
+
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
-    const int wc = warp & 1;        // which half of the 128 output channels
-    const int wr = warp >> 1;       // interleave over input tiles
     const int g = lane >> 2, q = lane & 3;
     const int NB = P.nb;
+    const DecodeConsts dc(P.one);
 
     const int ob = local / S.splitk, ks = local - ob * S.splitk;
     const int kb0 = (int)((long long)ks * P.kblocks / S.splitk);
     const int kb1 = (int)((long long)(ks + 1) * P.kblocks / S.splitk);
-    const int nblk = kb1 - kb0;
-    const int nsteps = nblk * 2;    // 8 tiles per block / 4 row groups
+    const int nblk = kb1 - kb0;                      // = steps per warp (one tile of each block)
 
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
     uint32_t *xf = reinterpret_cast<uint32_t *>(smem + kBarBytes);
     unsigned char *region = smem + kBarBytes + P.xf_bytes;
-    constexpr int kStageWords = 4 * 8 * K;          // four tiles
-    constexpr uint32_t kStageBytes = kStageWords * 4;
     uint32_t *ring = reinterpret_cast<uint32_t *>(region) + warp * (kDepth * kStageWords);
-    const uint32_t bar0 = smem_u32(bars + warp * kDepth);
+    const uint32_t bar0 = smem_u32(bars + warp * 8);
     const uint32_t ring0 = smem_u32(ring);
 
     if (lane == 0) {
@@ -162,26 +172,45 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     }
     __syncwarp();
 
-    const uint32_t *src0 =
-        S.trellis + ((size_t)(kb0 * 8 + wr) * S.tiles_j + (size_t)(ob * 8 + wc * 4)) * (size_t)(8 * K);
-    const size_t src_step = (size_t)4 * S.tiles_j * (8 * K);   // four tile rows further
+    // warp w owns tile rows kb0*8 + w + 8*s of the 128-column block ob
+    const uint32_t *src0 = S.trellis + ((size_t)(kb0 * 8 + warp) * S.tiles_j + (size_t)ob * 8) * (size_t)(8 * K);
+    const size_t src_step = (size_t)8 * S.tiles_j * (8 * K);
     if (lane == 0) {
-        const int pre = nsteps < kDepth ? nsteps : kDepth;
+        const int pre = nblk < kDepth ? nblk : kDepth;
         for (int s = 0; s < pre; ++s) {
             mbar_expect_tx(bar0 + 8 * s, kStageBytes);
             bulk_g2s(ring0 + s * kStageBytes, src0 + s * src_step, kStageBytes, bar0 + 8 * s);
         }
     }
 
-    // ---- prologue: H128(x * suh) for the slice, in B-fragment order, both halves equal
-    {
-        const int nrow = NT * NB;
-        const int tasks = nrow * nblk;
-        for (int task = warp; task < tasks; task += kWarps) {
+    float acc[NT][2][4][4];
+#pragma unroll
+    for (int t = 0; t < NT; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) acc[t][h][a][e] = 0.f;
+
+    const int nrow = NT * NB;
+    const int xf_tile_words = nrow * 16;             // words of fragments per tile
+    const uint32_t *xf_lane = xf + ((g & (NB - 1)) * 4 + q) * 4 + warp * xf_tile_words;
+    const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
+    const int sub_max = P.xf_blocks;                 // blocks of fragments that fit at once
+    int slot = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+
+    for (int b0 = 0; b0 < nblk; b0 += sub_max) {
+        const int nb_sub = min(sub_max, nblk - b0);
+        if (b0) __syncthreads();                     // the previous fragments are no longer read
+        // ---- H128(x * suh) for these blocks, in B-fragment order, both halves equal
+        for (int task = warp; task < nrow * nb_sub; task += kWarps) {
             const int blk = task / nrow, n = task - blk * nrow;
             float v[4] = {0.f, 0.f, 0.f, 0.f};
             if (n < P.rows) {
-                const int col = (kb0 + blk) * 128 + 4 * lane;
+                const int col = (kb0 + b0 + blk) * 128 + 4 * lane;
                 const uint2 xr = *reinterpret_cast<const uint2 *>(P.x + (size_t)n * P.ic + col);
                 const uint2 sr = __ldg(reinterpret_cast<const uint2 *>(S.suh + col));
                 const __half2 x01 = *reinterpret_cast<const __half2 *>(&xr.x);
@@ -197,75 +226,76 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             const int tile_local = blk * 8 + (lane >> 2);
             const int t = (NT == 2) ? (n >> 3) : 0;
             const int nn = (NT == 2) ? (n & 7) : n;
-            uint32_t *dst = xf + (((size_t)(tile_local * NT + t) * NB + nn) * 4) * 4 + (lane & 3);
+            uint32_t *dst = xf + (size_t)tile_local * xf_tile_words + ((t * NB + nn) * 4) * 4 + (lane & 3);
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
                 const __half2 d = __float2half2_rn(v[k] * kHadScale);
                 dst[k * 4] = *reinterpret_cast<const uint32_t *>(&d);
             }
         }
-    }
-    __syncthreads();
+        __syncthreads();
 
-    // ---- main loop
-    float acc[NT][4][4];
+        // ---- stream, decode, multiply
+        const uint32_t *xfp = xf_lane;
+        for (int s = b0; s < b0 + nb_sub && ok; ++s) {
+            ok = mbar_wait(bar0 + 8 * slot, phase, P.status);
+            const uint32_t *stage = ring + slot * kStageWords + lane * K;
+            uint32_t wa[K + 1], wb[K + 1];
+            load_words<K>(stage, wa);
+            load_words<K>(stage + kHalfWords, wb);
+            uint4 xa[NT];
 #pragma unroll
-    for (int t = 0; t < NT; ++t)
-#pragma unroll
-        for (int a = 0; a < 4; ++a)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) acc[t][a][e] = 0.f;
+            for (int t = 0; t < NT; ++t) xa[t] = *reinterpret_cast<const uint4 *>(xfp + t * NB * 16);
+            xfp += 8 * xf_tile_words;
+            wa[K] = __shfl_sync(0xffffffffu, wa[0], nxt_lane);
+            wb[K] = __shfl_sync(0xffffffffu, wb[0], nxt_lane);
 
-    const int nsel = g & (NB - 1);
-    const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
-    bool ok = true;
-    for (int s = 0; s < nsteps && ok; ++s) {
-        const int slot = s & (kDepth - 1);
-        ok = mbar_wait(bar0 + 8 * slot, (s / kDepth) & 1, P.status);
-        uint32_t wd[K + 1];
-        load_words<K>(ring + slot * kStageWords + lane * K, wd);
-        const int tile_local = wr + 4 * s;
-        uint4 xa[NT];
+            uint32_t z[32];
+            decode_chunk_fast<K>(wa, z, dc);
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
-            xa[t] = *reinterpret_cast<const uint4 *>(xf + (((size_t)(tile_local * NT + t) * NB + nsel) * 4 + q) * 4);
-        wd[K] = __shfl_sync(0xffffffffu, wd[0], nxt_lane);
-        __syncwarp();
-        if (lane == 0 && s + kDepth < nsteps) {
-            // the slot has been read by every lane; hand it back to the async proxy
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            mbar_expect_tx(bar0 + 8 * slot, kStageBytes);
-            bulk_g2s(ring0 + slot * kStageBytes, src0 + (size_t)(s + kDepth) * src_step, kStageBytes,
-                     bar0 + 8 * slot);
-        }
-        uint32_t z[32];
-        decode_chunk<K>(wd, z);
+            for (int bsel = 0; bsel < 2; ++bsel)
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
+                for (int a = 0; a < 4; ++a)
 #pragma unroll
-            for (int t = 0; t < NT; ++t) {
-                mma16816(acc[t][a], &z[8 * a], xa[t].x, xa[t].y);
-                mma16816(acc[t][a], &z[8 * a + 4], xa[t].z, xa[t].w);
+                    for (int t = 0; t < NT; ++t)
+                        mma16816(acc[t][0][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
+            decode_chunk_fast<K>(wb, z, dc);
+            // every lane has consumed the slot (its words are in registers): refill it
+            __syncwarp();
+            if (lane == 0 && s + kDepth < nblk) {
+                mbar_expect_tx(bar0 + 8 * slot, kStageBytes);
+                bulk_g2s(ring0 + slot * kStageBytes, src0 + (size_t)(s + kDepth) * src_step, kStageBytes,
+                         bar0 + 8 * slot);
             }
+#pragma unroll
+            for (int bsel = 0; bsel < 2; ++bsel)
+#pragma unroll
+                for (int a = 0; a < 4; ++a)
+#pragma unroll
+                    for (int t = 0; t < NT; ++t)
+                        mma16816(acc[t][1][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
+            if (++slot == kDepth) { slot = 0; phase ^= 1u; }
         }
     }
     __syncthreads();   // every warp is done with its ring: the region is reused below
 
-    // ---- reduce the four row-group warps
-    float *red = reinterpret_cast<float *>(region);                  // [4][NT*8][128]
-    float *fin = red + kRowGroups * (NT * 8) * 128;                  // [NT*8][128]
+    // ---- reduce the eight warps
+    float *red = reinterpret_cast<float *>(region);                  // [8][NT*8][128]
+    float *fin = red + kWarps * (NT * 8) * 128;                      // [NT*8][128]
     {
         const int u = g >> 1, p = g & 1;
 #pragma unroll
         for (int t = 0; t < NT; ++t)
 #pragma unroll
-            for (int a = 0; a < 4; ++a) {
-                const int oc_lo = 64 * wc + 16 * u + 4 * a + p;
-                const int n0 = 8 * t + 2 * q;
-                float *r0 = red + ((size_t)(wr * (NT * 8) + n0)) * 128 + oc_lo;
-                if (n0 < P.rows) { r0[0] = acc[t][a][0]; r0[2] = acc[t][a][2]; }
-                if (n0 + 1 < P.rows) { r0[128] = acc[t][a][1]; r0[130] = acc[t][a][3]; }
-            }
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int a = 0; a < 4; ++a) {
+                    const int oc_lo = 64 * h + 16 * u + 4 * a + p;
+                    const int n0 = 8 * t + 2 * q;
+                    float *r0 = red + ((size_t)(warp * (NT * 8) + n0)) * 128 + oc_lo;
+                    if (n0 < P.rows) { r0[0] = acc[t][h][a][0]; r0[2] = acc[t][h][a][2]; }
+                    if (n0 + 1 < P.rows) { r0[128] = acc[t][h][a][1]; r0[130] = acc[t][h][a][3]; }
+                }
     }
     __syncthreads();
 
@@ -275,7 +305,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     for (int n = tid >> 7; n < P.rows; n += 2) {
         float v = 0.f;
 #pragma unroll
-        for (int r = 0; r < kRowGroups; ++r) v += red[((size_t)(r * (NT * 8) + n)) * 128 + ocl];
+        for (int r = 0; r < kWarps; ++r) v += red[((size_t)(r * (NT * 8) + n)) * 128 + ocl];
         if (S.splitk == 1) fin[n * 128 + ocl] = v;
         else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
     }
@@ -342,7 +372,7 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const __grid_constant
 // ---------------------------------------------------------------------------------------------
 // host-side plan: how the shards are cut into CTAs and how the scratch is laid out
 struct GemvPlan {
-    int nt, nb, xf_bytes, region_bytes, total_ctas, total_units, kblocks;
+    int nt, nb, xf_bytes, xf_blocks, region_bytes, total_ctas, total_units, kblocks;
     long long partial_floats;
     int splitk[EXL3_MAX_SHARDS], cta_begin[EXL3_MAX_SHARDS], unit_begin[EXL3_MAX_SHARDS], K[EXL3_MAX_SHARDS];
     long long partial_off[EXL3_MAX_SHARDS];
@@ -358,7 +388,6 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     const int frag_bytes_per_block = 8 * pl.nt * pl.nb * 64;
     const int max_slice = kXfMaxBytes / frag_bytes_per_block;
     double total_bytes = 0;
-    int maxK = 0;
     for (int i = 0; i < n; ++i) {
         if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
         if (sh[i].mcg || sh[i].mul1) return EXL3_E_UNSUPPORTED;
@@ -367,17 +396,14 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         if (!sh[i].trellis || !sh[i].suh || !sh[i].svh) return EXL3_E_NULL;
         if (!aligned(sh[i].trellis, 16) || !aligned(sh[i].suh, 8) || !aligned(sh[i].svh, 8)) return EXL3_E_ALIGN;
         pl.K[i] = K;
-        maxK = K > maxK ? K : maxK;
         total_bytes += (double)ic * sh[i].oc * K / 8.0;
     }
-    int ctas = 0, units = 0, max_nblk = 0;
+    int ctas = 0, units = 0, max_nblk = 0, ring = 0;
     long long pf = 0;
     for (int i = 0; i < n; ++i) {
         const int ocb = sh[i].oc / 128;
         const double share = (double)ic * sh[i].oc * pl.K[i] / 8.0 / total_bytes;
         int sk = (int)(kTargetCtas * share / ocb + 0.5);
-        const int min_sk = (pl.kblocks + max_slice - 1) / max_slice;
-        if (sk < min_sk) sk = min_sk;
         if (sk < 1) sk = 1;
         if (sk > pl.kblocks) sk = pl.kblocks;
         pl.splitk[i] = sk;
@@ -389,21 +415,22 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         if (sk > 1) pf += (long long)ocb * sk * rows * 128;
         const int nblk = (pl.kblocks + sk - 1) / sk;
         max_nblk = nblk > max_nblk ? nblk : max_nblk;
+        const int r = kWarps * ring_depth(pl.K[i]) * 8 * 8 * pl.K[i] * 4;
+        ring = r > ring ? r : ring;
     }
+    if (units > kWsMaxUnits) return EXL3_E_SHAPE;
     pl.total_ctas = ctas;
     pl.total_units = units;
     pl.partial_floats = pf;
-    pl.xf_bytes = ((max_nblk * frag_bytes_per_block) + 127) & ~127;
-    const int ring = kWarps * kDepth * 4 * 8 * maxK * 4;
-    const int red = (kRowGroups + 1) * pl.nt * 8 * 128 * 4;
+    pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
+    pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
+    const int red = (kWarps + 1) * pl.nt * 8 * 128 * 4;
     pl.region_bytes = ring > red ? ring : red;
     return EXL3_OK;
 }
 
 static size_t plan_workspace_bytes(const GemvPlan &pl) {
-    size_t b = kWsStatusBytes + (size_t)pl.total_units * 4;
-    b = (b + 255) & ~(size_t)255;
-    return b + (size_t)pl.partial_floats * 4;
+    return kWsHeadBytes + (size_t)pl.partial_floats * 4;
 }
 
 }  // namespace exl3
@@ -433,14 +460,15 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     P.status = reinterpret_cast<unsigned *>(ws);
     P.tickets = reinterpret_cast<unsigned *>(ws + kWsStatusBytes);
-    const size_t head = ((size_t)kWsStatusBytes + (size_t)pl.total_units * 4 + 255) & ~(size_t)255;
-    P.partial = reinterpret_cast<float *>(ws + head);
+    P.partial = reinterpret_cast<float *>(ws + kWsHeadBytes);
     P.rows = rows;
     P.ic = ic;
     P.ldy = ldy;
     P.kblocks = pl.kblocks;
     P.nb = pl.nb;
     P.xf_bytes = pl.xf_bytes;
+    P.xf_blocks = pl.xf_blocks;
+    P.one = 1u;
     P.nshards = nshards;
     for (int i = 0; i < nshards; ++i) {
         GemvShardDev &d = P.sh[i];

@@ -227,6 +227,8 @@ def int8_embed(qweight: torch.Tensor, scales: torch.Tensor, ids: torch.Tensor) -
         raise RuntimeError("scales must hold one value per table row")
     flat = ids.reshape(-1).contiguous()
     out = torch.empty((flat.numel(), hidden), dtype=scales.dtype, device=qweight.device)
+    if flat.numel() == 0:
+        return out.reshape(*ids.shape, hidden)
     _check(lib().exl3_int8_embed(qweight.data_ptr(), scales.data_ptr(), flat.data_ptr(), out.data_ptr(),
                                  flat.numel(), vocab, hidden, int(scales.dtype == torch.bfloat16),
                                  int(flat.dtype == torch.int32), None, _stream(qweight)),

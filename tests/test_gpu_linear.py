@@ -172,3 +172,23 @@ def test_gemm_matches_reconstruct_path(ext):
     ext.had_r_128(y2, y2, None, svg, 1.0)
     rel = (y.float() - y2.float()).abs().max() / y2.float().abs().max()
     assert rel < 5e-3
+
+
+def test_workspace_reuse_across_shapes(ext):
+    """Launches of different shapes share one scratch buffer: the partial sums of one launch must
+    never disturb the arrival tickets of the next (wide layer after a narrower one)."""
+    def run(ic, oc, K, rows, seed):
+        tr, suh, svh, x = R.make_layer(seed, ic, oc, K, rows)
+        xg, trg, sug, svg = x.cuda(), tr.cuda(), suh.cuda(), svh.cuda()
+        y = torch.empty((rows, oc), dtype=torch.half, device="cuda")
+        ext.exl3_gemm(xg, trg, y, sug, torch.empty_like(xg), svg, -1, False, False, 0)
+        xh = torch.empty_like(xg)
+        ext.had_r_128(xg, xh, sug, None, 1.0)
+        w = torch.empty((ic, oc), dtype=torch.half, device="cuda")
+        ext.reconstruct(w, trg, K, False, False)
+        y2 = (xh.float() @ w.float()).half()
+        ext.had_r_128(y2, y2, None, svg, 1.0)
+        return float((y.float() - y2.float()).abs().max() / y2.float().abs().max())
+    for ic, oc, K, rows in [(2560, 8704, 3, 4), (2560, 17408, 3, 4), (512, 1024, 4, 16), (2560, 17408 + 256, 2, 1),
+                            (1024, 128, 6, 3), (2560, 17408, 5, 16)]:
+        assert run(ic, oc, K, rows, ic + oc) < 5e-3, (ic, oc, K, rows)

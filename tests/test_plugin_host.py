@@ -1,0 +1,175 @@
+"""Host-side logic of the plugin mirror on CPU: API surface, fixtures from the reference's own
+Python, shard capture and slot mapping, tensor-parallel slicing, custom-op fake kernels, and the
+loud failure when the CUDA library or a CUDA tensor is missing."""
+import os
+import types
+
+import numpy as np
+import pytest
+import torch
+
+import exl3_ref as R
+
+GOLD = np.load(os.path.join(os.path.dirname(__file__), "golden", "reference_golden.npz"))
+
+
+def test_hadamard_and_t128_match_reference():
+    import orcasaq2
+    assert orcasaq2.BLOCK == 128
+    h = orcasaq2._had("cpu", torch.float64).numpy()
+    assert np.array_equal(np.sign(h).astype(np.int8), GOLD["had_sign"])
+    assert abs(abs(h[0, 0]) - GOLD["had_scale"][0]) < 1e-8
+    y = orcasaq2._t128(torch.from_numpy(GOLD["t128_in"])).numpy()
+    assert np.allclose(y, GOLD["t128_out"], atol=1e-6)
+    assert orcasaq2._had("cpu", torch.float64) is orcasaq2._had("cpu", torch.float64)     # cached
+
+
+def test_exl3_k_and_dispatch_threshold():
+    from orcasaq2 import ops
+    for wd, v, is_int in zip(GOLD["k_widths"], GOLD["k_values"], GOLD["k_is_int"]):
+        k = ops.exl3_K(torch.empty((1, 1, int(wd))))
+        assert float(k) == v and isinstance(k, int) == bool(is_int)
+    assert ops.GEMM_MAX_ROWS == int(GOLD["gemm_max_rows"][0]) == 144
+
+
+def test_custom_op_schemas_and_fake_kernels():
+    from orcasaq2 import ops  # noqa: F401
+    schema = str(torch.ops.orcasaq2.shard_gemm.default._schema)
+    assert "(Tensor x, Tensor trellis, Tensor suh, Tensor svh, SymInt oc, float k, bool mcg, bool mul1) -> Tensor" in schema
+    x = torch.empty((5, 256), dtype=torch.half, device="meta")
+    tr = torch.empty((16, 8, 64), dtype=torch.int16, device="meta")
+    v = torch.empty((256,), dtype=torch.half, device="meta")
+    y = torch.ops.orcasaq2.shard_gemm(x, tr, v, v, 128, 4.0, False, False)
+    assert y.shape == (5, 128) and y.dtype == torch.half and y.device.type == "meta"
+    y = torch.ops.orcasaq2.layer_gemm(x, [tr, tr], [v, v], [v, v], [128, 128], [4.0, 4.0], [False] * 2, [False] * 2)
+    assert y.shape == (5, 256) and y.dtype == torch.half
+
+
+def test_no_cpu_fallback():
+    from orcasaq2 import _ext
+    x = torch.zeros((1, 128), dtype=torch.half)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _ext.had_r_128(x, x, None, None, 1.0)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _ext.reconstruct(torch.zeros((16, 16), dtype=torch.half), torch.zeros((1, 1, 64), dtype=torch.int16), 4, False, False)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _ext.int8_embed(torch.zeros((4, 16), dtype=torch.int8), torch.zeros(4, dtype=torch.half), torch.zeros(1, dtype=torch.long))
+
+
+def test_missing_library_is_loud(monkeypatch):
+    from orcasaq2 import _ext
+    monkeypatch.setattr(_ext, "_lib", None)
+    monkeypatch.setattr(_ext, "_LIB_PATH", "/nonexistent/libexl3_b200.so")
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        _ext.lib()
+
+
+# ----------------------------------------------------------------------------- vLLM-facing classes
+@pytest.fixture(scope="module")
+def cfgmod():
+    import vllm.model_executor.parameter as vp
+    vp.get_tensor_model_parallel_rank = lambda: 0
+    vp.get_tensor_model_parallel_world_size = lambda: 1
+    from orcasaq2 import config
+    return config
+
+
+def test_shard_param_slots_match_reference(cfgmod):
+    p = cfgmod.Exl3ShardParam(suffix="trellis")
+    probes = [None, 0, 1, 3, (0, 1, 2), (2, 3), "q", "k", "v"]
+    assert [repr(s) for s in probes] == list(GOLD["slot_probes"])
+    assert [p.slot(s) for s in probes] == list(GOLD["slot_values"])
+    assert repr(cfgmod.SHARD_IDS) == GOLD["shard_ids"][0]
+    with pytest.raises(ValueError):
+        p.slot("nope")
+    t = torch.arange(6)
+    p.weight_loader(p, t, "k")
+    p.load_qkv_weight(t + 1, shard_id="v")
+    p.load_merged_column_weight(t + 2, shard_id=0)
+    assert set(p.shards) == {0, 1, 2} and p.shards[1] is t and p.numel() == 0
+
+
+def test_quant_config(cfgmod):
+    raw = {"bits": 4.0, "head_bits": 6, "tensor_storage": {
+        "model.layers.0.self_attn.q_proj": {"stored_tensors": {"model.layers.0.self_attn.q_proj.trellis": {}}},
+        "model.layers.0.mlp.gate": {"stored_tensors": {"model.layers.0.mlp.gate.weight": {}}}}}
+    c = cfgmod.Exl3Config.from_config(raw)
+    assert (c.bits, c.codebook, c.head_bits) == (4.0, "mul1", 6.0)
+    assert c.quantized_prefixes == {"model.layers.0.self_attn.q_proj"}
+    assert c.get_name() == "exl3" and c.get_config_filenames() == ["quantization_config.json"]
+    assert torch.half in c.get_supported_act_dtypes() and torch.bfloat16 in c.get_supported_act_dtypes()
+    assert cfgmod._expand("m.layers.0.self_attn.qkv_proj", "qkv_proj") == [
+        "m.layers.0.self_attn.q_proj", "m.layers.0.self_attn.k_proj", "m.layers.0.self_attn.v_proj"]
+    assert cfgmod._expand("m.mlp.down_proj", "down_proj") == ["m.mlp.down_proj"]
+    assert c.get_quant_method(torch.nn.Linear(2, 2), "x") is None
+    assert "Exl3Config(bits=4.0" in repr(c)
+
+
+def test_create_weights_registers_placeholders(cfgmod):
+    m = cfgmod.Exl3LinearMethod(cfgmod.Exl3Config.from_config({}), "l.qkv_proj")
+    layer = torch.nn.Module()
+    m.create_weights(layer, 256, [256, 128, 128], 256, 512, torch.half)
+    for name in ("trellis", "suh", "svh", "mcg", "mul1", "weight"):
+        assert isinstance(getattr(layer, name), cfgmod.Exl3ShardParam)
+    assert layer.exl3_out_total == 512
+
+
+def test_slice_shard_rejects_unaligned(cfgmod):
+    tr, suh, svh, _ = R.make_layer(1, 256, 256, 2, 1)
+    with pytest.raises(RuntimeError, match="128-aligned"):
+        cfgmod.slice_shard(tr, suh, svh, 0, 256, 64, 192)
+    t, a, b = cfgmod.slice_shard(tr, suh, svh, 128, 256, 0, 128)
+    assert t.shape == (8, 8, 32) and a.numel() == 128 and b.numel() == 128 and t.is_contiguous()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_tp_slicing_rules(cfgmod, coracle, monkeypatch, world):
+    """Column-parallel qkv with replicated KV heads and row-parallel down_proj: every rank's
+    slice, run through the oracle, reassembles the unsharded layer."""
+    ic, rows = 256, 2
+    x = torch.randn((rows, ic), generator=torch.Generator().manual_seed(3)).half()
+    # q: 8 blocks of 128 ("heads"), k/v: 2 blocks each -> replicated when world > 2
+    spec = [(1024, 3), (256, 4), (256, 5)]
+    full = [R.make_layer(60 + i, ic, oc, K, 1)[:3] for i, (oc, K) in enumerate(spec)]
+    ref = [coracle.layer(x.numpy(), coracle.reconstruct(t.numpy()), a.numpy(), b.numpy()) for t, a, b in full]
+    m = cfgmod.Exl3LinearMethod(cfgmod.Exl3Config.from_config({}), "l.qkv_proj")
+    kv_part = max(128, 256 // world)
+    layer = types.SimpleNamespace(exl3_tp=dict(in_part=ic, in_full=ic, out_parts=[1024 // world, kv_part, kv_part],
+                                               out_full=1536))
+    got = [[None] * world for _ in spec]
+    for rank in range(world):
+        monkeypatch.setattr(cfgmod, "_tp_info", lambda r=rank: (r, world))
+        for pos, (t, a, b) in enumerate(full):
+            ts, as_, bs = m._slice_for_rank(layer, pos, 3, t, a, b)
+            assert bs.numel() == layer.exl3_tp["out_parts"][pos]
+            got[pos][rank] = coracle.layer(x.numpy(), coracle.reconstruct(ts.numpy()), as_.numpy(), bs.numpy())
+    assert np.allclose(np.concatenate(got[0], 1), ref[0], atol=1e-3)
+    rep = max(1, world // (256 // kv_part))
+    for pos in (1, 2):
+        uniq = [got[pos][r] for r in range(0, world, rep)]
+        assert np.allclose(np.concatenate(uniq, 1), ref[pos], atol=1e-3)
+        for r in range(world):
+            assert np.array_equal(got[pos][r], got[pos][(r // rep) * rep])
+    # row-parallel: partial sums add up
+    ic2, oc2 = 128 * world, 256
+    t, a, b = R.make_layer(70, ic2, oc2, 4, 1)[:3]
+    x2 = torch.randn((rows, ic2), generator=torch.Generator().manual_seed(5)).half()
+    ref2 = coracle.layer(x2.numpy(), coracle.reconstruct(t.numpy()), a.numpy(), b.numpy())
+    layer2 = types.SimpleNamespace(exl3_tp=dict(in_part=128, in_full=ic2, out_parts=[oc2], out_full=oc2))
+    acc = 0
+    for rank in range(world):
+        monkeypatch.setattr(cfgmod, "_tp_info", lambda r=rank: (r, world))
+        ts, as_, bs = m._slice_for_rank(layer2, 0, 1, t, a, b)
+        xs = np.ascontiguousarray(x2.numpy()[:, rank * 128:(rank + 1) * 128])
+        acc = acc + coracle.layer(xs, coracle.reconstruct(ts.numpy()), as_.numpy(), bs.numpy())
+    assert np.allclose(acc, ref2, atol=1e-3)
+
+
+def test_int8_embedding_table_api():
+    from orcasaq2.patches.int8_embedding import Int8EmbeddingTable, apply
+    q, s = R.make_int8_table(2, 8, 16)
+    tab = Int8EmbeddingTable(q, s, torch.half)
+    assert tab.scales.shape == (8, 1) and tab.weight.shape == (8, 16) and tab.weight.dtype == torch.half
+    assert torch.equal(tab.weight, q.half() * s.reshape(-1, 1))
+    with pytest.raises(RuntimeError, match="exllamav3"):
+        apply()
