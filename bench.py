@@ -1,0 +1,421 @@
+"""Benchmark of the EXL3 fused decode path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--rows R] [--impl reference]
+
+Workload (`config.workload`): the mixed-bitwidth decode shards of one 27B-class decoder layer --
+qkv_proj (q 5120->6144 @4 bpw, k 5120->1024 @5, v 5120->1024 @6; one grouped launch),
+gate_up_proj (2 x 5120->17408 @3; one grouped launch), down_proj (17408->5120 @4) -- at batch
+`--rows` (default 1), fp16 activations ~N(0,1), uniform-random trellis words, +-1 sign vectors.
+One step = one pass over the three fused layers (3 kernel launches).  Three independent weight
+sets (3 x 134 MB) are rotated so no step finds its trellis in the 126 MB L2.
+
+metric  = algorithmic bytes (trellis + activations in + out) moved per second, whole job.
+value   = inputs resident in HBM, device-timed with CUDA events.
+e2e     = same metric through the plugin's custom op with HOST activations: pinned host x ->
+          device, three `orcasaq2::layer_gemm` calls, outputs back to pinned host, every step.
+N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
+          down_proj followed by an NCCL all-reduce), strong scaling: the job's total bytes are fixed.
+
+`--impl reference` times the CPU restatement of the reference path (PyTorch on the host cores:
+decode -> Hadamard -> matmul) on a bounded sample of the same workload.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "orcasaq2-kernel_b200"))
+
+# (name, ic, [(oc, K), ...]) -- one grouped launch each
+LAYERS = [
+    ("qkv_proj", 5120, [(6144, 4), (1024, 5), (1024, 6)]),
+    ("gate_up_proj", 5120, [(17408, 3), (17408, 3)]),
+    ("down_proj", 17408, [(5120, 4)]),
+]
+N_SETS = 3
+FALLBACK_HBM_GBS = 6650.0
+
+
+def algorithmic_bytes(ic, spec, rows):
+    """trellis + activations in + activations out (sign vectors, <0.1 %, left out)."""
+    return sum(ic * oc * K // 8 for oc, K in spec) + rows * ic * 2 + rows * sum(oc for oc, _ in spec) * 2
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:                                    # noqa: BLE001
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons, sampled while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.samples, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:                                    # noqa: BLE001
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        self.thread.join(timeout=2)
+        sm, mx, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for s in self.samples:
+            f = [x.strip() for x in s.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx = float(f[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+def make_shard(torch, ic, oc, K, seed, device):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    tr = torch.randint(0, 65536, (ic // 16, oc // 16, 16 * K), generator=g, dtype=torch.int32).to(torch.int16)
+    suh = (torch.randint(0, 2, (ic,), generator=g) * 2 - 1).to(torch.float16)
+    svh = (torch.randint(0, 2, (oc,), generator=g) * 2 - 1).to(torch.float16)
+    return dict(trellis=tr.to(device), suh=suh.to(device), svh=svh.to(device), mcg=False, mul1=False,
+                K=K, ic=ic, oc=oc)
+
+
+def tp_slice(name, ic, spec, rank, world):
+    """This rank's part of a layer: column-parallel slices every shard's outputs, row-parallel
+    (down_proj) slices the inputs.  Replicated KV heads: a shard narrower than 128*world keeps
+    128-wide groups and ranks share them."""
+    if world == 1:
+        return ic, spec, (0, ic), [(0, oc) for oc, _ in spec]
+    if name == "down_proj":
+        part = ic // world
+        return part, spec, (rank * part, (rank + 1) * part), [(0, oc) for oc, _ in spec]
+    out, rng = [], []
+    for oc, K in spec:
+        width = max(128, oc // world)
+        groups = oc // width
+        idx = rank // max(1, world // groups) if groups < world else rank
+        out.append((width, K))
+        rng.append((idx * width, (idx + 1) * width))
+    return ic, out, (0, ic), rng
+
+
+def build_sets(torch, device, rank, world):
+    """N_SETS independent weight sets of this rank's slices (seeded; the full tensors are never
+    materialised for world > 1: a slice of random words is random words)."""
+    sets = []
+    for s in range(N_SETS):
+        layers = []
+        for li, (name, ic, spec) in enumerate(LAYERS):
+            ic_r, spec_r, _, _ = tp_slice(name, ic, spec, rank, world)
+            shards = [make_shard(torch, ic_r, oc, K, 1000 * 2 + 100 * s + 10 * li + i + 7919 * rank, device)
+                      for i, (oc, K) in enumerate(spec_r)]
+            col = 0
+            for sh in shards:
+                sh["out_col"] = col
+                col += sh["oc"]
+            layers.append((name, ic_r, shards, col))
+        sets.append(layers)
+    return sets
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+    from orcasaq2 import _ext
+    from orcasaq2 import ops  # noqa: F401  (registers orcasaq2::layer_gemm)
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("--gpus N > 1 must be launched with torch.distributed.run (one rank per GPU)")
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    _ext.lib()
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    rows = args.rows
+    sets = build_sets(torch, dev, rank, world)
+    xs = {ic: torch.randn((rows, ic), generator=torch.Generator().manual_seed(5)).half().to(dev)
+          for ic in {l[1] for l in sets[0]}}
+    ys = [[torch.empty((rows, tot), dtype=torch.half, device=dev) for (_, _, _, tot) in layers] for layers in sets]
+    full_bytes = sum(algorithmic_bytes(ic, spec, rows) for _, ic, spec in LAYERS)
+
+    def step(i):
+        layers, out = sets[i % N_SETS], ys[i % N_SETS]
+        for (name, ic_r, shards, _), y in zip(layers, out):
+            _ext.gemv_grouped(xs[ic_r], shards, y)
+            if world > 1 and name == "down_proj":
+                dist.all_reduce(y)                          # row-parallel partial sums
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(max(3, args.warmup)):
+        step(i)
+    sampler = ClockSampler(local)
+    barrier()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(args.steps):
+        step(i)
+    e1.record()
+    barrier()
+    ms = e0.elapsed_time(e1)
+    if ms < 300:                                            # keep sampling long enough to see clocks
+        t_end = time.time() + 0.4
+        j = 0
+        while time.time() < t_end:
+            step(j)
+            j += 1
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_step = ms / args.steps
+    value = full_bytes / (ms_step * 1e-3) / 1e9
+
+    if args.skip_extras:
+        if rank == 0:
+            print(json.dumps({"metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)",
+                              "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms_step, 5),
+                              "config": {"workload": ",".join(l[0] for l in LAYERS), "rows": rows},
+                              "note": "profiling run: extras skipped"}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    # ---- end to end: host activations in, host outputs back, through the plugin's custom op
+    hx = {ic: x.cpu().pin_memory() for ic, x in xs.items()}
+    hy = [torch.empty((rows, tot), dtype=torch.half).pin_memory() for (_, _, _, tot) in sets[0]]
+    lay_args = [[([s["trellis"] for s in sh], [s["suh"] for s in sh], [s["svh"] for s in sh],
+                  [s["oc"] for s in sh], [float(s["K"]) for s in sh], [False] * len(sh), [False] * len(sh))
+                 for (_, _, sh, _) in layers] for layers in sets]
+
+    def e2e_step(i):
+        layers = sets[i % N_SETS]
+        for li, (name, ic_r, _, _) in enumerate(layers):
+            xd = hx[ic_r].to(dev, non_blocking=True)
+            y = torch.ops.orcasaq2.layer_gemm(xd, *lay_args[i % N_SETS][li])
+            if world > 1 and name == "down_proj":
+                dist.all_reduce(y)
+            hy[li].copy_(y, non_blocking=True)
+        torch.cuda.synchronize()
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    e2e_s = (time.perf_counter() - t0) / args.steps
+    if world > 1:
+        t = torch.tensor([e2e_s], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+    h2d = sum(rows * ic_r * 2 for (_, ic_r, _, _) in sets[0])
+    d2h = sum(rows * tot * 2 for (_, _, _, tot) in sets[0])
+
+    # ---- roofline of the dominant kernel (the gate_up grouped GEMV), timed alone on rank 0
+    roof = None
+    cpu = None
+    if rank == 0:
+        gi = max(range(len(sets[0])), key=lambda j: sum(s_["ic"] * s_["oc"] * s_["K"] for s_ in sets[0][j][2]))
+        name, ic_r, _, _ = sets[0][gi]
+        spec_r = [(s["oc"], s["K"]) for s in sets[0][gi][2]]
+        kb = algorithmic_bytes(ic_r, spec_r, rows)
+        n = 60
+        for i in range(6):
+            _ext.gemv_grouped(xs[ic_r], sets[i % N_SETS][gi][2], ys[i % N_SETS][gi])
+        torch.cuda.synchronize()
+        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+        evs[0].record()
+        for i in range(n):
+            # rotate through all sets plus the other layers' traffic-free gap: 3 x 67 MB > L2
+            _ext.gemv_grouped(xs[ic_r], sets[i % N_SETS][gi][2], ys[i % N_SETS][gi])
+            evs[i + 1].record()
+        torch.cuda.synchronize()
+        avg_ms = evs[0].elapsed_time(evs[n]) / n
+        peak, kind = measured_peaks()
+        achieved = kb / (avg_ms * 1e-3) / 1e9
+        roof = {"bound": "hbm", "kernel": f"gemv_kernel ({name}, {len(spec_r)} shard(s), one launch)",
+                "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+                "frac": round(achieved / peak, 4), "frac_of_8000_nominal": round(achieved / 8000.0, 4),
+                "algorithmic_bytes_per_launch": kb, "avg_launch_us": round(avg_ms * 1e3, 2),
+                "traffic": NCU_TRAFFIC_BYTES.get((rows, world))}
+        if world == 1:
+            cpu = cpu_baseline(rows)
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    line = {
+        "metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)", "value": round(value, 1),
+        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "ms_per_step": round(ms_step, 5), "higher_is_better": True,
+        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16",
+        "data": "synthetic",
+        "config": {"workload": f"mixed-bitwidth decode shards of one layer (qkv 4/5/6 bpw, gate_up 3 bpw, "
+                               f"down 4 bpw), rows={rows}", "rows": rows,
+                   "bytes_per_step": full_bytes, "l2": "inputs larger than L2: 3 weight sets of 134 MB rotated",
+                   "parallelism": f"tp{world}" if world > 1 else "single GPU",
+                   "pct_of_8TBs_nominal": round(value / 8000.0 * 100, 2)},
+        "e2e": {"value": round(full_bytes / e2e_s / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 5)},
+        "gpu_launches": args.steps * len(LAYERS), "clocks": clocks, "roofline": roof,
+    }
+    if cpu is not None:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# per-launch DRAM traffic of the gate_up kernel from ncu (dram__bytes_read.sum + write), keyed by
+# (rows, world); filled from the captures summarised under profiles/
+NCU_TRAFFIC_BYTES = {}
+
+
+# ------------------------------------------------------------------------------------ CPU arms
+CPU_SAMPLE = ("q shard 5120->6144 @4 bpw", 5120, 6144, 4)
+
+
+def _cpu_layer_once(torch, R, rows, threads):
+    """One pass of the reference's CPU PyTorch path on the sample shard; seconds."""
+    _, ic, oc, K = CPU_SAMPLE
+    tr, suh, svh, x = R.make_layer(4242, ic, oc, K, rows)
+    torch.set_num_threads(threads)
+    t0 = time.perf_counter()
+    y = R.torch_layer(x, tr, suh, svh)
+    dt = time.perf_counter() - t0
+    assert torch.isfinite(y.float()).all()
+    return dt
+
+
+def cpu_baseline(rows):
+    """The oracle's PyTorch-CPU path (decode -> Hadamard -> matmul) on the host cores, on a
+    bounded sample, as the same metric (algorithmic bytes per second)."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import exl3_ref as R
+    threads = os.cpu_count() or 1
+    _, ic, oc, K = CPU_SAMPLE
+    _cpu_layer_once(torch, R, rows, threads)
+    n, total = 0, 0.0
+    while total < 10.0 and n < 8:
+        total += _cpu_layer_once(torch, R, rows, threads)
+        n += 1
+    sec = total / n
+    b = algorithmic_bytes(ic, [(oc, K)], rows)
+    out = {"value": round(b / sec / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": f"{CPU_SAMPLE[0]}, rows={rows}, {n} passes of {sec:.2f} s (PyTorch-CPU restatement "
+                     f"of the reference path, torch.set_num_threads({threads}))"}
+    try:                                                    # second CPU number: the C/OpenMP oracle
+        co = R.COracle()
+        tr, suh, svh, x = R.make_layer(4242, ic, oc, K, rows)
+        t0 = time.perf_counter()
+        w = co.reconstruct(tr.numpy())
+        co.layer(x.numpy(), w, suh.numpy(), svh.numpy())
+        out["c_openmp_value"] = round(b / (time.perf_counter() - t0) / 1e9, 4)
+    except Exception as e:                                  # noqa: BLE001
+        out["c_openmp_value"] = None
+        out["c_openmp_error"] = str(e)[:80]
+    return out
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path (its PyTorch restatement: the trellis
+    kernels themselves live in a wheel that is not part of the reference tree), host cores only.
+    Same metric and config as the GPU arm; each step is one pass over the bounded sample."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import exl3_ref as R
+    threads = os.cpu_count() or 1
+    rows = args.rows
+    steps = max(1, min(args.steps, 6))
+    for _ in range(max(1, min(args.warmup, 2))):
+        _cpu_layer_once(torch, R, rows, threads)
+    t = [_cpu_layer_once(torch, R, rows, threads) for _ in range(steps)]
+    sec = sum(t) / len(t)
+    _, ic, oc, K = CPU_SAMPLE
+    b = algorithmic_bytes(ic, [(oc, K)], rows)
+    v = round(b / sec / 1e9, 4)
+    full_bytes = sum(algorithmic_bytes(i, spec, rows) for _, i, spec in LAYERS)
+    sample = (f"{CPU_SAMPLE[0]}, rows={rows}: each step is one pass over this shard "
+              f"({b} of the workload's {full_bytes} bytes)")
+    print(json.dumps({
+        "impl": "reference", "metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)",
+        "value": v, "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
+        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"mixed-bitwidth decode shards of one layer (qkv 4/5/6 bpw, gate_up 3 bpw, "
+                               f"down 4 bpw), rows={rows}", "rows": rows, "sample": sample},
+        "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--rows", type=int, default=1, choices=range(1, 17))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default=None, choices=[l[0] for l in LAYERS],
+                    help="run just this fused layer each step (small case for profiling)")
+    ap.add_argument("--skip-extras", action="store_true",
+                    help="skip the end-to-end, roofline and CPU-baseline legs (profiling runs)")
+    args = ap.parse_args()
+    if args.only:
+        LAYERS[:] = [l for l in LAYERS if l[0] == args.only]
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()
