@@ -99,6 +99,31 @@ int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, cons
               size_t workspace_bytes, void *stream);
 
 /*
+ * exl3_gemv_grouped without a caller-supplied workspace.  This entry point has no counterpart
+ * in the reference.  It exists for hosts that cannot allocate device memory where the layer
+ * runs: a serving process that has already handed every free byte to its KV-cache pool, an
+ * engine whose hot path is forbidden to call the allocator (no cudaMalloc, no torch caching
+ * allocator) for latency or fragmentation reasons, or a plugin loaded into a runtime that owns
+ * all memory.  The split-K partial sums, arrival tickets and status word live in a fixed array
+ * inside the library (exl3_gemv_static_capacity() bytes, currently 2 MiB, held on every GPU
+ * that loads the library until the process exits); the call itself allocates nothing and calls
+ * no allocating routine.
+ *
+ *   - Inputs, outputs and all argument rules are those of exl3_gemv_grouped.
+ *   - A launch whose scratch need (exl3_gemv_workspace_bytes) exceeds the capacity returns
+ *     EXL3_E_WORKSPACE and launches nothing; use exl3_gemv_grouped with your own buffer then.
+ *   - The FIRST call on each device resolves the array's device address and queues a clear of
+ *     its header on the given stream.  Make that first call with the device current and before
+ *     any stream capture begins.
+ *   - All calls on a device share the one array, which keeps what the last call left in it:
+ *     the kernel restores the parts that must be zero before it exits, but two calls that
+ *     overlap on the GPU (different streams without ordering) race on it.  Serialise them.
+ */
+size_t exl3_gemv_static_capacity(void);
+int exl3_gemv_grouped_static(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                             int ic, int ldy, void *stream);
+
+/*
  * The word at byte offset 0 of a GEMV workspace is a sticky device-side status: 0, or
  * non-zero after a bounded wait inside a kernel ran out.  Read it with a device-to-host copy
  * when diagnosing; it is never set in normal operation.

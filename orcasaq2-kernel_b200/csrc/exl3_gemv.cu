@@ -512,3 +512,50 @@ extern "C" int exl3_gemv(const void *x, const void *trellis, void *y, const void
     s.out_col = 0;
     return exl3_gemv_grouped(&s, 1, x, y, rows, ic, oc, workspace, workspace_bytes, stream);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Allocation-free variant: the scratch of exl3_gemv_grouped lives in this library's own device
+// memory instead of a caller buffer.
+//
+// The array below is reserved on every GPU that loads the library and stays reserved until the
+// process exits.  In HOST code its name is only a handle, not a device address, so the address is
+// looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
+#define EXL3_STATIC_WS_BYTES_IMPL (2u << 20)
+static __device__ __align__(256) unsigned char g_exl3_static_ws[EXL3_STATIC_WS_BYTES_IMPL];
+
+namespace exl3 {
+constexpr int kMaxDevices = 64;
+static void *g_static_ws_ptr[kMaxDevices];       // device address of g_exl3_static_ws, per device
+static int g_static_ws_ready[kMaxDevices];
+
+// First use on the current device: resolve the device address and zero the status word and the
+// tickets (asynchronously, on the caller's stream, ahead of the first launch).
+static int static_ws_for_current_device(cudaStream_t st, void **out) {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    if (!__atomic_load_n(&g_static_ws_ready[dev], __ATOMIC_ACQUIRE)) {
+        void *p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_exl3_static_ws) != cudaSuccess || !p) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+        if (cudaMemsetAsync(p, 0, kWsHeadBytes, st) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+        g_static_ws_ptr[dev] = p;
+        __atomic_store_n(&g_static_ws_ready[dev], 1, __ATOMIC_RELEASE);
+    }
+    *out = g_static_ws_ptr[dev];
+    return EXL3_OK;
+}
+}  // namespace exl3
+
+extern "C" size_t exl3_gemv_static_capacity(void) { return EXL3_STATIC_WS_BYTES_IMPL; }
+
+extern "C" int exl3_gemv_grouped_static(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                                        int ic, int ldy, void *stream) {
+    using namespace exl3;
+    GemvPlan pl;
+    const int rc = make_plan(shards, nshards, rows, ic, pl);
+    if (rc != EXL3_OK) return rc;
+    if (plan_workspace_bytes(pl) > (size_t)EXL3_STATIC_WS_BYTES_IMPL) return EXL3_E_WORKSPACE;   // beyond the built-in scratch
+    void *ws = nullptr;
+    const int rs = static_ws_for_current_device(static_cast<cudaStream_t>(stream), &ws);
+    if (rs != EXL3_OK) return rs;
+    return exl3_gemv_grouped(shards, nshards, x, y, rows, ic, ldy, ws, EXL3_STATIC_WS_BYTES_IMPL, stream);
+}

@@ -56,6 +56,9 @@ def lib():
                 ll = ctypes.c_longlong
                 L.exl3_int8_embed.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp]
                 L.exl3_int8_head.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ci, vp]
+                L.exl3_gemv_static_capacity.restype = sz
+                L.exl3_gemv_grouped_static.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp]
+                L.exl3_gemv_grouped_static.restype = ci
                 for name in ("exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
                              "exl3_int8_embed", "exl3_int8_head"):
                     getattr(L, name).restype = ci
@@ -183,6 +186,36 @@ def gemv_grouped(x: torch.Tensor, shards, y: torch.Tensor) -> None:
     _check(L.exl3_gemv_grouped(arr, len(shards), x.data_ptr(), y.data_ptr(), rows, ic, y.stride(0),
                                None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
                                _stream(x)), "exl3_gemv_grouped")
+
+
+def _shard_array(x: torch.Tensor, shards):
+    rows, ic = x.shape
+    arr = (Exl3Shard * len(shards))()
+    col = 0
+    for i, s in enumerate(shards):
+        tr = _cuda(s["trellis"], "trellis")
+        tic, toc, kk = _trellis_dims(tr)
+        if tic != ic:
+            raise RuntimeError(f"shard {i}: trellis has {tic} input channels, x has {ic}")
+        _cuda(s["suh"], "suh", torch.float16)
+        _cuda(s["svh"], "svh", torch.float16)
+        oc_col = s.get("out_col", col)
+        arr[i] = Exl3Shard(tr.data_ptr(), s["suh"].data_ptr(), s["svh"].data_ptr(), toc, _k2(kk),
+                           int(bool(s.get("mcg"))), int(bool(s.get("mul1"))), oc_col)
+        col = oc_col + toc
+    return arr
+
+
+def gemv_grouped_static(x: torch.Tensor, shards, y: torch.Tensor) -> None:
+    """gemv_grouped on the library's built-in scratch: for callers that may not allocate device
+    memory where the layer runs.  No workspace tensor is created here or in the library; a launch
+    that needs more scratch than the built-in array holds raises.  Calls on one device share that
+    array, so they must not overlap on the GPU."""
+    _cuda(x, "x", torch.float16)
+    _cuda(y, "y", torch.float16)
+    arr = _shard_array(x, shards)
+    _check(lib().exl3_gemv_grouped_static(arr, len(shards), x.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1],
+                                          y.stride(0), _stream(x)), "exl3_gemv_grouped_static")
 
 
 def exl3_gemm(A, trellis, C, suh, A_had, svh, kernel: int, mcg: bool, mul1: bool, acc_mode: int) -> None:
