@@ -202,6 +202,13 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     uint32_t phase = 0;
     bool ok = true;
 
+    // Programmatic dependent launch: everything above touched only constants (the trellis stream
+    // and its barriers).  From here on the kernel reads the activations, which the previous grid
+    // on the stream may still be writing, and later the shared scratch: wait for that grid to
+    // finish, and let the grid after this one begin its own weight prefetch.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+
     for (int b0 = 0; b0 < nblk; b0 += sub_max) {
         const int nb_sub = min(sub_max, nblk - b0);
         if (b0) __syncthreads();                     // the previous fragments are no longer read
@@ -485,16 +492,29 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
     }
     const size_t smem = (size_t)kBarBytes + pl.xf_bytes + pl.region_bytes;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // launched with programmatic stream serialization: this grid may start (and prefetch weights)
+    // while the previous kernel on the stream drains; it synchronises inside (griddepcontrol.wait)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)pl.total_ctas);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
     cudaError_t e;
     if (pl.nt == 1) {
         e = cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-        gemv_kernel<1><<<pl.total_ctas, kThreads, smem, st>>>(P);
+        e = cudaLaunchKernelEx(&cfg, gemv_kernel<1>, P);
     } else {
         e = cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-        gemv_kernel<2><<<pl.total_ctas, kThreads, smem, st>>>(P);
+        e = cudaLaunchKernelEx(&cfg, gemv_kernel<2>, P);
     }
+    if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     return launch_status();
 }
 
