@@ -99,6 +99,23 @@ int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, cons
               size_t workspace_bytes, void *stream);
 
 /*
+ * Many-row form (mid-batch and prefill):  y[rows][oc] = H(H(x*suh) W) * svh  with the trellis
+ * decoded inside the kernel into shared-memory fp16 tiles that feed tcgen05.mma (fp32
+ * accumulators in tensor memory); the decoded weight is never written to global memory.
+ * x is fp16 (or bf16 when x_is_bf16; it is narrowed to fp16 as the reference does,
+ * orcasaq2/config.py:233), y fp16, xh_scratch a caller buffer of rows*ic fp16 (the reference's
+ * `xh`, orcasaq2/ops.py:53).  Replaces the rows > GEMM_MAX_ROWS branch
+ * had_r_128 -> reconstruct -> hgemm_recon -> had_r_128 of orcasaq2/ops.py:50-59 (and serves
+ * 17..144 rows, which the reference sends to exl3_gemm).  Three launches on `stream`.
+ * exl3_gemm_tc_status() returns a sticky device word that is non-zero only if a bounded wait
+ * inside the kernel ran out (it synchronises the device; for diagnosis and tests).
+ */
+int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
+                 void *xh_scratch, int rows, int ic, int oc, int k_times_2, int mcg, int mul1,
+                 int x_is_bf16, void *stream);
+unsigned exl3_gemm_tc_status(void);
+
+/*
  * exl3_gemv_grouped without a caller-supplied workspace.  This entry point has no counterpart
  * in the reference.  It exists for hosts that cannot allocate device memory where the layer
  * runs: a serving process that has already handed every free byte to its KV-cache pool, an

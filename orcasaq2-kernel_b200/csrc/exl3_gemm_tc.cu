@@ -1,0 +1,444 @@
+// EXL3 GEMM for many rows (mid-batch and prefill): trellis decode into shared-memory fp16 tiles
+// that feed tcgen05.mma, accumulators in tensor memory.
+//
+//     Yt[tokens][oc] = Xh[tokens][ic] . W(trellis)[ic][oc]          (fp16 in, fp32 accumulate, fp16 out)
+//
+// where Xh = H128(x * suh) is produced by a small pre-pass and the output Hadamard / svh by a
+// post-pass (exl3_gemm_tc below chains the three).  The weights are the M side of the MMA (128
+// output channels per CTA = the 128 TMEM lanes), tokens the N side (up to 512 per CTA = all 512
+// TMEM columns), so every decoded weight tile is used for up to 512 tokens.
+//
+// CTA = 10 warps, one CTA per SM:
+//   warp 0      producer: 1-D bulk copies of packed trellis rows and 2-D tiled TMA loads (128-byte
+//               swizzle) of the activation tiles, mbarrier completion
+//   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
+//   warps 2..9  decode: packed words -> 3INST codewords -> fp16 (the same rounding as
+//               reconstruct) -> swizzled K-major A tile in shared memory; afterwards the epilogue
+//               (tcgen05.ld of their TMEM lane quadrant, fp16 stores)
+// The K order inside each 16-channel tile is permuted (k' = 4*(ic&3) + (ic>>2)) so that the four
+// input channels a lane decodes for one output channel are adjacent in shared memory; the
+// pre-pass writes Xh in the same order, which leaves the contraction unchanged.
+// Every wait is bounded; a wait that runs out sets a status word and the kernel still frees its
+// tensor memory and exits.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "exl3_codec.cuh"
+#include "exl3_common.cuh"
+#include "exl3_decode_fast.cuh"
+#include "exl3_hadamard.cuh"
+
+namespace exl3 {
+namespace tc {
+
+constexpr int kThreads = 320;            // 10 warps
+constexpr int kDecodeWarps = 8;
+constexpr int kBM = 128;                 // output channels per CTA
+constexpr int kBK = 64;                  // input channels per stage (one 128-byte swizzle row)
+constexpr int kBN = 256;                 // tokens per accumulator / per TMA box
+constexpr int kMaxHalves = 2;            // accumulators per CTA (512 tokens)
+constexpr int kStagesA = 3;
+constexpr int kStagesB = 2;
+constexpr int kStagesRaw = 4;
+constexpr int kABytes = kBM * kBK * 2;               // 16 KB
+constexpr int kBHalfBytes = kBN * kBK * 2;           // 32 KB
+constexpr int kBBytes = kBHalfBytes * kMaxHalves;    // 64 KB
+constexpr int kSpin = 1 << 26;
+constexpr unsigned long long kWaitNs = 1000000000ull;   // one second
+
+static __device__ unsigned g_tc_status;  // sticky: non-zero after a bounded wait ran out
+
+__device__ __forceinline__ uint32_t s32(const void *p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ unsigned long long now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait: polls the barrier; after kWaitNs without success it records the failure in the
+// status word and returns false (the caller stops its loop, the kernel still exits cleanly).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+    unsigned long long t0 = 0;
+    for (int it = 0; it < kSpin; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((it & 255) == 255) {
+            const unsigned long long t = now_ns();
+            if (t0 == 0) t0 = t;
+            else if (t - t0 > kWaitNs) break;
+        }
+    }
+    atomicOr(&g_tc_status, 1u);
+    return false;
+}
+__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar) : "memory");
+}
+
+// K-major, 128-byte-swizzled operand whose rows are exactly 128 bytes: 8-row groups are 1024 bytes
+// apart (SBO), the leading-dimension field is unused, descriptor version 1, layout type 2.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// kind::f16, fp16 A and B (both K-major), fp32 accumulate, M = 128, N = n
+__device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+__device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct Params {
+    const uint32_t *trellis;
+    __half *y;             // [tokens][ldy]
+    int tokens, ic, oc, ldy;
+    int tiles_j;           // oc / 16
+    uint32_t one;
+};
+
+struct __align__(1024) Smem {
+    unsigned char a[kStagesA][kABytes];
+    unsigned char b[kStagesB][kBBytes];
+    uint64_t raw_full[kStagesRaw], raw_empty[kStagesRaw];
+    uint64_t a_full[kStagesA], a_empty[kStagesA];
+    uint64_t b_full[kStagesB], b_empty[kStagesB];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+};
+
+template <int K>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+    extern __shared__ unsigned char smem_dyn[];
+    // swizzled tiles need 1024-byte alignment; the launch reserves the slack
+    unsigned char *smem_raw = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);
+    Smem &S = *reinterpret_cast<Smem *>(smem_raw);
+    constexpr int kRawWords = 4 * 8 * 8 * K;                      // four tile rows of eight tiles
+    constexpr uint32_t kRawRowBytes = 8 * 8 * K * 4;
+    uint32_t *raw = reinterpret_cast<uint32_t *>(smem_raw + sizeof(Smem));
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ob = blockIdx.x;                                    // 128-column block of outputs
+    const int tok0 = blockIdx.y * (kBN * kMaxHalves);
+    const int tok_here = min(P.tokens - tok0, kBN * kMaxHalves);
+    const int halves = tok_here > kBN ? 2 : 1;
+    const int nsteps = P.ic / kBK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStagesRaw; ++s) { mbar_init(s32(&S.raw_full[s]), 1); mbar_init(s32(&S.raw_empty[s]), kDecodeWarps); }
+        for (int s = 0; s < kStagesA; ++s) { mbar_init(s32(&S.a_full[s]), kDecodeWarps); mbar_init(s32(&S.a_empty[s]), 1); }
+        for (int s = 0; s < kStagesB; ++s) { mbar_init(s32(&S.b_full[s]), 1); mbar_init(s32(&S.b_empty[s]), 1); }
+        mbar_init(s32(&S.acc_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {   // tensor memory: all 512 columns (one CTA per SM by construction)
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(s32(&S.tmem_base)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = S.tmem_base;
+
+    if (warp == 0) {
+        // ---------------- producer
+        if (lane == 0) {
+            const uint32_t *src_row0 = P.trellis + (size_t)ob * 8 * (8 * K);
+            const size_t row_words = (size_t)P.tiles_j * (8 * K);
+            bool ok = true;
+            for (int s = 0; s < nsteps && ok; ++s) {
+                const int rs = s % kStagesRaw, bs = s % kStagesB;
+                if (s >= kStagesRaw) ok = mbar_wait(s32(&S.raw_empty[rs]), ((s / kStagesRaw) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(s32(&S.raw_full[rs]), 4 * kRawRowBytes);
+                for (int r = 0; r < 4; ++r)
+                    bulk_g2s(s32(raw + rs * kRawWords + r * (kRawWords / 4)), src_row0 + (size_t)(4 * s + r) * row_words,
+                             kRawRowBytes, s32(&S.raw_full[rs]));
+                if (s >= kStagesB) ok = mbar_wait(s32(&S.b_empty[bs]), ((s / kStagesB) - 1) & 1);
+                if (!ok) break;
+                mbar_expect_tx(s32(&S.b_full[bs]), (uint32_t)(halves * kBHalfBytes));
+                for (int h = 0; h < halves; ++h)
+                    tma_2d(s32(&S.b[bs][h * kBHalfBytes]), &xmap, s * kBK, tok0 + h * kBN, s32(&S.b_full[bs]));
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue
+        if (lane == 0) {
+            const int n_last = ((tok_here - (halves - 1) * kBN) + 15) & ~15;      // tokens in the last half, padded to 16
+            bool ok = true;
+            for (int s = 0; s < nsteps && ok; ++s) {
+                const int as = s % kStagesA, bs = s % kStagesB;
+                ok = mbar_wait(s32(&S.a_full[as]), (s / kStagesA) & 1);
+                ok = ok && mbar_wait(s32(&S.b_full[bs]), (s / kStagesB) & 1);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a0 = s32(&S.a[as][0]);
+#pragma unroll
+                for (int h = 0; h < kMaxHalves; ++h) {
+                    if (h < halves) {
+                        const uint32_t b0 = s32(&S.b[bs][h * kBHalfBytes]);
+                        const uint32_t idesc = umma_idesc(h == halves - 1 ? n_last : kBN);
+#pragma unroll
+                        for (int k = 0; k < kBK / 16; ++k)
+                            umma(tmem + h * kBN, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (s | k) ? 1u : 0u);
+                    }
+                }
+                umma_commit(s32(&S.a_empty[as]));       // both arrive when the MMAs above have read smem
+                umma_commit(s32(&S.b_empty[bs]));
+            }
+            umma_commit(s32(&S.acc_full));
+        }
+    } else {
+        // ---------------- decode warps
+        const int dw = warp - 2;                   // 0..7
+        const int t_ic = dw >> 1;                  // which of the four 16-channel tiles of the stage
+        const int half_oc = dw & 1;                // which four of the eight output tiles
+        const int u = lane >> 3, c = lane & 7, p = c >> 2, q = c & 3;
+        const DecodeConsts dc(P.one);
+        const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
+        bool ok = true;
+        for (int s = 0; s < nsteps && ok; ++s) {
+            const int rs = s % kStagesRaw, as = s % kStagesA;
+            ok = mbar_wait(s32(&S.raw_full[rs]), (s / kStagesRaw) & 1);
+            uint32_t wd[K + 1];
+            {
+                const uint32_t *src = raw + rs * kRawWords + t_ic * (kRawWords / 4) + half_oc * (4 * 8 * K) + lane * K;
+#pragma unroll
+                for (int k = 0; k < K; ++k) wd[k] = src[k];
+            }
+            wd[K] = __shfl_sync(0xffffffffu, wd[0], nxt_lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s32(&S.raw_empty[rs]));
+            uint32_t z[32];
+            decode_chunk_fast<K>(wd, z, dc);
+            if (s >= kStagesA) ok = ok && mbar_wait(s32(&S.a_empty[as]), ((s / kStagesA) - 1) & 1);
+            // weights of output channel (a, hm): input channels j = 2b + hk, adjacent in k'
+            unsigned char *abase = &S.a[as][0];
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int hm = 0; hm < 2; ++hm) {
+                    const uint32_t z0 = z[8 * a + hm], z1 = z[8 * a + 2 + hm], z2 = z[8 * a + 4 + hm], z3 = z[8 * a + 6 + hm];
+                    uint32_t lo01, hi01, lo23, hi23;
+                    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(lo01) : "r"(z0), "r"(z1));
+                    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(hi01) : "r"(z0), "r"(z1));
+                    asm("prmt.b32 %0, %1, %2, 0x5410;" : "=r"(lo23) : "r"(z2), "r"(z3));
+                    asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(hi23) : "r"(z2), "r"(z3));
+                    const __half2 w01 = __hadd2(*reinterpret_cast<__half2 *>(&lo01), *reinterpret_cast<__half2 *>(&hi01));
+                    const __half2 w23 = __hadd2(*reinterpret_cast<__half2 *>(&lo23), *reinterpret_cast<__half2 *>(&hi23));
+                    const int r = 16 * (4 * half_oc + u) + 4 * a + 2 * hm + p;          // row of the A tile
+                    const int chunk = (2 * t_ic + (q >> 1)) ^ (r & 7);                  // 128-byte swizzle
+                    uint2 v;
+                    v.x = *reinterpret_cast<const uint32_t *>(&w01);
+                    v.y = *reinterpret_cast<const uint32_t *>(&w23);
+                    *reinterpret_cast<uint2 *>(abase + r * 128 + chunk * 16 + (q & 1) * 8) = v;
+                }
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s32(&S.a_full[as]));
+        }
+
+        // ---------------- epilogue: TMEM -> fp16 -> y[token][oc]
+        ok = mbar_wait(s32(&S.acc_full), 0) && ok;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
+        const int oc_row = ob * kBM + 32 * quad + lane;
+        // the two warps of a quadrant split the columns of every half
+        const int col_part = dw >> 2;
+        for (int h = 0; h < halves; ++h) {
+            const int ncols = min(kBN, tok_here - h * kBN);
+            for (int c0 = col_part * 32; c0 < ncols; c0 += 64) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(h * kBN + c0);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) {
+                        const int tok = tok0 + h * kBN + c0 + j;
+                        if (c0 + j < ncols) P.y[(size_t)tok * P.ldy + oc_row] = __float2half_rn(__uint_as_float(v[j]));
+                    }
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+    }
+}
+
+// Pre-pass: Xh = H128(x * suh) as fp16, with the K order permuted inside every 16-channel tile
+// (channel 8b + 4h + q is stored at 4q + 2b + h) to match the A tiles written by the decode warps.
+// x may be fp16 or bf16 (the reference casts activations to fp16 first: config.py:233).
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __half *__restrict__ xh,
+                  long long nblocks, int blocks_per_row) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wid >= nblocks) return;
+    const int blk = (int)(wid % blocks_per_row);
+    const size_t off = (size_t)wid * 128 + 4 * lane;
+    float v[4];
+    if (BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(x) + off);
+        v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k]));      // the reference's .half()
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __half *>(x) + off);
+        const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
+        v[0] = __low2float(h01); v[1] = __high2float(h01); v[2] = __low2float(h23); v[3] = __high2float(h23);
+    }
+    const uint2 sr = *reinterpret_cast<const uint2 *>(suh + blk * 128 + 4 * lane);
+    const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x), s23 = *reinterpret_cast<const __half2 *>(&sr.y);
+    v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
+    fwht128_warp(v, lane);
+    // lane holds channels 16T + 4*(lane&3) + j (j = 0..3) of tile T = lane >> 2: b = (lane&3)>>1,
+    // h = lane&1, q = j  ->  position 4j + (lane&3)
+    __half *dst = xh + (size_t)wid * 128 + 16 * (lane >> 2) + (lane & 3);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[4 * j] = __float2half_rn(v[j] * kHadScale);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                  const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void *p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(p);
+        else
+            cudaGetLastError();
+    }
+    return fn;
+}
+
+template <int K>
+static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
+    const size_t smem = sizeof(Smem) + (size_t)kStagesRaw * (4 * 8 * 8 * K) * 4 + 1024;
+    if (cudaFuncSetAttribute(gemm_tc_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    dim3 grid(P.oc / kBM, (P.tokens + kBN * kMaxHalves - 1) / (kBN * kMaxHalves));
+    gemm_tc_kernel<K><<<grid, kThreads, smem, st>>>(map, P);
+    return launch_status();
+}
+
+}  // namespace tc
+}  // namespace exl3
+
+extern "C" int exl3_had_r_128(const void *in, void *out, const void *pre, const void *post, float scale, int rows,
+                              int n, void *stream);
+
+extern "C" unsigned exl3_gemm_tc_status(void) {
+    unsigned v = 0;
+    if (cudaMemcpyFromSymbol(&v, exl3::tc::g_tc_status, sizeof(v)) != cudaSuccess) { cudaGetLastError(); return ~0u; }
+    return v;
+}
+
+extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
+                            void *xh_scratch, int rows, int ic, int oc, int k_times_2, int mcg, int mul1,
+                            int x_is_bf16, void *stream) {
+    using namespace exl3;
+    using namespace exl3::tc;
+    if (!x || !trellis || !y || !suh || !svh || !xh_scratch) return EXL3_E_NULL;
+    if (rows < 1 || ic <= 0 || oc <= 0 || (ic & 127) || (oc & 127) || oc / kBM > 65535) return EXL3_E_SHAPE;
+    if (mcg || mul1) return EXL3_E_UNSUPPORTED;
+    const int K = integer_k(k_times_2);
+    if (!K) return EXL3_E_UNSUPPORTED;
+    if (!aligned(x, 8) || !aligned(y, 8) || !aligned(trellis, 16) || !aligned(xh_scratch, 16) || !aligned(suh, 8) ||
+        !aligned(svh, 8))
+        return EXL3_E_ALIGN;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return EXL3_E_LAUNCH;
+
+    // 1. rotate and permute the activations
+    const long long nblocks = (long long)rows * (ic / 128);
+    const unsigned g1 = (unsigned)((nblocks + 7) / 8);
+    if (x_is_bf16)
+        xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(xh_scratch), nblocks, ic / 128);
+    else
+        xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(xh_scratch), nblocks, ic / 128);
+    if (cudaGetLastError() != cudaSuccess) return EXL3_E_LAUNCH;
+
+    // 2. decode + tcgen05 contraction
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
+    const cuuint64_t gstr[1] = {(cuuint64_t)ic * 2};
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBN};
+    const cuuint32_t estr[2] = {1, 1};
+    if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh_scratch, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return EXL3_E_LAUNCH;
+    Params P;
+    P.trellis = static_cast<const uint32_t *>(trellis);
+    P.y = static_cast<__half *>(y);
+    P.tokens = rows; P.ic = ic; P.oc = oc; P.ldy = oc; P.tiles_j = oc / 16; P.one = 1u;
+    int rc;
+    switch (K) {
+        case 1: rc = launch<1>(map, P, st); break;
+        case 2: rc = launch<2>(map, P, st); break;
+        case 3: rc = launch<3>(map, P, st); break;
+        case 4: rc = launch<4>(map, P, st); break;
+        case 5: rc = launch<5>(map, P, st); break;
+        case 6: rc = launch<6>(map, P, st); break;
+        case 7: rc = launch<7>(map, P, st); break;
+        default: rc = launch<8>(map, P, st); break;
+    }
+    if (rc != EXL3_OK) return rc;
+
+    // 3. output rotation and signs, in place
+    return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
+}

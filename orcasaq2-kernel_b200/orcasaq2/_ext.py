@@ -56,6 +56,9 @@ def lib():
                 ll = ctypes.c_longlong
                 L.exl3_int8_embed.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp]
                 L.exl3_int8_head.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ci, vp]
+                L.exl3_gemm_tc.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]
+                L.exl3_gemm_tc.restype = ci
+                L.exl3_gemm_tc_status.restype = ctypes.c_uint
                 L.exl3_gemv_static_capacity.restype = sz
                 L.exl3_gemv_grouped_static.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp]
                 L.exl3_gemv_grouped_static.restype = ci
@@ -288,3 +291,26 @@ def int8_head(qweight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor) -> t
                                 out[r0:r1].data_ptr(), r1 - r0, vocab, hidden, vocab,
                                 int(x.dtype == torch.bfloat16), _stream(x)), "exl3_int8_head")
     return out
+
+
+def gemm_tc(x: torch.Tensor, trellis: torch.Tensor, y: torch.Tensor, suh: torch.Tensor, svh: torch.Tensor,
+            mcg: bool = False, mul1: bool = False) -> None:
+    """y[rows, oc] <- H(H(x*suh) W) * svh for many rows: in-kernel trellis decode into shared-memory
+    tiles feeding tcgen05.mma.  x fp16 or bf16, y fp16."""
+    _cuda(x, "x", _DT)
+    _cuda(y, "y", torch.float16)
+    _cuda(trellis, "trellis")
+    _cuda(suh, "suh", torch.float16)
+    _cuda(svh, "svh", torch.float16)
+    ic, oc, kk = _trellis_dims(trellis)
+    rows = x.shape[0]
+    if x.shape[1] != ic or tuple(y.shape) != (rows, oc) or suh.numel() != ic or svh.numel() != oc:
+        raise RuntimeError("gemm_tc: shapes of x, y, suh, svh do not match the trellis")
+    xh = torch.empty((rows, ic), dtype=torch.float16, device=x.device)
+    _check(lib().exl3_gemm_tc(x.data_ptr(), trellis.data_ptr(), y.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                              xh.data_ptr(), rows, ic, oc, _k2(kk), int(bool(mcg)), int(bool(mul1)),
+                              int(x.dtype == torch.bfloat16), _stream(x)), "exl3_gemm_tc")
+
+
+def gemm_tc_status() -> int:
+    return int(lib().exl3_gemm_tc_status())
