@@ -103,16 +103,18 @@ int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, cons
  * decoded inside the kernel into shared-memory fp16 tiles that feed tcgen05.mma (fp32
  * accumulators in tensor memory); the decoded weight is never written to global memory.
  * x is fp16 (or bf16 when x_is_bf16; it is narrowed to fp16 as the reference does,
- * orcasaq2/config.py:233), y fp16, xh_scratch a caller buffer of rows*ic fp16 (the reference's
- * `xh`, orcasaq2/ops.py:53).  Replaces the rows > GEMM_MAX_ROWS branch
+ * orcasaq2/config.py:233), y fp16, scratch a caller buffer of exl3_gemm_tc_scratch_bytes() bytes,
+ * 256-byte aligned: the rotated activations (the reference's `xh`, orcasaq2/ops.py:53) and, when the
+ * output grid alone cannot fill the GPU, fp32 partial sums of the input slices.  Replaces the rows > GEMM_MAX_ROWS branch
  * had_r_128 -> reconstruct -> hgemm_recon -> had_r_128 of orcasaq2/ops.py:50-59 (and serves
  * 17..144 rows, which the reference sends to exl3_gemm).  Three launches on `stream`.
  * exl3_gemm_tc_status() returns a sticky device word that is non-zero only if a bounded wait
  * inside the kernel ran out (it synchronises the device; for diagnosis and tests).
  */
+size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc);
 int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
-                 void *xh_scratch, int rows, int ic, int oc, int k_times_2, int mcg, int mul1,
-                 int x_is_bf16, void *stream);
+                 void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
+                 int mul1, int x_is_bf16, void *stream);
 unsigned exl3_gemm_tc_status(void);
 
 /*

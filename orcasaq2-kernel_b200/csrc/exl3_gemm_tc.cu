@@ -8,11 +8,11 @@
 // output channels per CTA = the 128 TMEM lanes), tokens the N side (up to 512 per CTA = all 512
 // TMEM columns), so every decoded weight tile is used for up to 512 tokens.
 //
-// CTA = 10 warps, one CTA per SM:
-//   warp 0      producer: 1-D bulk copies of packed trellis rows and 2-D tiled TMA loads (128-byte
-//               swizzle) of the activation tiles, mbarrier completion
+// CTA = 19 warps, one CTA per SM:
+//   warp 0      producer of the packed trellis: 1-D bulk copies into a deep ring (mbarrier completion)
+//   warp 18     producer of the activation tiles: 2-D tiled TMA loads with 128-byte swizzle
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
-//   warps 2..9  decode: packed words -> 3INST codewords -> fp16 (the same rounding as
+//   warps 2..17 decode (two groups of eight, alternating stages): packed words -> 3INST codewords -> fp16 (the same rounding as
 //               reconstruct) -> swizzled K-major A tile in shared memory; afterwards the epilogue
 //               (tcgen05.ld of their TMEM lane quadrant, fp16 stores)
 // The K order inside each 16-channel tile is permuted (k' = 4*(ic&3) + (ic>>2)) so that the four
@@ -33,18 +33,16 @@
 namespace exl3 {
 namespace tc {
 
-constexpr int kThreads = 320;            // 10 warps
-constexpr int kDecodeWarps = 8;
+constexpr int kThreads = 608;            // 19 warps
+constexpr int kDecodeWarps = 8;          // per group; two groups take alternate stages
 constexpr int kBM = 128;                 // output channels per CTA
 constexpr int kBK = 64;                  // input channels per stage (one 128-byte swizzle row)
 constexpr int kBN = 256;                 // tokens per accumulator / per TMA box
 constexpr int kMaxHalves = 2;            // accumulators per CTA (512 tokens)
-constexpr int kStagesA = 3;
-constexpr int kStagesB = 2;
-constexpr int kStagesRaw = 4;
+constexpr int kStagesA = 4;
+constexpr int kMaxSlotsB = 16;            // ring of token-half tiles: 4 x 32 KB, more when the tiles are small
 constexpr int kABytes = kBM * kBK * 2;               // 16 KB
 constexpr int kBHalfBytes = kBN * kBK * 2;           // 32 KB
-constexpr int kBBytes = kBHalfBytes * kMaxHalves;    // 64 KB
 constexpr int kSpin = 1 << 26;
 constexpr unsigned long long kWaitNs = 1000000000ull;   // one second
 
@@ -124,17 +122,28 @@ struct Params {
     __half *y;             // [tokens][ldy]
     int tokens, ic, oc, ldy;
     int tiles_j;           // oc / 16
+    int box_rows;          // token rows of one TMA box (<= 256)
+    int b_slot_bytes;      // box_rows * 128, rounded up to 1024
+    int raw_stages;        // depth of the packed-trellis ring
+    int b_slots;           // depth of the activation-tile ring
+    int splitk;            // slices of the input dimension (grid.z)
+    float *partial;        // [splitk][tokens][oc] fp32 when splitk > 1
     uint32_t one;
 };
 
-struct __align__(1024) Smem {
-    unsigned char a[kStagesA][kABytes];
-    unsigned char b[kStagesB][kBBytes];
-    uint64_t raw_full[kStagesRaw], raw_empty[kStagesRaw];
+constexpr int kMaxRawStages = 32;
+struct Barriers {
+    uint64_t raw_full[kMaxRawStages], raw_empty[kMaxRawStages];
     uint64_t a_full[kStagesA], a_empty[kStagesA];
-    uint64_t b_full[kStagesB], b_empty[kStagesB];
+    uint64_t b_full[kMaxSlotsB], b_empty[kMaxSlotsB];
     uint64_t acc_full;
     uint32_t tmem_base;
+};
+// shared-memory plan: [A stages][B slots][barriers][raw trellis ring]
+struct SmemView {
+    unsigned char *a, *b;
+    Barriers *bar;
+    uint32_t *raw;
 };
 
 template <int K>
@@ -143,22 +152,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     extern __shared__ unsigned char smem_dyn[];
     // swizzled tiles need 1024-byte alignment; the launch reserves the slack
     unsigned char *smem_raw = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);
-    Smem &S = *reinterpret_cast<Smem *>(smem_raw);
     constexpr int kRawWords = 4 * 8 * 8 * K;                      // four tile rows of eight tiles
     constexpr uint32_t kRawRowBytes = 8 * 8 * K * 4;
-    uint32_t *raw = reinterpret_cast<uint32_t *>(smem_raw + sizeof(Smem));
+    unsigned char *const smA = smem_raw;
+    unsigned char *const smB = smem_raw + kStagesA * kABytes;
+    Barriers &S = *reinterpret_cast<Barriers *>(smB + (size_t)P.b_slots * P.b_slot_bytes);
+    uint32_t *raw = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(&S) + 1024);
+    const int kStagesRaw = P.raw_stages;
+    const int kSlotsB = P.b_slots;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ob = blockIdx.x;                                    // 128-column block of outputs
     const int tok0 = blockIdx.y * (kBN * kMaxHalves);
     const int tok_here = min(P.tokens - tok0, kBN * kMaxHalves);
     const int halves = tok_here > kBN ? 2 : 1;
-    const int nsteps = P.ic / kBK;
+    const int total_steps = P.ic / kBK;
+    const int step0 = (int)((long long)blockIdx.z * total_steps / P.splitk);
+    const int nsteps = (int)((long long)(blockIdx.z + 1) * total_steps / P.splitk) - step0;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kStagesRaw; ++s) { mbar_init(s32(&S.raw_full[s]), 1); mbar_init(s32(&S.raw_empty[s]), kDecodeWarps); }
         for (int s = 0; s < kStagesA; ++s) { mbar_init(s32(&S.a_full[s]), kDecodeWarps); mbar_init(s32(&S.a_empty[s]), 1); }
-        for (int s = 0; s < kStagesB; ++s) { mbar_init(s32(&S.b_full[s]), 1); mbar_init(s32(&S.b_empty[s]), 1); }
+        for (int s = 0; s < kSlotsB; ++s) { mbar_init(s32(&S.b_full[s]), 1); mbar_init(s32(&S.b_empty[s]), 1); }
         mbar_init(s32(&S.acc_full), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -173,24 +188,35 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     const uint32_t tmem = S.tmem_base;
 
     if (warp == 0) {
-        // ---------------- producer
+        // ---------------- producer of the packed trellis (runs ahead by the whole ring)
         if (lane == 0) {
             const uint32_t *src_row0 = P.trellis + (size_t)ob * 8 * (8 * K);
             const size_t row_words = (size_t)P.tiles_j * (8 * K);
             bool ok = true;
             for (int s = 0; s < nsteps && ok; ++s) {
-                const int rs = s % kStagesRaw, bs = s % kStagesB;
+                const int rs = s % kStagesRaw;
                 if (s >= kStagesRaw) ok = mbar_wait(s32(&S.raw_empty[rs]), ((s / kStagesRaw) - 1) & 1);
                 if (!ok) break;
                 mbar_expect_tx(s32(&S.raw_full[rs]), 4 * kRawRowBytes);
                 for (int r = 0; r < 4; ++r)
-                    bulk_g2s(s32(raw + rs * kRawWords + r * (kRawWords / 4)), src_row0 + (size_t)(4 * s + r) * row_words,
+                    bulk_g2s(s32(raw + rs * kRawWords + r * (kRawWords / 4)), src_row0 + (size_t)(4 * (step0 + s) + r) * row_words,
                              kRawRowBytes, s32(&S.raw_full[rs]));
-                if (s >= kStagesB) ok = mbar_wait(s32(&S.b_empty[bs]), ((s / kStagesB) - 1) & 1);
-                if (!ok) break;
-                mbar_expect_tx(s32(&S.b_full[bs]), (uint32_t)(halves * kBHalfBytes));
-                for (int h = 0; h < halves; ++h)
-                    tma_2d(s32(&S.b[bs][h * kBHalfBytes]), &xmap, s * kBK, tok0 + h * kBN, s32(&S.b_full[bs]));
+            }
+        }
+    } else if (warp == kThreads / 32 - 1) {
+        // ---------------- producer of the activation tiles
+        if (lane == 0) {
+            const uint32_t box_bytes = (uint32_t)P.box_rows * (kBK * 2);
+            int bi = 0;                                          // running index of token-half tiles
+            bool ok = true;
+            for (int s = 0; s < nsteps && ok; ++s) {
+                for (int h = 0; h < halves && ok; ++h, ++bi) {
+                    const int bs = bi % kSlotsB;
+                    if (bi >= kSlotsB) ok = mbar_wait(s32(&S.b_empty[bs]), ((bi / kSlotsB) - 1) & 1);
+                    if (!ok) break;
+                    mbar_expect_tx(s32(&S.b_full[bs]), box_bytes);
+                    tma_2d(s32(smB + (size_t)bs * P.b_slot_bytes), &xmap, (step0 + s) * kBK, tok0 + h * kBN, s32(&S.b_full[bs]));
+                }
             }
         }
     } else if (warp == 1) {
@@ -198,38 +224,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         if (lane == 0) {
             const int n_last = ((tok_here - (halves - 1) * kBN) + 15) & ~15;      // tokens in the last half, padded to 16
             bool ok = true;
+            int bi = 0;
             for (int s = 0; s < nsteps && ok; ++s) {
-                const int as = s % kStagesA, bs = s % kStagesB;
+                const int as = s % kStagesA;
                 ok = mbar_wait(s32(&S.a_full[as]), (s / kStagesA) & 1);
-                ok = ok && mbar_wait(s32(&S.b_full[bs]), (s / kStagesB) & 1);
-                if (!ok) break;
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a0 = s32(&S.a[as][0]);
+                const uint32_t a0 = s32(smA + as * kABytes);
+                for (int h = 0; h < halves && ok; ++h, ++bi) {
+                    const int bs = bi % kSlotsB;
+                    ok = mbar_wait(s32(&S.b_full[bs]), (bi / kSlotsB) & 1);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t b0 = s32(smB + (size_t)bs * P.b_slot_bytes);
+                    const uint32_t idesc = umma_idesc(h == halves - 1 ? n_last : kBN);
 #pragma unroll
-                for (int h = 0; h < kMaxHalves; ++h) {
-                    if (h < halves) {
-                        const uint32_t b0 = s32(&S.b[bs][h * kBHalfBytes]);
-                        const uint32_t idesc = umma_idesc(h == halves - 1 ? n_last : kBN);
-#pragma unroll
-                        for (int k = 0; k < kBK / 16; ++k)
-                            umma(tmem + h * kBN, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (s | k) ? 1u : 0u);
-                    }
+                    for (int k = 0; k < kBK / 16; ++k)
+                        umma(tmem + h * kBN, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (s | k) ? 1u : 0u);
+                    umma_commit(s32(&S.b_empty[bs]));   // arrives when the MMAs above have read smem
                 }
-                umma_commit(s32(&S.a_empty[as]));       // both arrive when the MMAs above have read smem
-                umma_commit(s32(&S.b_empty[bs]));
+                umma_commit(s32(&S.a_empty[as]));
             }
             umma_commit(s32(&S.acc_full));
         }
     } else {
         // ---------------- decode warps
-        const int dw = warp - 2;                   // 0..7
+        const int grp = (warp - 2) >> 3;           // stages s = grp, grp + 2, ...
+        const int dw = (warp - 2) & 7;             // 0..7 inside the group
         const int t_ic = dw >> 1;                  // which of the four 16-channel tiles of the stage
         const int half_oc = dw & 1;                // which four of the eight output tiles
         const int u = lane >> 3, c = lane & 7, p = c >> 2, q = c & 3;
         const DecodeConsts dc(P.one);
         const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
         bool ok = true;
-        for (int s = 0; s < nsteps && ok; ++s) {
+        for (int s = grp; s < nsteps && ok; s += 2) {
             const int rs = s % kStagesRaw, as = s % kStagesA;
             ok = mbar_wait(s32(&S.raw_full[rs]), (s / kStagesRaw) & 1);
             uint32_t wd[K + 1];
@@ -245,7 +271,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             decode_chunk_fast<K>(wd, z, dc);
             if (s >= kStagesA) ok = ok && mbar_wait(s32(&S.a_empty[as]), ((s / kStagesA) - 1) & 1);
             // weights of output channel (a, hm): input channels j = 2b + hk, adjacent in k'
-            unsigned char *abase = &S.a[as][0];
+            unsigned char *abase = smA + as * kABytes;
 #pragma unroll
             for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -276,10 +302,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
         const int oc_row = ob * kBM + 32 * quad + lane;
         // the two warps of a quadrant split the columns of every half
-        const int col_part = dw >> 2;
+        const int col_part = (warp - 2) >> 2;     // four warps share a lane quadrant
         for (int h = 0; h < halves; ++h) {
             const int ncols = min(kBN, tok_here - h * kBN);
-            for (int c0 = col_part * 32; c0 < ncols; c0 += 64) {
+            for (int c0 = col_part * 32; c0 < ncols; c0 += 128) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(h * kBN + c0);
                 asm volatile(
@@ -295,7 +321,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
 #pragma unroll
                     for (int j = 0; j < 32; ++j) {
                         const int tok = tok0 + h * kBN + c0 + j;
-                        if (c0 + j < ncols) P.y[(size_t)tok * P.ldy + oc_row] = __float2half_rn(__uint_as_float(v[j]));
+                        if (c0 + j < ncols) {
+                            if (P.splitk > 1)
+                                P.partial[((size_t)blockIdx.z * P.tokens + tok) * P.oc + oc_row] = __uint_as_float(v[j]);
+                            else
+                                P.y[(size_t)tok * P.ldy + oc_row] = __float2half_rn(__uint_as_float(v[j]));
+                        }
                     }
                 }
             }
@@ -345,6 +376,33 @@ xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __
     for (int j = 0; j < 4; ++j) dst[4 * j] = __float2half_rn(v[j] * kHadScale);
 }
 
+// Post-pass for split-K: sum the fp32 slices in order, H128, svh, fp16.
+__global__ void __launch_bounds__(256)
+reduce_had_kernel(const float *__restrict__ partial, int splitk, const __half *__restrict__ svh,
+                  __half *__restrict__ y, long long nblocks, int blocks_per_row, size_t slice_elems) {
+    const int lane = threadIdx.x & 31;
+    const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wid >= nblocks) return;
+    const int blk = (int)(wid % blocks_per_row);
+    const size_t off = (size_t)wid * 128 + 4 * lane;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < splitk; ++k) {
+        const float4 p = *reinterpret_cast<const float4 *>(partial + k * slice_elems + off);
+        v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __half2float(__float2half_rn(v[j]));   // same rounding point as the unsplit path
+    fwht128_warp(v, lane);
+    const uint2 sr = *reinterpret_cast<const uint2 *>(svh + blk * 128 + 4 * lane);
+    const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x), s23 = *reinterpret_cast<const __half2 *>(&sr.y);
+    const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * __low2float(s01), v[1] * kHadScale * __high2float(s01));
+    const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * __low2float(s23), v[3] * kHadScale * __high2float(s23));
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&o01);
+    o.y = *reinterpret_cast<const uint32_t *>(&o23);
+    *reinterpret_cast<uint2 *>(y + off) = o;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -364,13 +422,24 @@ static EncodeTiledFn encode_fn() {
 }
 
 template <int K>
-static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
-    const size_t smem = sizeof(Smem) + (size_t)kStagesRaw * (4 * 8 * 8 * K) * 4 + 1024;
+static int launch(const CUtensorMap &map, Params P, cudaStream_t st) {
+    const size_t raw_stage = (size_t)(4 * 8 * 8 * K) * 4;
+    P.b_slots = 4;
+    const size_t fixed = (size_t)kStagesA * kABytes + (size_t)P.b_slots * P.b_slot_bytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+    const size_t budget = 226 * 1024;
+    // keep ~64 KB of packed trellis in flight when the tiles leave room for it
+    size_t stages = (budget - fixed) / raw_stage;
+    const size_t want = (64 * 1024 + raw_stage - 1) / raw_stage;
+    if (stages > want) stages = want;
+    if (stages > (size_t)kMaxRawStages) stages = kMaxRawStages;
+    if (stages < 2) return EXL3_E_SHAPE;
+    P.raw_stages = (int)stages;
+    const size_t smem = fixed + stages * raw_stage;
     if (cudaFuncSetAttribute(gemm_tc_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
     }
-    dim3 grid(P.oc / kBM, (P.tokens + kBN * kMaxHalves - 1) / (kBN * kMaxHalves));
+    dim3 grid(P.oc / kBM, (P.tokens + kBN * kMaxHalves - 1) / (kBN * kMaxHalves), P.splitk);
     gemm_tc_kernel<K><<<grid, kThreads, smem, st>>>(map, P);
     return launch_status();
 }
@@ -387,19 +456,41 @@ extern "C" unsigned exl3_gemm_tc_status(void) {
     return v;
 }
 
+namespace exl3 { namespace tc {
+// slices of the input dimension: fill the 148 SMs when the output grid alone cannot
+static int choose_splitk(int rows, int ic, int oc) {
+    const int ctas = (oc / kBM) * ((rows + kBN * kMaxHalves - 1) / (kBN * kMaxHalves));
+    const int steps = ic / kBK;
+    int sk = 1;
+    if (ctas < 120) sk = (148 + ctas - 1) / ctas;
+    if (sk > steps / 8) sk = steps / 8;
+    return sk < 1 ? 1 : sk;
+}
+static size_t xh_bytes(int rows, int ic) { return (((size_t)rows * ic * 2) + 255) & ~(size_t)255; }
+} }
+
+extern "C" size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc) {
+    if (rows < 1 || ic <= 0 || oc <= 0) return 0;
+    const int sk = exl3::tc::choose_splitk(rows, ic, oc);
+    return exl3::tc::xh_bytes(rows, ic) + (sk > 1 ? (size_t)sk * rows * oc * 4 : 0);
+}
+
 extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
-                            void *xh_scratch, int rows, int ic, int oc, int k_times_2, int mcg, int mul1,
-                            int x_is_bf16, void *stream) {
+                            void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
+                            int mul1, int x_is_bf16, void *stream) {
     using namespace exl3;
     using namespace exl3::tc;
-    if (!x || !trellis || !y || !suh || !svh || !xh_scratch) return EXL3_E_NULL;
+    if (!x || !trellis || !y || !suh || !svh || !scratch) return EXL3_E_NULL;
+    void *xh_scratch = scratch;
     if (rows < 1 || ic <= 0 || oc <= 0 || (ic & 127) || (oc & 127) || oc / kBM > 65535) return EXL3_E_SHAPE;
     if (mcg || mul1) return EXL3_E_UNSUPPORTED;
     const int K = integer_k(k_times_2);
     if (!K) return EXL3_E_UNSUPPORTED;
-    if (!aligned(x, 8) || !aligned(y, 8) || !aligned(trellis, 16) || !aligned(xh_scratch, 16) || !aligned(suh, 8) ||
+    if (!aligned(x, 8) || !aligned(y, 8) || !aligned(trellis, 16) || !aligned(scratch, 256) || !aligned(suh, 8) ||
         !aligned(svh, 8))
         return EXL3_E_ALIGN;
+    if (scratch_bytes < exl3_gemm_tc_scratch_bytes(rows, ic, oc)) return EXL3_E_WORKSPACE;
+    const int splitk = choose_splitk(rows, ic, oc);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     EncodeTiledFn enc = encode_fn();
     if (!enc) return EXL3_E_LAUNCH;
@@ -417,7 +508,8 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
     const cuuint64_t gstr[1] = {(cuuint64_t)ic * 2};
-    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)kBN};
+    const int box_rows = rows >= kBN ? kBN : ((rows + 15) & ~15);
+    const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
     const cuuint32_t estr[2] = {1, 1};
     if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh_scratch, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
@@ -426,6 +518,10 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
     P.trellis = static_cast<const uint32_t *>(trellis);
     P.y = static_cast<__half *>(y);
     P.tokens = rows; P.ic = ic; P.oc = oc; P.ldy = oc; P.tiles_j = oc / 16; P.one = 1u;
+    P.splitk = splitk;
+    P.box_rows = box_rows;
+    P.b_slot_bytes = (box_rows * kBK * 2 + 1023) & ~1023;
+    P.partial = splitk > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic)) : nullptr;
     int rc;
     switch (K) {
         case 1: rc = launch<1>(map, P, st); break;
@@ -439,6 +535,10 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
     }
     if (rc != EXL3_OK) return rc;
 
-    // 3. output rotation and signs, in place
-    return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
+    // 3. output rotation and signs (in place), or the split-K reduction fused with them
+    if (splitk == 1) return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
+    const long long nb = (long long)rows * (oc / 128);
+    reduce_had_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(P.partial, splitk, static_cast<const __half *>(svh),
+                                                               static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc);
+    return launch_status();
 }

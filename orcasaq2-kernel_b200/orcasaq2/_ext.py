@@ -56,7 +56,9 @@ def lib():
                 ll = ctypes.c_longlong
                 L.exl3_int8_embed.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp]
                 L.exl3_int8_head.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ci, vp]
-                L.exl3_gemm_tc.argtypes = [vp, vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, ci, vp]
+                L.exl3_gemm_tc.argtypes = [vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ci, vp]
+                L.exl3_gemm_tc_scratch_bytes.restype = sz
+                L.exl3_gemm_tc_scratch_bytes.argtypes = [ci, ci, ci]
                 L.exl3_gemm_tc.restype = ci
                 L.exl3_gemm_tc_status.restype = ctypes.c_uint
                 L.exl3_gemv_static_capacity.restype = sz
@@ -306,9 +308,11 @@ def gemm_tc(x: torch.Tensor, trellis: torch.Tensor, y: torch.Tensor, suh: torch.
     rows = x.shape[0]
     if x.shape[1] != ic or tuple(y.shape) != (rows, oc) or suh.numel() != ic or svh.numel() != oc:
         raise RuntimeError("gemm_tc: shapes of x, y, suh, svh do not match the trellis")
-    xh = torch.empty((rows, ic), dtype=torch.float16, device=x.device)
-    _check(lib().exl3_gemm_tc(x.data_ptr(), trellis.data_ptr(), y.data_ptr(), suh.data_ptr(), svh.data_ptr(),
-                              xh.data_ptr(), rows, ic, oc, _k2(kk), int(bool(mcg)), int(bool(mul1)),
+    L = lib()
+    nbytes = L.exl3_gemm_tc_scratch_bytes(rows, ic, oc)
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x.device)     # freed on exit, like the reference's xh / w
+    _check(L.exl3_gemm_tc(x.data_ptr(), trellis.data_ptr(), y.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                              scratch.data_ptr(), nbytes, rows, ic, oc, _k2(kk), int(bool(mcg)), int(bool(mul1)),
                               int(x.dtype == torch.bfloat16), _stream(x)), "exl3_gemm_tc")
 
 

@@ -5,9 +5,13 @@ torch.compile and replays inside CUDA graphs (reference orcasaq2/ops.py:1-66).
 used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, written straight
 into the concatenated output.
 
-Row-count dispatch (reference ops.py:25,46): at or below GEMM_MAX_ROWS the fused decode kernel
-reads the packed trellis directly (in passes of 16 rows); above it the weight is rebuilt once
-into a scratch buffer and handed to a dense GEMM, bracketed by the two Hadamard passes.
+Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
+streaming of the packed trellis).  17 rows up to TC_MAX_ROWS: the tcgen05 kernel that decodes the
+trellis into shared-memory tiles inside the GEMM (one pass over the weights, no dense copy in
+memory).  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
+weight once into a scratch buffer, dense library GEMM, rotate back.  GEMM_MAX_ROWS keeps the
+reference's name and default; it is the bound up to which the packed trellis is read directly
+when the tcgen05 path is switched off (ORCA_EXL3_TC=0).
 """
 import os
 from typing import List
@@ -18,6 +22,8 @@ from torch import Tensor
 from . import _ext
 
 GEMM_MAX_ROWS = int(os.environ.get("ORCA_EXL3_GEMM_MAX_ROWS", "144"))
+USE_TC = os.environ.get("ORCA_EXL3_TC", "1") != "0"
+TC_MAX_ROWS = int(os.environ.get("ORCA_EXL3_TC_MAX_ROWS", "1023"))
 
 
 def exl3_K(trellis: Tensor):
@@ -52,8 +58,10 @@ def shard_gemm(x: Tensor, trellis: Tensor, suh: Tensor, svh: Tensor,
     y = torch.empty((rows, oc), dtype=torch.half, device=x.device)
     if rows == 0:
         return y
-    if rows <= GEMM_MAX_ROWS:
+    if rows <= _ext.GEMV_MAX_ROWS or (not USE_TC and rows <= GEMM_MAX_ROWS):
         _ext.exl3_gemm(x, trellis, y, suh, x, svh, -1, mcg, mul1, 0)
+    elif USE_TC and rows <= TC_MAX_ROWS:
+        _ext.gemm_tc(x, trellis, y, suh, svh, mcg, mul1)
     else:
         _dense_path(x, trellis, suh, svh, k, mcg, mul1, y)
     return y
@@ -75,7 +83,14 @@ def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Te
     if rows == 0:
         return y
     n = len(trellis)
-    if rows <= GEMM_MAX_ROWS:
+    if rows > _ext.GEMV_MAX_ROWS and USE_TC and rows <= TC_MAX_ROWS:
+        col = 0
+        for i in range(n):
+            yi = torch.empty((rows, ocs[i]), dtype=torch.half, device=x.device)
+            _ext.gemm_tc(x, trellis[i], yi, suh[i], svh[i], mcg[i], mul1[i])
+            y[:, col:col + ocs[i]] = yi
+            col += ocs[i]
+    elif rows <= GEMM_MAX_ROWS:
         shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i])
                   for i in range(n)]
         for g0 in range(0, n, _ext.MAX_SHARDS):
