@@ -1,0 +1,200 @@
+"""Decode benchmark of a random-init 27B-class decoder whose every projection is an EXL3 layer
+(BASELINE.json configs 4 and 5), on the kernels of this repository.
+
+    python bench_model.py --batch 1 --ctx 4096                       # 1 GPU
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29511 \
+        bench_model.py --batch 64 --ctx 8192                         # tensor parallel
+
+Model: 64 layers, hidden 5120, FFN 17408, 24 query / 4 KV heads of 256, vocabulary 151936; each
+projection (q, k, v, o, gate, up, down) gets a seeded bitrate from {2,..,6}; embed_tokens and the
+tied lm_head are one int8 table with per-row scales.  Weights are random (no checkpoint is
+involved); the KV cache is filled with random values for `ctx` tokens.  One step = one decoded
+token per sequence: RMSNorm, fused qkv GEMV, rotary, attention over the cache (library SDPA), o_proj,
+RMSNorm, fused gate_up GEMV, SiLU*up, down_proj, final norm, int8 head, argmax.  The whole step is
+captured in a CUDA graph.  Under tensor parallelism qkv / gate_up are column-sliced, o_proj /
+down_proj row-sliced with an NCCL all-reduce after each, the head is vocabulary-sliced.
+
+Prints one JSON line: tokens/s, ms per step, bytes moved per step (packed weights + KV cache) and
+their share of the measured HBM bandwidth.
+"""
+import argparse
+import json
+import os
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "orcasaq2-kernel_b200"))
+
+import torch  # noqa: E402
+import torch.distributed as dist  # noqa: E402
+import torch.nn.functional as F  # noqa: E402
+
+HIDDEN, FFN, LAYERS, QH, KVH, HD, VOCAB = 5120, 17408, 64, 24, 4, 256, 151936
+
+
+def rand_shard(ic, oc, K, dev, gen):
+    tr = torch.randint(-32768, 32768, (ic // 16, oc // 16, 16 * K), dtype=torch.int16, device=dev, generator=gen)
+    suh = (torch.randint(0, 2, (ic,), device=dev, generator=gen) * 2 - 1).half()
+    svh = (torch.randint(0, 2, (oc,), device=dev, generator=gen) * 2 - 1).half()
+    return dict(trellis=tr, suh=suh, svh=svh, mcg=False, mul1=False, K=K, ic=ic, oc=oc)
+
+
+class Linear:
+    """One (possibly fused) EXL3 layer on this rank: list of shards + preallocated output."""
+
+    def __init__(self, shards, rows, dev):
+        from orcasaq2 import _ext
+        self.ext, self.shards = _ext, shards
+        col = 0
+        for s in shards:
+            s["out_col"] = col
+            col += s["oc"]
+        self.out = torch.empty((rows, col), dtype=torch.half, device=dev)
+        self.rows = rows
+        self.bytes = sum(s["ic"] * s["oc"] * s["K"] // 8 for s in shards)
+
+    def __call__(self, x):
+        if self.rows <= self.ext.GEMV_MAX_ROWS:
+            self.ext.gemv_grouped(x, self.shards, self.out)
+        else:
+            for s in self.shards:                       # many rows: tcgen05 path, shard by shard
+                y = torch.empty((self.rows, s["oc"]), dtype=torch.half, device=x.device)
+                self.ext.gemm_tc(x, s["trellis"], y, s["suh"], s["svh"])
+                self.out[:, s["out_col"]:s["out_col"] + s["oc"]] = y
+        return self.out
+
+
+def rms(x, eps=1e-6):
+    v = x.float()
+    return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).half()
+
+
+def build(rank, world, batch, ctx, dev, layers):
+    kgen = torch.Generator().manual_seed(2026)                        # bitrates: same on every rank
+    wgen = torch.Generator(device=dev).manual_seed(1234 + rank)
+    qh, kvh = QH // world, max(1, KVH // world)
+    model, wbytes, kvbytes = [], 0, 0
+    for _ in range(layers):
+        ks = torch.randint(2, 7, (7,), generator=kgen).tolist()       # q k v o gate up down
+        qkv = Linear([rand_shard(HIDDEN, qh * HD, ks[0], dev, wgen), rand_shard(HIDDEN, kvh * HD, ks[1], dev, wgen),
+                      rand_shard(HIDDEN, kvh * HD, ks[2], dev, wgen)], batch, dev)
+        o = Linear([rand_shard(qh * HD, HIDDEN, ks[3], dev, wgen)], batch, dev)
+        gu = Linear([rand_shard(HIDDEN, FFN // world, ks[4], dev, wgen), rand_shard(HIDDEN, FFN // world, ks[5], dev, wgen)], batch, dev)
+        down = Linear([rand_shard(FFN // world, HIDDEN, ks[6], dev, wgen)], batch, dev)
+        kc = torch.randn((batch, kvh, ctx + 1, HD), device=dev, generator=wgen).half()
+        vc = torch.randn((batch, kvh, ctx + 1, HD), device=dev, generator=wgen).half()
+        model.append((qkv, o, gu, down, kc, vc))
+        wbytes += qkv.bytes + o.bytes + gu.bytes + down.bytes
+        kvbytes += 2 * batch * kvh * ctx * HD * 2
+    vslice = VOCAB // world
+    table = torch.randint(-127, 128, (vslice, HIDDEN), dtype=torch.int8, device=dev, generator=wgen)
+    scales = (torch.rand((vslice,), device=dev, generator=wgen) * 0.02 + 1e-3).half()
+    return model, table, scales, wbytes + vslice * HIDDEN, kvbytes, qh, kvh
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for a quick functional run")
+    ap.add_argument("--no-graph", action="store_true")
+    args = ap.parse_args()
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    from orcasaq2 import _ext
+    _ext.lib()
+    B, ctx = args.batch, args.ctx
+    model, table, scales, wbytes, kvbytes, qh, kvh = build(rank, world, B, ctx, dev, args.layers)
+    ids = torch.randint(0, table.shape[0], (B,), device=dev)
+    pos = torch.arange(HD // 2, device=dev).float()
+    ang = ctx / (10000.0 ** (pos / (HD // 2)))
+    cos, sin = torch.cos(ang).half(), torch.sin(ang).half()
+
+    def rope(t):                                    # [B, heads, HD]
+        a, b = t[..., : HD // 2], t[..., HD // 2:]
+        return torch.cat([a * cos - b * sin, a * sin + b * cos], -1)
+
+    def step():
+        h = _ext.int8_embed(table, scales, ids)                           # [B, HIDDEN] (rank-local rows)
+        if world > 1:
+            dist.all_reduce(h)                                            # vocabulary-parallel embedding
+        for qkv, o, gu, down, kc, vc in model:
+            y = qkv(rms(h))
+            q = rope(y[:, : qh * HD].reshape(B, qh, HD))
+            k = rope(y[:, qh * HD:(qh + kvh) * HD].reshape(B, kvh, HD))
+            v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
+            kc[:, :, ctx] = k
+            vc[:, :, ctx] = v
+            att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
+            a = o(att.reshape(B, qh * HD))
+            if world > 1:
+                dist.all_reduce(a)
+            h = h + a
+            g = gu(rms(h))
+            half = g.shape[1] // 2
+            d = down(F.silu(g[:, :half]) * g[:, half:])
+            if world > 1:
+                dist.all_reduce(d)
+            h = h + d
+        logits = _ext.int8_head(table, scales, rms(h))                    # vocabulary slice of this rank
+        return logits.argmax(-1)
+
+    for _ in range(max(2, args.warmup)):
+        out = step()
+    torch.cuda.synchronize()
+    graph = None
+    if not args.no_graph:
+        s = torch.cuda.Stream()
+        s.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(s):
+            step()                                   # warm the side stream's workspace before capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=s):
+                out = step()
+        torch.cuda.current_stream().wait_stream(s)
+        torch.cuda.synchronize()
+    run = graph.replay if graph is not None else step
+    for _ in range(3):
+        run()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        run()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    if rank == 0:
+        peak = 6549.8
+        try:
+            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+        except Exception:                                                 # noqa: BLE001
+            pass
+        per_gpu = (wbytes + kvbytes) / (ms * 1e-3) / 1e9
+        print(json.dumps({
+            "metric": "27B EXL3 decode tokens/s", "value": round(B / (ms * 1e-3), 2), "unit": "tok/s",
+            "ms_per_step": round(ms, 4), "n_gpus": world, "batch": B, "ctx": ctx, "layers": args.layers,
+            "cuda_graph": graph is not None, "status_word": _ext.workspace_status(dev),
+            "per_gpu_bytes_per_step": {"packed_weights": wbytes, "kv_cache": kvbytes},
+            "per_gpu_hbm_gbs": round(per_gpu, 1), "frac_of_measured_hbm": round(per_gpu / peak, 4),
+            "data": "synthetic (random-init weights, random KV cache)", "attention": "torch SDPA (library)",
+        }), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
