@@ -199,18 +199,17 @@ def run_gpu(args):
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    if ms < 300:                                            # keep sampling long enough to see clocks
-        t_end = time.time() + 0.4
-        j = 0
-        while time.time() < t_end:
-            step(j)
-            j += 1
-        torch.cuda.synchronize()
-    clocks = sampler.stop()
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    if ms < 400:
+        # keep the GPU under the same load long enough for the 100 ms clock sampler to see it; the
+        # repeat count comes from the rank-agreed time so every rank issues the same collectives
+        for j in range(int(400.0 / max(ms / args.steps, 1e-3))):
+            step(j)
+        torch.cuda.synchronize()
+    clocks = sampler.stop()
     ms_step = ms / args.steps
     value = full_bytes / (ms_step * 1e-3) / 1e9
 

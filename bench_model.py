@@ -193,7 +193,11 @@ def main():
             "data": "synthetic (random-init weights, random KV cache)", "attention": "torch SDPA (library)",
         }), flush=True)
     if world > 1:
-        dist.destroy_process_group()
+        # leave without tearing down NCCL under a live captured graph (that teardown can block)
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":

@@ -33,6 +33,7 @@ constexpr int kThreads = kWarps * 32;
 // B200, deeper rings LOSE bandwidth again (1 KB pieces: 7.2 TB/s at depth 4, 3.0 TB/s at depth 8).
 __host__ __device__ constexpr int ring_depth(int K) { return K <= 4 ? 4 : 3; }
 constexpr int kTargetCtas = 296;       // two resident CTAs on each of 148 SMs
+constexpr int kMaxSplitK = 16;         // more slices cost more in the final reduction than they gain
 constexpr int kXfMaxBytes = 48 * 1024; // activation fragments
 constexpr int kBarBytes = 1024;
 constexpr int kSpinLimit = 1 << 22;
@@ -50,6 +51,7 @@ struct GemvShardDev {
     const __half *suh;
     const __half *svh;
     long long partial_off;  // in floats
+    long long xf_off;       // in 32-bit words, into the fragment scratch
     int tiles_j;            // oc / 16
     int K;
     int out_col;
@@ -62,6 +64,7 @@ struct GemvParams {
     const __half *x;
     __half *y;
     float *partial;
+    uint32_t *xfg;          // rotated activations in B-fragment order, per shard
     unsigned *tickets;
     unsigned *status;
     int rows, ic, ldy, kblocks;
@@ -164,13 +167,16 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     const uint32_t bar0 = smem_u32(bars + warp * 8);
     const uint32_t ring0 = smem_u32(ring);
 
+    const uint32_t xbar = smem_u32(bars + kWarps * 8);      // CTA-wide: activation fragments landed
+    uint32_t xphase = 0;
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < kDepth; ++s) mbar_init(bar0 + 8 * s, 1);
+        if (warp == 0) mbar_init(xbar, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
-    __syncwarp();
+    __syncthreads();
 
     // warp w owns tile rows kb0*8 + w + 8*s of the 128-column block ob
     const uint32_t *src0 = S.trellis + ((size_t)(kb0 * 8 + warp) * S.tiles_j + (size_t)ob * 8) * (size_t)(8 * K);
@@ -212,35 +218,14 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     for (int b0 = 0; b0 < nblk; b0 += sub_max) {
         const int nb_sub = min(sub_max, nblk - b0);
         if (b0) __syncthreads();                     // the previous fragments are no longer read
-        // ---- H128(x * suh) for these blocks, in B-fragment order, both halves equal
-        for (int task = warp; task < nrow * nb_sub; task += kWarps) {
-            const int blk = task / nrow, n = task - blk * nrow;
-            float v[4] = {0.f, 0.f, 0.f, 0.f};
-            if (n < P.rows) {
-                const int col = (kb0 + b0 + blk) * 128 + 4 * lane;
-                const uint2 xr = *reinterpret_cast<const uint2 *>(P.x + (size_t)n * P.ic + col);
-                const uint2 sr = __ldg(reinterpret_cast<const uint2 *>(S.suh + col));
-                const __half2 x01 = *reinterpret_cast<const __half2 *>(&xr.x);
-                const __half2 x23 = *reinterpret_cast<const __half2 *>(&xr.y);
-                const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x);
-                const __half2 s23 = *reinterpret_cast<const __half2 *>(&sr.y);
-                v[0] = __low2float(x01) * __low2float(s01);
-                v[1] = __high2float(x01) * __high2float(s01);
-                v[2] = __low2float(x23) * __low2float(s23);
-                v[3] = __high2float(x23) * __high2float(s23);
-                fwht128_warp(v, lane);
-            }
-            const int tile_local = blk * 8 + (lane >> 2);
-            const int t = (NT == 2) ? (n >> 3) : 0;
-            const int nn = (NT == 2) ? (n & 7) : n;
-            uint32_t *dst = xf + (size_t)tile_local * xf_tile_words + ((t * NB + nn) * 4) * 4 + (lane & 3);
-#pragma unroll
-            for (int k = 0; k < 4; ++k) {
-                const __half2 d = __float2half2_rn(v[k] * kHadScale);
-                dst[k * 4] = *reinterpret_cast<const uint32_t *>(&d);
-            }
+        // ---- rotated activations of these blocks: one bulk copy from the fragment scratch
+        if (tid == 0) {
+            const uint32_t bytes = (uint32_t)nb_sub * 8u * (uint32_t)xf_tile_words * 4u;
+            mbar_expect_tx(xbar, bytes);
+            bulk_g2s(smem_u32(xf), P.xfg + S.xf_off + (size_t)(kb0 + b0) * 8 * xf_tile_words, bytes, xbar);
         }
-        __syncthreads();
+        ok = mbar_wait(xbar, xphase, P.status) && ok;
+        xphase ^= 1u;
 
         // ---- stream, decode, multiply
         const uint32_t *xfp = xf_lane;
@@ -330,8 +315,17 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         if (!s_last) return;
         __threadfence();
         for (int n = tid >> 7; n < P.rows; n += 2) {
+            // fixed summation order (slice 0, 1, 2, ...) with the loads issued four at a time
             float v = 0.f;
-            for (int k2 = 0; k2 < S.splitk; ++k2) v += __ldcg(part + ((size_t)k2 * P.rows + n) * 128 + ocl);
+            int k2 = 0;
+            for (; k2 + 4 <= S.splitk; k2 += 4) {
+                const float p0 = __ldcg(part + ((size_t)(k2 + 0) * P.rows + n) * 128 + ocl);
+                const float p1 = __ldcg(part + ((size_t)(k2 + 1) * P.rows + n) * 128 + ocl);
+                const float p2 = __ldcg(part + ((size_t)(k2 + 2) * P.rows + n) * 128 + ocl);
+                const float p3 = __ldcg(part + ((size_t)(k2 + 3) * P.rows + n) * 128 + ocl);
+                v = (((v + p0) + p1) + p2) + p3;
+            }
+            for (; k2 < S.splitk; ++k2) v += __ldcg(part + ((size_t)k2 * P.rows + n) * 128 + ocl);
             fin[n * 128 + ocl] = v;
         }
     }
@@ -354,6 +348,45 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         o.x = *reinterpret_cast<const uint32_t *>(&o01);
         o.y = *reinterpret_cast<const uint32_t *>(&o23);
         *reinterpret_cast<uint2 *>(P.y + (size_t)n * P.ldy + ocol) = o;
+    }
+}
+
+// Pre-pass: H128(x * suh) of every shard, rounded to fp16 once, written in the order the GEMV's
+// mma B fragments read it (per 16-channel tile: [row group][row][q][4 slots], both halves of a
+// word equal).  One warp per (shard, row, 128-block).
+__global__ void __launch_bounds__(256) xfrag_kernel(const __grid_constant__ GemvParams P, int nt) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");          // x may come from the previous kernel
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int lane = threadIdx.x & 31;
+    const int nrow = nt * P.nb;
+    const int per_shard = nrow * P.kblocks;
+    const int task = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (task >= per_shard * P.nshards) return;
+    const int sh = task / per_shard, r = task - sh * per_shard;
+    const int blk = r / nrow, n = r - blk * nrow;
+    const GemvShardDev &S = P.sh[sh];
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    if (n < P.rows) {
+        const int col = blk * 128 + 4 * lane;
+        const uint2 xr = *reinterpret_cast<const uint2 *>(P.x + (size_t)n * P.ic + col);
+        const uint2 sr = __ldg(reinterpret_cast<const uint2 *>(S.suh + col));
+        const __half2 x01 = *reinterpret_cast<const __half2 *>(&xr.x), x23 = *reinterpret_cast<const __half2 *>(&xr.y);
+        const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x), s23 = *reinterpret_cast<const __half2 *>(&sr.y);
+        v[0] = __low2float(x01) * __low2float(s01);
+        v[1] = __high2float(x01) * __high2float(s01);
+        v[2] = __low2float(x23) * __low2float(s23);
+        v[3] = __high2float(x23) * __high2float(s23);
+        fwht128_warp(v, lane);
+    }
+    const int xf_tile_words = nrow * 16;
+    const int tile = blk * 8 + (lane >> 2);
+    const int t = (nt == 2) ? (n >> 3) : 0;
+    const int nn = (nt == 2) ? (n & 7) : n;
+    uint32_t *dst = P.xfg + S.xf_off + (size_t)tile * xf_tile_words + ((t * P.nb + nn) * 4) * 4 + (lane & 3);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const __half2 d = __float2half2_rn(v[k] * kHadScale);
+        dst[k * 4] = *reinterpret_cast<const uint32_t *>(&d);
     }
 }
 
@@ -381,6 +414,8 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const __grid_constant
 struct GemvPlan {
     int nt, nb, xf_bytes, xf_blocks, region_bytes, total_ctas, total_units, kblocks;
     long long partial_floats;
+    long long xf_words;
+    long long xf_off[EXL3_MAX_SHARDS];
     int splitk[EXL3_MAX_SHARDS], cta_begin[EXL3_MAX_SHARDS], unit_begin[EXL3_MAX_SHARDS], K[EXL3_MAX_SHARDS];
     long long partial_off[EXL3_MAX_SHARDS];
 };
@@ -413,6 +448,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         int sk = (int)(kTargetCtas * share / ocb + 0.5);
         if (sk < 1) sk = 1;
         if (sk > pl.kblocks) sk = pl.kblocks;
+        if (sk > kMaxSplitK) sk = kMaxSplitK;
         pl.splitk[i] = sk;
         pl.cta_begin[i] = ctas;
         pl.unit_begin[i] = units;
@@ -429,6 +465,11 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     pl.total_ctas = ctas;
     pl.total_units = units;
     pl.partial_floats = pf;
+    pl.xf_words = 0;
+    for (int i = 0; i < n; ++i) {
+        pl.xf_off[i] = pl.xf_words;
+        pl.xf_words += (long long)pl.kblocks * frag_bytes_per_block / 4;
+    }
     pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
     pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
     const int red = (kWarps + 1) * pl.nt * 8 * 128 * 4;
@@ -437,7 +478,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
 }
 
 static size_t plan_workspace_bytes(const GemvPlan &pl) {
-    return kWsHeadBytes + (size_t)pl.partial_floats * 4;
+    return kWsHeadBytes + (((size_t)pl.partial_floats * 4 + 255) & ~(size_t)255) + (size_t)pl.xf_words * 4;
 }
 
 }  // namespace exl3
@@ -468,6 +509,7 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
     P.status = reinterpret_cast<unsigned *>(ws);
     P.tickets = reinterpret_cast<unsigned *>(ws + kWsStatusBytes);
     P.partial = reinterpret_cast<float *>(ws + kWsHeadBytes);
+    P.xfg = reinterpret_cast<uint32_t *>(ws + kWsHeadBytes + (((size_t)pl.partial_floats * 4 + 255) & ~(size_t)255));
     P.rows = rows;
     P.ic = ic;
     P.ldy = ldy;
@@ -483,6 +525,7 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
         d.suh = static_cast<const __half *>(shards[i].suh);
         d.svh = static_cast<const __half *>(shards[i].svh);
         d.partial_off = pl.partial_off[i];
+        d.xf_off = pl.xf_off[i];
         d.tiles_j = shards[i].oc / 16;
         d.K = pl.K[i];
         d.out_col = shards[i].out_col;
@@ -505,6 +548,15 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     cudaError_t e;
+    {
+        const int tasks = pl.nt * pl.nb * pl.kblocks * nshards;
+        cudaLaunchConfig_t pc = cfg;
+        pc.gridDim = dim3((unsigned)((tasks + 7) / 8));
+        pc.blockDim = dim3(256);
+        pc.dynamicSmemBytes = 0;
+        e = cudaLaunchKernelEx(&pc, xfrag_kernel, P, pl.nt);
+        if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    }
     if (pl.nt == 1) {
         e = cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }

@@ -133,7 +133,7 @@ int8_head_kernel(const int8_t *__restrict__ q, const T *__restrict__ s, const T 
 #pragma unroll
             for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
 
-#pragma unroll 2
+#pragma unroll 4
         for (int h0 = 0; h0 < hidden; h0 += 64) {
             const uint4 wa = __ldg(reinterpret_cast<const uint4 *>(ra + h0));
             const uint4 wb = __ldg(reinterpret_cast<const uint4 *>(rb + h0));
