@@ -54,15 +54,24 @@ class Linear:
         self.rows = rows
         self.bytes = sum(s["ic"] * s["oc"] * s["K"] // 8 for s in shards)
 
-    def __call__(self, x):
+    def __call__(self, x, in_mode=0, residual=None, out=None):
+        """in_mode: 0 plain, 1 RMSNorm(x), 2 silu(x[:, :ic]) * x[:, ic:]; `residual` is added to the
+        result (both fused into the GEMV for <= 16 rows, separate torch ops above that)."""
         if self.rows <= self.ext.GEMV_MAX_ROWS:
-            self.ext.gemv_grouped(x, self.shards, self.out)
-        else:
+            out = self.out if out is None else out
+            self.ext.gemv_grouped(x, self.shards, out, in_mode=in_mode, residual=residual)
+            return out
+        if in_mode == 1:
+            x = rms(x)
+        elif in_mode == 2:
+            half = x.shape[1] // 2
+            x = F.silu(x[:, :half]) * x[:, half:]
+        if True:
             for s in self.shards:                       # many rows: tcgen05 path, shard by shard
                 y = torch.empty((self.rows, s["oc"]), dtype=torch.half, device=x.device)
                 self.ext.gemm_tc(x, s["trellis"], y, s["suh"], s["svh"])
                 self.out[:, s["out_col"]:s["out_col"] + s["oc"]] = y
-        return self.out
+        return self.out if residual is None else residual + self.out
 
 
 def rms(x, eps=1e-6):
@@ -125,23 +134,26 @@ def main():
         if world > 1:
             dist.all_reduce(h)                                            # vocabulary-parallel embedding
         for qkv, o, gu, down, kc, vc in model:
-            y = qkv(rms(h))
+            y = qkv(h, in_mode=1)
             q = rope(y[:, : qh * HD].reshape(B, qh, HD))
             k = rope(y[:, qh * HD:(qh + kvh) * HD].reshape(B, kvh, HD))
             v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
             kc[:, :, ctx] = k
             vc[:, :, ctx] = v
             att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
-            a = o(att.reshape(B, qh * HD))
             if world > 1:
+                a = o(att.reshape(B, qh * HD))
                 dist.all_reduce(a)
-            h = h + a
-            g = gu(rms(h))
-            half = g.shape[1] // 2
-            d = down(F.silu(g[:, :half]) * g[:, half:])
+                h = h + a
+            else:
+                h = o(att.reshape(B, qh * HD), residual=h)           # residual add in the epilogue
+            g = gu(h, in_mode=1)
             if world > 1:
+                d = down(g, in_mode=2)
                 dist.all_reduce(d)
-            h = h + d
+                h = h + d
+            else:
+                h = down(g, in_mode=2, residual=h)
         logits = _ext.int8_head(table, scales, rms(h))                    # vocabulary slice of this rank
         return logits.argmax(-1)
 

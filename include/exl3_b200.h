@@ -93,6 +93,30 @@ size_t exl3_gemv_workspace_bytes(const exl3_shard *shards, int nshards, int rows
 int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
                       int ic, int ldy, void *workspace, size_t workspace_bytes, void *stream);
 
+/*
+ * exl3_gemv_grouped with the elementwise neighbours of the layer folded in (no counterpart in the
+ * reference plugin, which leaves these to the serving engine): the input transform runs inside the
+ * activation pre-pass, the residual add inside the output epilogue.
+ *   in_mode 0  x is used as it is ([rows][ldx], ldx >= ic)
+ *   in_mode 1  RMSNorm first: x * rsqrt(mean(x^2) + eps) * norm_weight (norm_weight fp16 [ic] or NULL
+ *              for all ones), rounded to fp16 as a stand-alone norm would
+ *   in_mode 2  gated activation first: silu(x[:, 0:ic]) * x[:, ic:2ic]  (x is [rows][ldx], ldx >= 2*ic)
+ *   residual   optional fp16 [rows][ld_residual] added to every output before its single rounding;
+ *              may alias y (in-place residual update)
+ * ldx / ld_residual: 0 selects the natural value.  fusion == NULL is exl3_gemv_grouped.
+ */
+typedef struct exl3_gemv_fusion {
+    int in_mode;
+    const void *norm_weight;
+    float eps;
+    int ldx;
+    const void *residual;
+    int ld_residual;
+} exl3_gemv_fusion;
+int exl3_gemv_grouped_ex(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                         int ic, int ldy, void *workspace, size_t workspace_bytes,
+                         const exl3_gemv_fusion *fusion, void *stream);
+
 /* Single-shard convenience form of exl3_gemv_grouped (y is [rows][oc]). */
 int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
               int rows, int ic, int oc, int k_times_2, int mcg, int mul1, void *workspace,

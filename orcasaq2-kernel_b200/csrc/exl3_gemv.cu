@@ -63,6 +63,11 @@ struct GemvShardDev {
 struct GemvParams {
     const __half *x;
     __half *y;
+    const __half *residual;   // optional [rows][ld_res], added to the result before the final rounding
+    const __half *norm_w;     // RMSNorm weight [ic] (in_mode 1), may be null for all ones
+    float eps;
+    int in_mode;              // 0 plain, 1 RMSNorm of x, 2 silu(x[:, :ic]) * x[:, ic:]
+    int ldx, ld_res;
     float *partial;
     uint32_t *xfg;          // rotated activations in B-fragment order, per shard
     unsigned *tickets;
@@ -340,10 +345,16 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         const float4 f = *reinterpret_cast<const float4 *>(fin + n * 128 + 4 * lane);
         float v[4] = {f.x, f.y, f.z, f.w};
         fwht128_warp(v, lane);
-        const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * __low2float(sv01),
-                                              v[1] * kHadScale * __high2float(sv01));
-        const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * __low2float(sv23),
-                                              v[3] * kHadScale * __high2float(sv23));
+        float r[4] = {0.f, 0.f, 0.f, 0.f};
+        if (P.residual) {
+            const uint2 rr = *reinterpret_cast<const uint2 *>(P.residual + (size_t)n * P.ld_res + ocol);
+            const __half2 r01 = *reinterpret_cast<const __half2 *>(&rr.x), r23 = *reinterpret_cast<const __half2 *>(&rr.y);
+            r[0] = __low2float(r01); r[1] = __high2float(r01); r[2] = __low2float(r23); r[3] = __high2float(r23);
+        }
+        const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * __low2float(sv01) + r[0],
+                                              v[1] * kHadScale * __high2float(sv01) + r[1]);
+        const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * __low2float(sv23) + r[2],
+                                              v[3] * kHadScale * __high2float(sv23) + r[3]);
         uint2 o;
         o.x = *reinterpret_cast<const uint32_t *>(&o01);
         o.y = *reinterpret_cast<const uint32_t *>(&o23);
@@ -368,14 +379,43 @@ __global__ void __launch_bounds__(256) xfrag_kernel(const __grid_constant__ Gemv
     float v[4] = {0.f, 0.f, 0.f, 0.f};
     if (n < P.rows) {
         const int col = blk * 128 + 4 * lane;
-        const uint2 xr = *reinterpret_cast<const uint2 *>(P.x + (size_t)n * P.ic + col);
+        const __half *xrow = P.x + (size_t)n * P.ldx;
+        const uint2 xr = *reinterpret_cast<const uint2 *>(xrow + col);
         const uint2 sr = __ldg(reinterpret_cast<const uint2 *>(S.suh + col));
         const __half2 x01 = *reinterpret_cast<const __half2 *>(&xr.x), x23 = *reinterpret_cast<const __half2 *>(&xr.y);
         const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x), s23 = *reinterpret_cast<const __half2 *>(&sr.y);
-        v[0] = __low2float(x01) * __low2float(s01);
-        v[1] = __high2float(x01) * __high2float(s01);
-        v[2] = __low2float(x23) * __low2float(s23);
-        v[3] = __high2float(x23) * __high2float(s23);
+        v[0] = __low2float(x01); v[1] = __high2float(x01); v[2] = __low2float(x23); v[3] = __high2float(x23);
+        if (P.in_mode == 1) {
+            // RMSNorm folded in: every warp reduces the whole row (it is short and sits in L2)
+            float ss = 0.f;
+            for (int c = 8 * lane; c < P.ic; c += 256) {
+                const uint4 q4 = *reinterpret_cast<const uint4 *>(xrow + c);
+                const __half2 *h2 = reinterpret_cast<const __half2 *>(&q4);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 f = __half22float2(h2[j]);
+                    ss += f.x * f.x + f.y * f.y;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float rn = rsqrtf(ss / (float)P.ic + P.eps);
+            float g[4] = {1.f, 1.f, 1.f, 1.f};
+            if (P.norm_w) {
+                const uint2 gr = __ldg(reinterpret_cast<const uint2 *>(P.norm_w + col));
+                const __half2 g01 = *reinterpret_cast<const __half2 *>(&gr.x), g23 = *reinterpret_cast<const __half2 *>(&gr.y);
+                g[0] = __low2float(g01); g[1] = __high2float(g01); g[2] = __low2float(g23); g[3] = __high2float(g23);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __half2float(__float2half_rn(v[j] * rn * g[j]));   // the norm's own fp16 output
+        } else if (P.in_mode == 2) {
+            const uint2 ur = *reinterpret_cast<const uint2 *>(xrow + P.ic + col);
+            const __half2 u01 = *reinterpret_cast<const __half2 *>(&ur.x), u23 = *reinterpret_cast<const __half2 *>(&ur.y);
+            const float u[4] = {__low2float(u01), __high2float(u01), __low2float(u23), __high2float(u23)};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = __half2float(__float2half_rn(v[j] / (1.f + __expf(-v[j])) * u[j]));
+        }
+        v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
         fwht128_warp(v, lane);
     }
     const int xf_tile_words = nrow * 16;
@@ -489,8 +529,9 @@ extern "C" size_t exl3_gemv_workspace_bytes(const exl3_shard *shards, int nshard
     return exl3::plan_workspace_bytes(pl);
 }
 
-extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
-                                 int ic, int ldy, void *workspace, size_t workspace_bytes, void *stream) {
+extern "C" int exl3_gemv_grouped_ex(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                                    int ic, int ldy, void *workspace, size_t workspace_bytes,
+                                    const exl3_gemv_fusion *fusion, void *stream) {
     using namespace exl3;
     GemvPlan pl;
     const int rc = make_plan(shards, nshards, rows, ic, pl);
@@ -513,6 +554,19 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
     P.rows = rows;
     P.ic = ic;
     P.ldy = ldy;
+    P.residual = nullptr; P.norm_w = nullptr; P.eps = 0.f; P.in_mode = 0; P.ldx = ic; P.ld_res = ldy;
+    if (fusion) {
+        if (fusion->in_mode < 0 || fusion->in_mode > 2) return EXL3_E_UNSUPPORTED;
+        P.in_mode = fusion->in_mode;
+        P.norm_w = static_cast<const __half *>(fusion->norm_weight);
+        P.eps = fusion->eps;
+        P.ldx = fusion->ldx > 0 ? fusion->ldx : (fusion->in_mode == 2 ? 2 * ic : ic);
+        P.residual = static_cast<const __half *>(fusion->residual);
+        P.ld_res = fusion->ld_residual > 0 ? fusion->ld_residual : ldy;
+        if ((P.ldx & 7) || (P.ld_res & 3) || (P.norm_w && !aligned(P.norm_w, 8)) || (P.residual && !aligned(P.residual, 8)) || !aligned(x, 16))
+            return EXL3_E_ALIGN;
+        if (P.ldx < (P.in_mode == 2 ? 2 * ic : ic)) return EXL3_E_SHAPE;
+    }
     P.kblocks = pl.kblocks;
     P.nb = pl.nb;
     P.xf_bytes = pl.xf_bytes;
@@ -568,6 +622,11 @@ extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const vo
     }
     if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     return launch_status();
+}
+
+extern "C" int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
+                                 int ic, int ldy, void *workspace, size_t workspace_bytes, void *stream) {
+    return exl3_gemv_grouped_ex(shards, nshards, x, y, rows, ic, ldy, workspace, workspace_bytes, nullptr, stream);
 }
 
 extern "C" int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, const void *svh,

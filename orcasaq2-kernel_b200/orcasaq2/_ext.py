@@ -28,6 +28,14 @@ class Exl3Shard(ctypes.Structure):
                 ("mul1", ctypes.c_int), ("out_col", ctypes.c_int)]
 
 
+class Exl3GemvFusion(ctypes.Structure):
+    _fields_ = [("in_mode", ctypes.c_int), ("norm_weight", ctypes.c_void_p), ("eps", ctypes.c_float),
+                ("ldx", ctypes.c_int), ("residual", ctypes.c_void_p), ("ld_residual", ctypes.c_int)]
+
+
+IN_PLAIN, IN_RMSNORM, IN_SILU_MUL = 0, 1, 2
+
+
 def library_path() -> str:
     return _LIB_PATH
 
@@ -53,6 +61,9 @@ def lib():
                 L.exl3_gemv_workspace_bytes.argtypes = [ctypes.POINTER(Exl3Shard), ci, ci, ci]
                 L.exl3_gemv_grouped.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp, sz, vp]
                 L.exl3_gemv.argtypes = [vp, vp, vp, vp, vp, ci, ci, ci, ci, ci, ci, vp, sz, vp]
+                L.exl3_gemv_grouped_ex.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp, sz,
+                                                   ctypes.POINTER(Exl3GemvFusion), vp]
+                L.exl3_gemv_grouped_ex.restype = ci
                 ll = ctypes.c_longlong
                 L.exl3_int8_embed.argtypes = [vp, vp, vp, vp, ci, ci, ci, ci, ci, vp, vp]
                 L.exl3_int8_head.argtypes = [vp, vp, vp, vp, ci, ci, ci, ll, ci, vp]
@@ -163,38 +174,39 @@ def had_r_128(inp: torch.Tensor, out: torch.Tensor, pre_scale, post_scale, scale
                                 float(scale), rows, n, _stream(inp)), "exl3_had_r_128")
 
 
-def gemv_grouped(x: torch.Tensor, shards, y: torch.Tensor) -> None:
-    """y[:, cols of shard s] <- H(H(x*suh_s) W_s) * svh_s for every shard, one launch.
-    `shards` is a sequence of dicts with trellis, suh, svh, mcg, mul1 and (optionally)
-    out_col; columns default to the running sum of the shard widths."""
+def gemv_grouped(x: torch.Tensor, shards, y: torch.Tensor, in_mode: int = IN_PLAIN, norm_weight=None,
+                 eps: float = 1e-6, residual=None) -> None:
+    """y[:, cols of shard s] <- H(H(f(x)*suh_s) W_s) * svh_s (+ residual) for every shard, one launch.
+    `shards` is a sequence of dicts with trellis, suh, svh, mcg, mul1 and (optionally) out_col;
+    columns default to the running sum of the shard widths.  f is the identity, an RMSNorm
+    (in_mode=IN_RMSNORM, optional norm_weight) or silu(x[:, :ic]) * x[:, ic:] (IN_SILU_MUL, x has
+    2*ic columns); `residual` ([rows, y.shape[1]] fp16, may be y itself) is added in the epilogue."""
     _cuda(x, "x", torch.float16)
     _cuda(y, "y", torch.float16)
-    rows, ic = x.shape
-    arr = (Exl3Shard * len(shards))()
-    col = 0
-    for i, s in enumerate(shards):
-        tr = _cuda(s["trellis"], "trellis")
-        tic, toc, kk = _trellis_dims(tr)
-        if tic != ic:
-            raise RuntimeError(f"shard {i}: trellis has {tic} input channels, x has {ic}")
-        _cuda(s["suh"], "suh", torch.float16)
-        _cuda(s["svh"], "svh", torch.float16)
-        if s["suh"].numel() != ic or s["svh"].numel() != toc:
-            raise RuntimeError(f"shard {i}: suh/svh sizes do not match the trellis")
-        oc_col = s.get("out_col", col)
-        arr[i] = Exl3Shard(tr.data_ptr(), s["suh"].data_ptr(), s["svh"].data_ptr(), toc, _k2(kk),
-                           int(bool(s.get("mcg"))), int(bool(s.get("mul1"))), oc_col)
-        col = oc_col + toc
+    rows = x.shape[0]
+    ic = x.shape[1] // 2 if in_mode == IN_SILU_MUL else x.shape[1]
+    arr = _shard_array(x, shards, ic)
     L = lib()
     need = L.exl3_gemv_workspace_bytes(arr, len(shards), rows, ic)
     ws = gemv_workspace(x.device, need) if need else None
-    _check(L.exl3_gemv_grouped(arr, len(shards), x.data_ptr(), y.data_ptr(), rows, ic, y.stride(0),
-                               None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
-                               _stream(x)), "exl3_gemv_grouped")
+    fus = None
+    if in_mode != IN_PLAIN or residual is not None:
+        if norm_weight is not None:
+            _cuda(norm_weight, "norm_weight", torch.float16)
+        if residual is not None:
+            _cuda(residual, "residual", torch.float16)
+            if residual.shape != y.shape:
+                raise RuntimeError("residual must have the shape of y")
+        fus = Exl3GemvFusion(in_mode, None if norm_weight is None else norm_weight.data_ptr(), float(eps), x.stride(0),
+                             None if residual is None else residual.data_ptr(),
+                             0 if residual is None else residual.stride(0))
+    _check(L.exl3_gemv_grouped_ex(arr, len(shards), x.data_ptr(), y.data_ptr(), rows, ic, y.stride(0),
+                                  None if ws is None else ws.data_ptr(), 0 if ws is None else ws.numel(),
+                                  None if fus is None else ctypes.byref(fus), _stream(x)), "exl3_gemv_grouped")
 
 
-def _shard_array(x: torch.Tensor, shards):
-    rows, ic = x.shape
+def _shard_array(x: torch.Tensor, shards, ic=None):
+    ic = x.shape[1] if ic is None else ic
     arr = (Exl3Shard * len(shards))()
     col = 0
     for i, s in enumerate(shards):

@@ -192,3 +192,49 @@ def test_workspace_reuse_across_shapes(ext):
     for ic, oc, K, rows in [(2560, 8704, 3, 4), (2560, 17408, 3, 4), (512, 1024, 4, 16), (2560, 17408 + 256, 2, 1),
                             (1024, 128, 6, 3), (2560, 17408, 5, 16)]:
         assert run(ic, oc, K, rows, ic + oc) < 5e-3, (ic, oc, K, rows)
+
+
+def _ref_layer(ext, x, tr, suh, svh, K):
+    xh = torch.empty_like(x)
+    ext.had_r_128(x, xh, suh, None, 1.0)
+    w = torch.empty((x.shape[1], svh.numel()), dtype=torch.half, device="cuda")
+    ext.reconstruct(w, tr, K, False, False)
+    y = (xh.float() @ w.float()).half()
+    ext.had_r_128(y, y, None, svh, 1.0)
+    return y
+
+
+@pytest.mark.parametrize("rows", [1, 5, 16])
+def test_gemv_fused_rmsnorm_and_residual(ext, rows):
+    """RMSNorm folded into the activation pre-pass and the residual add into the epilogue equal the
+    separate operations."""
+    ic, oc, K = 1024, 512, 4
+    tr, suh, svh, x = R.make_layer(300 + rows, ic, oc, K, rows)
+    g = torch.Generator().manual_seed(3)
+    gamma = (1.0 + 0.1 * torch.randn(ic, generator=g)).half().cuda()
+    res = torch.randn((rows, oc), generator=g).half().cuda()
+    xg, trg, sug, svg = (x * 3.0).half().cuda(), tr.cuda(), suh.cuda(), svh.cuda()
+    sh = [dict(trellis=trg, suh=sug, svh=svg, mcg=False, mul1=False)]
+    y = torch.empty((rows, oc), dtype=torch.half, device="cuda")
+    ext.gemv_grouped(xg, sh, y, in_mode=ext.IN_RMSNORM, norm_weight=gamma, eps=1e-5, residual=res)
+    xf = xg.float()
+    xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()).half()
+    ref = (_ref_layer(ext, xn, trg, sug, svg, K).float() + res.float())
+    assert (y.float() - ref).abs().max() / ref.abs().max() < 5e-3
+    # in-place residual update
+    y2 = res.clone()
+    ext.gemv_grouped(xg, sh, y2, in_mode=ext.IN_RMSNORM, norm_weight=gamma, eps=1e-5, residual=y2)
+    assert torch.equal(y2, y)
+
+
+@pytest.mark.parametrize("rows", [1, 7])
+def test_gemv_fused_silu_mul(ext, rows):
+    ic, oc, K = 768, 256, 3
+    tr, suh, svh, _ = R.make_layer(400 + rows, ic, oc, K, 1)
+    gu = torch.randn((rows, 2 * ic), generator=torch.Generator().manual_seed(rows)).half().cuda()
+    trg, sug, svg = tr.cuda(), suh.cuda(), svh.cuda()
+    y = torch.empty((rows, oc), dtype=torch.half, device="cuda")
+    ext.gemv_grouped(gu, [dict(trellis=trg, suh=sug, svh=svg, mcg=False, mul1=False)], y, in_mode=ext.IN_SILU_MUL)
+    act = (torch.nn.functional.silu(gu[:, :ic].float()) * gu[:, ic:].float()).half()
+    ref = _ref_layer(ext, act, trg, sug, svg, K).float()
+    assert (y.float() - ref).abs().max() / ref.abs().max() < 5e-3
