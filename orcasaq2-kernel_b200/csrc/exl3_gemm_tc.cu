@@ -8,7 +8,8 @@
 // output channels per CTA = the 128 TMEM lanes), tokens the N side (up to 512 per CTA = all 512
 // TMEM columns), so every decoded weight tile is used for up to 512 tokens.
 //
-// CTA = 19 warps, one CTA per SM:
+// CTA = 19 warps, one CTA per SM (up to 256 rows: 11 warps, one decode group, two CTAs per SM, so
+// that one CTA's pipeline bubbles are filled by the other):
 //   warp 0      producer of the packed trellis: 1-D bulk copies into a deep ring (mbarrier completion)
 //   warp 18     producer of the activation tiles: 2-D tiled TMA loads with 128-byte swizzle
 //   warp 1      allocates tensor memory, issues tcgen05.mma (one elected lane), commits to mbarriers
@@ -33,12 +34,14 @@
 namespace exl3 {
 namespace tc {
 
-constexpr int kThreads = 608;            // 19 warps
+// warps: 0 trellis producer, 1 MMA issue, 2 .. 2+8G-1 decode (G groups of eight), last = activation producer
+__host__ __device__ constexpr int threads_for(int groups) { return 32 * (3 + 8 * groups); }
 constexpr int kDecodeWarps = 8;          // per group; two groups take alternate stages
 constexpr int kBM = 128;                 // output channels per CTA
 constexpr int kBK = 64;                  // input channels per stage (one 128-byte swizzle row)
 constexpr int kBN = 256;                 // tokens per accumulator / per TMA box
 constexpr int kMaxHalves = 2;            // accumulators per CTA (512 tokens)
+constexpr int kSmallRows = 64;           // up to here: one decode group per CTA, two CTAs per SM
 constexpr int kStagesA = 4;
 constexpr int kMaxSlotsB = 16;            // ring of token-half tiles: 4 x 32 KB, more when the tiles are small
 constexpr int kABytes = kBM * kBK * 2;               // 16 KB
@@ -126,6 +129,8 @@ struct Params {
     int b_slot_bytes;      // box_rows * 128, rounded up to 1024
     int raw_stages;        // depth of the packed-trellis ring
     int b_slots;           // depth of the activation-tile ring
+    int tmem_cols;         // tensor-memory columns to allocate (power of two, 32..512)
+    int a_stages;          // decoded-tile stages in use (<= kStagesA)
     int splitk;            // slices of the input dimension (grid.z)
     float *partial;        // [splitk][tokens][oc] fp32 when splitk > 1
     uint32_t one;
@@ -146,8 +151,8 @@ struct SmemView {
     uint32_t *raw;
 };
 
-template <int K>
-__global__ void __launch_bounds__(kThreads, 1)
+template <int K, int G>
+__global__ void __launch_bounds__(threads_for(G), G == 1 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     extern __shared__ unsigned char smem_dyn[];
     // swizzled tiles need 1024-byte alignment; the launch reserves the slack
@@ -155,7 +160,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     constexpr int kRawWords = 4 * 8 * 8 * K;                      // four tile rows of eight tiles
     constexpr uint32_t kRawRowBytes = 8 * 8 * K * 4;
     unsigned char *const smA = smem_raw;
-    unsigned char *const smB = smem_raw + kStagesA * kABytes;
+    const int nStagesA = P.a_stages;
+    unsigned char *const smB = smem_raw + nStagesA * kABytes;
     Barriers &S = *reinterpret_cast<Barriers *>(smB + (size_t)P.b_slots * P.b_slot_bytes);
     uint32_t *raw = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(&S) + 1024);
     const int kStagesRaw = P.raw_stages;
@@ -179,7 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) {   // tensor memory: all 512 columns (one CTA per SM by construction)
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(s32(&S.tmem_base)) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&S.tmem_base)), "r"(P.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -203,7 +209,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
                              kRawRowBytes, s32(&S.raw_full[rs]));
             }
         }
-    } else if (warp == kThreads / 32 - 1) {
+    } else if (warp == threads_for(G) / 32 - 1) {
         // ---------------- producer of the activation tiles
         if (lane == 0) {
             const uint32_t box_bytes = (uint32_t)P.box_rows * (kBK * 2);
@@ -226,8 +232,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             bool ok = true;
             int bi = 0;
             for (int s = 0; s < nsteps && ok; ++s) {
-                const int as = s % kStagesA;
-                ok = mbar_wait(s32(&S.a_full[as]), (s / kStagesA) & 1);
+                const int as = s % nStagesA;
+                ok = mbar_wait(s32(&S.a_full[as]), (s / nStagesA) & 1);
                 const uint32_t a0 = s32(smA + as * kABytes);
                 for (int h = 0; h < halves && ok; ++h, ++bi) {
                     const int bs = bi % kSlotsB;
@@ -255,8 +261,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         const DecodeConsts dc(P.one);
         const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
         bool ok = true;
-        for (int s = grp; s < nsteps && ok; s += 2) {
-            const int rs = s % kStagesRaw, as = s % kStagesA;
+        for (int s = grp; s < nsteps && ok; s += G) {
+            const int rs = s % kStagesRaw, as = s % nStagesA;
             ok = mbar_wait(s32(&S.raw_full[rs]), (s / kStagesRaw) & 1);
             uint32_t wd[K + 1];
             {
@@ -269,7 +275,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             if (lane == 0) mbar_arrive(s32(&S.raw_empty[rs]));
             uint32_t z[32];
             decode_chunk_fast<K>(wd, z, dc);
-            if (s >= kStagesA) ok = ok && mbar_wait(s32(&S.a_empty[as]), ((s / kStagesA) - 1) & 1);
+            if (s >= nStagesA) ok = ok && mbar_wait(s32(&S.a_empty[as]), ((s / nStagesA) - 1) & 1);
             // weights of output channel (a, hm): input channels j = 2b + hk, adjacent in k'
             unsigned char *abase = smA + as * kABytes;
 #pragma unroll
@@ -305,7 +311,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         const int col_part = (warp - 2) >> 2;     // four warps share a lane quadrant
         for (int h = 0; h < halves; ++h) {
             const int ncols = min(kBN, tok_here - h * kBN);
-            for (int c0 = col_part * 32; c0 < ncols; c0 += 128) {
+            for (int c0 = col_part * 32; c0 < ncols; c0 += 64 * G) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(h * kBN + c0);
                 asm volatile(
@@ -337,7 +343,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     __syncthreads();
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(P.tmem_cols) : "memory");
     }
 }
 
@@ -421,27 +427,33 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-template <int K>
-static int launch(const CUtensorMap &map, Params P, cudaStream_t st) {
+template <int K, int G>
+static int launch_g(const CUtensorMap &map, Params P, cudaStream_t st) {
     const size_t raw_stage = (size_t)(4 * 8 * 8 * K) * 4;
     P.b_slots = 4;
-    const size_t fixed = (size_t)kStagesA * kABytes + (size_t)P.b_slots * P.b_slot_bytes + 1024 /*barriers*/ + 1024 /*alignment*/;
-    const size_t budget = 226 * 1024;
-    // keep ~64 KB of packed trellis in flight when the tiles leave room for it
+    P.a_stages = G == 1 ? 3 : kStagesA;
+    const size_t fixed = (size_t)P.a_stages * kABytes + (size_t)P.b_slots * P.b_slot_bytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+    // G == 1: two CTAs share an SM (about 110 KB each); G == 2: one CTA owns it
+    const size_t budget = (G == 1 ? 112 : 226) * 1024;
+    if (fixed + 2 * raw_stage > budget) return EXL3_E_SHAPE;
     size_t stages = (budget - fixed) / raw_stage;
-    const size_t want = (64 * 1024 + raw_stage - 1) / raw_stage;
+    const size_t want = ((G == 1 ? 32 : 64) * 1024 + raw_stage - 1) / raw_stage;   // packed trellis in flight per CTA
     if (stages > want) stages = want;
     if (stages > (size_t)kMaxRawStages) stages = kMaxRawStages;
-    if (stages < 2) return EXL3_E_SHAPE;
     P.raw_stages = (int)stages;
     const size_t smem = fixed + stages * raw_stage;
-    if (cudaFuncSetAttribute(gemm_tc_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(gemm_tc_kernel<K, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
     }
     dim3 grid(P.oc / kBM, (P.tokens + kBN * kMaxHalves - 1) / (kBN * kMaxHalves), P.splitk);
-    gemm_tc_kernel<K><<<grid, kThreads, smem, st>>>(map, P);
+    gemm_tc_kernel<K, G><<<grid, threads_for(G), smem, st>>>(map, P);
     return launch_status();
+}
+
+template <int K>
+static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
+    return P.tokens <= kSmallRows ? launch_g<K, 1>(map, P, st) : launch_g<K, 2>(map, P, st);
 }
 
 }  // namespace tc
@@ -462,7 +474,8 @@ static int choose_splitk(int rows, int ic, int oc) {
     const int ctas = (oc / kBM) * ((rows + kBN * kMaxHalves - 1) / (kBN * kMaxHalves));
     const int steps = ic / kBK;
     int sk = 1;
-    if (ctas < 120) sk = (148 + ctas - 1) / ctas;
+    const int slots = rows <= kSmallRows ? 296 : 148;   // small batches: two CTAs share an SM
+    if (ctas < slots * 4 / 5) sk = (slots + ctas / 2) / ctas;
     if (sk > steps / 8) sk = steps / 8;
     return sk < 1 ? 1 : sk;
 }
@@ -520,6 +533,12 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
     P.tokens = rows; P.ic = ic; P.oc = oc; P.ldy = oc; P.tiles_j = oc / 16; P.one = 1u;
     P.splitk = splitk;
     P.box_rows = box_rows;
+    {
+        int cols = 32;
+        const int need = rows > kBN ? kBN * kMaxHalves : box_rows;
+        while (cols < need) cols <<= 1;
+        P.tmem_cols = cols;
+    }
     P.b_slot_bytes = (box_rows * kBK * 2 + 1023) & ~1023;
     P.partial = splitk > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic)) : nullptr;
     int rc;

@@ -19,6 +19,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #include "exl3_codec.cuh"
 #include "exl3_common.cuh"
@@ -460,6 +461,17 @@ struct GemvPlan {
     long long partial_off[EXL3_MAX_SHARDS];
 };
 
+// CTAs per launch the plan aims for; EXL3_GEMV_TARGET_CTAS overrides it (tuning knob).
+static int target_ctas() {
+    static int v = 0;
+    if (!v) {
+        const char *e = getenv("EXL3_GEMV_TARGET_CTAS");
+        v = e ? atoi(e) : kTargetCtas;
+        if (v < 1) v = kTargetCtas;
+    }
+    return v;
+}
+
 static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl) {
     if (!sh) return EXL3_E_NULL;
     if (n < 1 || n > EXL3_MAX_SHARDS || rows < 1 || rows > EXL3_GEMV_MAX_ROWS || ic <= 0 || (ic & 127))
@@ -485,7 +497,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     for (int i = 0; i < n; ++i) {
         const int ocb = sh[i].oc / 128;
         const double share = (double)ic * sh[i].oc * pl.K[i] / 8.0 / total_bytes;
-        int sk = (int)(kTargetCtas * share / ocb + 0.5);
+        int sk = (int)(target_ctas() * share / ocb + 0.5);
         if (sk < 1) sk = 1;
         if (sk > pl.kblocks) sk = pl.kblocks;
         if (sk > kMaxSplitK) sk = kMaxSplitK;
