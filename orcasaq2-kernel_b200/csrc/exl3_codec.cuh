@@ -81,6 +81,27 @@ __device__ __forceinline__ void decode_chunk(const uint32_t (&w)[K + 1], uint32_
     ChunkDecoder<K, 0>::run(w, z);
 }
 
+// K consecutive 32-bit words from shared memory, widest loads the alignment allows.
+template <int K>
+__device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&w)[K + 1]) {
+    if constexpr (K % 4 == 0) {
+#pragma unroll
+        for (int k = 0; k < K; k += 4) {
+            const uint4 v = *reinterpret_cast<const uint4 *>(src + k);
+            w[k] = v.x; w[k + 1] = v.y; w[k + 2] = v.z; w[k + 3] = v.w;
+        }
+    } else if constexpr (K % 2 == 0) {
+#pragma unroll
+        for (int k = 0; k < K; k += 2) {
+            const uint2 v = *reinterpret_cast<const uint2 *>(src + k);
+            w[k] = v.x; w[k + 1] = v.y;
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < K; ++k) w[k] = src[k];
+    }
+}
+
 // position of weight i of chunk c inside the 16x16 tile
 __device__ __forceinline__ int tile_row(int c, int i) {
     return 8 * ((i >> 2) & 1) + 4 * ((i >> 1) & 1) + (c & 3);

@@ -31,6 +31,10 @@
 #include "exl3_decode_fast.cuh"
 #include "exl3_hadamard.cuh"
 
+#ifndef EXL3_TC_WAIT_OP
+#define EXL3_TC_WAIT_OP "try_wait"
+#endif
+
 namespace exl3 {
 namespace tc {
 
@@ -68,14 +72,17 @@ __device__ __forceinline__ unsigned long long now_ns() {
 }
 // Bounded wait: polls the barrier; after kWaitNs without success it records the failure in the
 // status word and returns false (the caller stops its loop, the kernel still exits cleanly).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+// `sleep_ns` > 0 backs off between polls: a spinning warp competes with the decode warps for issue
+// slots (measured: more than half of the kernel's instructions were polls before this).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned sleep_ns = 0) {
     unsigned long long t0 = 0;
     for (int it = 0; it < kSpin; ++it) {
         uint32_t ok;
         asm volatile(
-            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            "{\n\t.reg .pred p;\n\tmbarrier." EXL3_TC_WAIT_OP ".parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
             : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
         if (ok) return true;
+        if (sleep_ns) __nanosleep(sleep_ns);
         if ((it & 255) == 255) {
             const unsigned long long t = now_ns();
             if (t0 == 0) t0 = t;
@@ -119,6 +126,19 @@ __device__ __forceinline__ void umma(uint32_t d_tmem, uint64_t a, uint64_t b, ui
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+
+// Position in a ring of `n` slots: slot index, phase bit of the current round, and whether the
+// first round is over (only then does a producer have to wait for the slot to be released).
+struct Cursor {
+    int idx, n;
+    uint32_t phase;
+    bool wrapped;
+    __device__ __forceinline__ Cursor(int start, int slots) : idx(start), n(slots), phase(0), wrapped(false) {}
+    __device__ __forceinline__ void advance(int by) {
+        idx += by;
+        if (idx >= n) { idx -= n; phase ^= 1u; wrapped = true; }
+    }
+};
 
 struct Params {
     const uint32_t *trellis;
@@ -194,31 +214,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     const uint32_t tmem = S.tmem_base;
 
     if (warp == 0) {
-        // ---------------- producer of the packed trellis (runs ahead by the whole ring)
-        if (lane == 0) {
+        // ---------------- producer of the packed trellis (runs ahead by the whole ring).  Lanes 0..3
+        // each issue one of the four row copies of a stage: issuing them from one thread was the
+        // bottleneck of the whole kernel (about a quarter microsecond per bulk copy).
+        {
             const uint32_t *src_row0 = P.trellis + (size_t)ob * 8 * (8 * K);
             const size_t row_words = (size_t)P.tiles_j * (8 * K);
             bool ok = true;
-            for (int s = 0; s < nsteps && ok; ++s) {
-                const int rs = s % kStagesRaw;
-                if (s >= kStagesRaw) ok = mbar_wait(s32(&S.raw_empty[rs]), ((s / kStagesRaw) - 1) & 1);
+            Cursor rc(0, kStagesRaw);
+            for (int s = 0; s < nsteps; ++s, rc.advance(1)) {
+                const int rs = rc.idx;
+                if (lane == 0) {
+                    if (rc.wrapped) ok = mbar_wait(s32(&S.raw_empty[rs]), rc.phase ^ 1u, 200);
+                    if (ok) mbar_expect_tx(s32(&S.raw_full[rs]), 4 * kRawRowBytes);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
-                mbar_expect_tx(s32(&S.raw_full[rs]), 4 * kRawRowBytes);
-                for (int r = 0; r < 4; ++r)
-                    bulk_g2s(s32(raw + rs * kRawWords + r * (kRawWords / 4)), src_row0 + (size_t)(4 * (step0 + s) + r) * row_words,
-                             kRawRowBytes, s32(&S.raw_full[rs]));
+                if (lane < 4)
+                    bulk_g2s(s32(raw + rs * kRawWords + lane * (kRawWords / 4)),
+                             src_row0 + (size_t)(4 * (step0 + s) + lane) * row_words, kRawRowBytes, s32(&S.raw_full[rs]));
             }
         }
     } else if (warp == threads_for(G) / 32 - 1) {
         // ---------------- producer of the activation tiles
         if (lane == 0) {
             const uint32_t box_bytes = (uint32_t)P.box_rows * (kBK * 2);
-            int bi = 0;                                          // running index of token-half tiles
+            Cursor bc(0, kSlotsB);                               // ring of token-half tiles
             bool ok = true;
             for (int s = 0; s < nsteps && ok; ++s) {
-                for (int h = 0; h < halves && ok; ++h, ++bi) {
-                    const int bs = bi % kSlotsB;
-                    if (bi >= kSlotsB) ok = mbar_wait(s32(&S.b_empty[bs]), ((bi / kSlotsB) - 1) & 1);
+                for (int h = 0; h < halves && ok; ++h, bc.advance(1)) {
+                    const int bs = bc.idx;
+                    if (bc.wrapped) ok = mbar_wait(s32(&S.b_empty[bs]), bc.phase ^ 1u, 200);
                     if (!ok) break;
                     mbar_expect_tx(s32(&S.b_full[bs]), box_bytes);
                     tma_2d(s32(smB + (size_t)bs * P.b_slot_bytes), &xmap, (step0 + s) * kBK, tok0 + h * kBN, s32(&S.b_full[bs]));
@@ -230,15 +256,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         if (lane == 0) {
             const int n_last = ((tok_here - (halves - 1) * kBN) + 15) & ~15;      // tokens in the last half, padded to 16
             bool ok = true;
-            int bi = 0;
-            for (int s = 0; s < nsteps && ok; ++s) {
-                const int as = s % nStagesA;
-                ok = mbar_wait(s32(&S.a_full[as]), (s / nStagesA) & 1);
+            Cursor ac(0, nStagesA), bc(0, kSlotsB);
+            for (int s = 0; s < nsteps && ok; ++s, ac.advance(1)) {
+                const int as = ac.idx;
+                ok = mbar_wait(s32(&S.a_full[as]), ac.phase, G == 1 ? 40 : 0);
                 const uint32_t a0 = s32(smA + as * kABytes);
-                for (int h = 0; h < halves && ok; ++h, ++bi) {
-                    const int bs = bi % kSlotsB;
-                    ok = mbar_wait(s32(&S.b_full[bs]), (bi / kSlotsB) & 1);
+                for (int h = 0; h < halves && ok; ++h, bc.advance(1)) {
+                    const int bs = bc.idx;
+                    ok = mbar_wait(s32(&S.b_full[bs]), bc.phase, G == 1 ? 40 : 0);
                     if (!ok) break;
+                    if (G == 1) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // decoded tile: generic writes -> tensor-core reads
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint32_t b0 = s32(smB + (size_t)bs * P.b_slot_bytes);
                     const uint32_t idesc = umma_idesc(h == halves - 1 ? n_last : kBN);
@@ -255,27 +282,28 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         // ---------------- decode warps
         const int grp = (warp - 2) >> 3;           // stages s = grp, grp + 2, ...
         const int dw = (warp - 2) & 7;             // 0..7 inside the group
-        const int t_ic = dw >> 1;                  // which of the four 16-channel tiles of the stage
-        const int half_oc = dw & 1;                // which four of the eight output tiles
+        // A warp takes ONE output tile (dw) and all four 16-channel input tiles of the stage: lane
+        // group u = lane >> 3 works on input tile u.  (Four output tiles at one input tile would send
+        // the four groups to the same shared-memory banks: the swizzle only depends on row & 7.)
         const int u = lane >> 3, c = lane & 7, p = c >> 2, q = c & 3;
         const DecodeConsts dc(P.one);
         const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
         bool ok = true;
-        for (int s = grp; s < nsteps && ok; s += G) {
-            const int rs = s % kStagesRaw, as = s % nStagesA;
-            ok = mbar_wait(s32(&S.raw_full[rs]), (s / kStagesRaw) & 1);
+        Cursor rc(grp, kStagesRaw), ac(grp, nStagesA);
+        for (int s = grp; s < nsteps && ok; s += G, rc.advance(G), ac.advance(G)) {
+            const int rs = rc.idx, as = ac.idx;
+            ok = mbar_wait(s32(&S.raw_full[rs]), rc.phase, 60);
             uint32_t wd[K + 1];
             {
-                const uint32_t *src = raw + rs * kRawWords + t_ic * (kRawWords / 4) + half_oc * (4 * 8 * K) + lane * K;
-#pragma unroll
-                for (int k = 0; k < K; ++k) wd[k] = src[k];
+                const uint32_t *src = raw + rs * kRawWords + u * (kRawWords / 4) + dw * (8 * K) + c * K;
+                load_words<K>(src, wd);
             }
             wd[K] = __shfl_sync(0xffffffffu, wd[0], nxt_lane);
             __syncwarp();
             if (lane == 0) mbar_arrive(s32(&S.raw_empty[rs]));
             uint32_t z[32];
             decode_chunk_fast<K>(wd, z, dc);
-            if (s >= nStagesA) ok = ok && mbar_wait(s32(&S.a_empty[as]), ((s / nStagesA) - 1) & 1);
+            if (ac.wrapped) ok = ok && mbar_wait(s32(&S.a_empty[as]), ac.phase ^ 1u, 60);
             // weights of output channel (a, hm): input channels j = 2b + hk, adjacent in k'
             unsigned char *abase = smA + as * kABytes;
 #pragma unroll
@@ -290,20 +318,24 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
                     asm("prmt.b32 %0, %1, %2, 0x7632;" : "=r"(hi23) : "r"(z2), "r"(z3));
                     const __half2 w01 = __hadd2(*reinterpret_cast<__half2 *>(&lo01), *reinterpret_cast<__half2 *>(&hi01));
                     const __half2 w23 = __hadd2(*reinterpret_cast<__half2 *>(&lo23), *reinterpret_cast<__half2 *>(&hi23));
-                    const int r = 16 * (4 * half_oc + u) + 4 * a + 2 * hm + p;          // row of the A tile
-                    const int chunk = (2 * t_ic + (q >> 1)) ^ (r & 7);                  // 128-byte swizzle
+                    const int r = 16 * dw + 4 * a + 2 * hm + p;                         // row of the A tile
+                    const int chunk = (2 * u + (q >> 1)) ^ (r & 7);                     // 128-byte swizzle
                     uint2 v;
                     v.x = *reinterpret_cast<const uint32_t *>(&w01);
                     v.y = *reinterpret_cast<const uint32_t *>(&w23);
                     *reinterpret_cast<uint2 *>(abase + r * 128 + chunk * 16 + (q & 1) * 8) = v;
                 }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> tensor-core reads
+            // release the tile.  Few rows (G == 1): decode is the critical path, so the MMA-issuing
+            // thread, which acquires the tile through the barrier, makes the generic-proxy writes
+            // visible to the tensor core with one proxy fence on its side.  Many rows (G == 2): the
+            // MMA issue is the critical path, so the writers fence instead.
+            if (G == 2) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // many rows: the writers have slack
             __syncwarp();
             if (lane == 0) mbar_arrive(s32(&S.a_full[as]));
         }
 
         // ---------------- epilogue: TMEM -> fp16 -> y[token][oc]
-        ok = mbar_wait(s32(&S.acc_full), 0) && ok;
+        ok = mbar_wait(s32(&S.acc_full), 0, 200) && ok;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
         const int oc_row = ob * kBM + 32 * quad + lane;

@@ -125,27 +125,6 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t *a, uint3
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// K consecutive 32-bit words from shared memory, widest loads the alignment allows.
-template <int K>
-__device__ __forceinline__ void load_words(const uint32_t *src, uint32_t (&w)[K + 1]) {
-    if constexpr (K % 4 == 0) {
-#pragma unroll
-        for (int k = 0; k < K; k += 4) {
-            const uint4 v = *reinterpret_cast<const uint4 *>(src + k);
-            w[k] = v.x; w[k + 1] = v.y; w[k + 2] = v.z; w[k + 3] = v.w;
-        }
-    } else if constexpr (K % 2 == 0) {
-#pragma unroll
-        for (int k = 0; k < K; k += 2) {
-            const uint2 v = *reinterpret_cast<const uint2 *>(src + k);
-            w[k] = v.x; w[k + 1] = v.y;
-        }
-    } else {
-#pragma unroll
-        for (int k = 0; k < K; ++k) w[k] = src[k];
-    }
-}
-
 // ---------------------------------------------------------------------------------------------
 template <int K, int NT>
 __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev &S, int local,
