@@ -189,13 +189,41 @@ def run_gpu(args):
 
     for i in range(max(3, args.warmup)):
         step(i)
+    # The timed region replays ONE CUDA graph holding exactly `--steps` steps (weight sets rotated):
+    # the launches, and for N > 1 the NCCL all-reduces, are issued by the GPU front end, so the
+    # host's launch cost (tens of microseconds per call from Python) is not what gets measured.
+    graph, period = None, args.steps
+    if not args.no_graph:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for i in range(N_SETS):
+                step(i)                                     # scratch for this stream exists before capture
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(period):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        graph.replay()
+    reps = max(1, args.steps // period) if graph is not None else 0
+    timed_steps = reps * period if graph is not None else args.steps
+
+    def timed():
+        if graph is not None:
+            for _ in range(reps):
+                graph.replay()
+        else:
+            for i in range(args.steps):
+                step(i)
+
     sampler = ClockSampler(local)
     barrier()
     sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(args.steps):
-        step(i)
+    timed()
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
@@ -206,17 +234,18 @@ def run_gpu(args):
     if ms < 400:
         # keep the GPU under the same load long enough for the 100 ms clock sampler to see it; the
         # repeat count comes from the rank-agreed time so every rank issues the same collectives
-        for j in range(int(400.0 / max(ms / args.steps, 1e-3))):
-            step(j)
+        for _ in range(int(400.0 / max(ms, 1e-3))):
+            timed()
         torch.cuda.synchronize()
     clocks = sampler.stop()
-    ms_step = ms / args.steps
+    ms_step = ms / timed_steps
     value = full_bytes / (ms_step * 1e-3) / 1e9
 
     if args.skip_extras:
         if rank == 0:
             print(json.dumps({"metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)",
                               "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms_step, 5),
+                              "steps": timed_steps,
                               "config": {"workload": ",".join(l[0] for l in LAYERS), "rows": rows},
                               "note": "profiling run: extras skipped"}), flush=True)
         if world > 1:
@@ -289,7 +318,7 @@ def run_gpu(args):
         return
     line = {
         "metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)", "value": round(value, 1),
-        "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(3, args.warmup),
+        "unit": "GB/s", "n_gpus": world, "steps": timed_steps, "warmup": max(3, args.warmup),
         "ms_per_step": round(ms_step, 5), "higher_is_better": True,
         "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
@@ -300,7 +329,9 @@ def run_gpu(args):
                    "pct_of_8TBs_nominal": round(value / 8000.0 * 100, 2)},
         "e2e": {"value": round(full_bytes / e2e_s / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 5)},
-        "gpu_launches": args.steps * len(LAYERS), "clocks": clocks, "roofline": roof,
+        # every fused layer is two kernels of this library: the activation pre-pass and the GEMV
+        "gpu_launches": timed_steps * len(LAYERS) * 2, "cuda_graph": graph is not None,
+        "clocks": clocks, "roofline": roof,
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
@@ -311,7 +342,7 @@ def run_gpu(args):
 
 # per-launch DRAM traffic of the gate_up kernel from ncu (dram__bytes_read.sum + write), keyed by
 # (rows, world); filled from the captures summarised under profiles/
-NCU_TRAFFIC_BYTES = {}
+NCU_TRAFFIC_BYTES = {(1, 1): 67_521_280}     # profiles/gemv_kernel_gate_up_rows1.md: 67.03 MB read + 0.49 MB written
 
 
 # ------------------------------------------------------------------------------------ CPU arms
@@ -405,6 +436,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--only", default=None, choices=[l[0] for l in LAYERS],
                     help="run just this fused layer each step (small case for profiling)")
+    ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
     ap.add_argument("--skip-extras", action="store_true",
                     help="skip the end-to-end, roofline and CPU-baseline legs (profiling runs)")
     args = ap.parse_args()
