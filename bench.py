@@ -149,6 +149,19 @@ def build_sets(torch, device, rank, world):
     return sets
 
 
+def _leave(world):
+    """End a multi-rank run without tearing NCCL down under a live captured graph (that teardown can
+    block): agree that everyone is done, flush, and exit the process."""
+    if world > 1:
+        import torch
+        import torch.distributed as dist
+        torch.cuda.synchronize()
+        dist.barrier()
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -248,8 +261,7 @@ def run_gpu(args):
                               "steps": timed_steps,
                               "config": {"workload": ",".join(l[0] for l in LAYERS), "rows": rows},
                               "note": "profiling run: extras skipped"}), flush=True)
-        if world > 1:
-            dist.destroy_process_group()
+        _leave(world)
         return
     # ---- end to end: host activations in, host outputs back, through the plugin's custom op
     hx = {ic: x.cpu().pin_memory() for ic, x in xs.items()}
@@ -313,8 +325,7 @@ def run_gpu(args):
         if world == 1:
             cpu = cpu_baseline(rows)
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
+        _leave(world)
         return
     line = {
         "metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)", "value": round(value, 1),
@@ -336,8 +347,7 @@ def run_gpu(args):
     if cpu is not None:
         line["cpu_baseline"] = cpu
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
+    _leave(world)
 
 
 # per-launch DRAM traffic of the gate_up kernel from ncu (dram__bytes_read.sum + write), keyed by
