@@ -171,6 +171,16 @@ struct SmemView {
     uint32_t *raw;
 };
 
+// Per-warp cycle counts of the decode loop's phases, compiled in only for the timing study.
+#ifdef EXL3_TC_TRACE
+__device__ unsigned long long g_tc_trace[4096][32][6];
+#define TC_CLK(v) const long long v = clock64()
+#define TC_ACC(i, a, b) tc_acc[i] += (unsigned long long)((b) - (a))
+#else
+#define TC_CLK(v) do { } while (0)
+#define TC_ACC(i, a, b) do { } while (0)
+#endif
+
 template <int K, int G>
 __global__ void __launch_bounds__(threads_for(G), G == 1 ? 2 : 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
@@ -289,10 +299,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         const DecodeConsts dc(P.one);
         const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
         bool ok = true;
+#ifdef EXL3_TC_TRACE
+        unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
+        const long long tc_begin = clock64();
+#endif
         Cursor rc(grp, kStagesRaw), ac(grp, nStagesA);
         for (int s = grp; s < nsteps && ok; s += G, rc.advance(G), ac.advance(G)) {
             const int rs = rc.idx, as = ac.idx;
+            TC_CLK(c0);
             ok = mbar_wait(s32(&S.raw_full[rs]), rc.phase, 60);
+            TC_CLK(c1);
+            TC_ACC(0, c0, c1);
             uint32_t wd[K + 1];
             {
                 const uint32_t *src = raw + rs * kRawWords + u * (kRawWords / 4) + dw * (8 * K) + c * K;
@@ -303,7 +320,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             if (lane == 0) mbar_arrive(s32(&S.raw_empty[rs]));
             uint32_t z[32];
             decode_chunk_fast<K>(wd, z, dc);
+            TC_CLK(c2);
+            TC_ACC(1, c1, c2);
             if (ac.wrapped) ok = ok && mbar_wait(s32(&S.a_empty[as]), ac.phase ^ 1u, 60);
+            TC_CLK(c3);
+            TC_ACC(2, c2, c3);
             // weights of output channel (a, hm): input channels j = 2b + hk, adjacent in k'
             unsigned char *abase = smA + as * kABytes;
 #pragma unroll
@@ -332,10 +353,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             if (G == 2) asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // many rows: the writers have slack
             __syncwarp();
             if (lane == 0) mbar_arrive(s32(&S.a_full[as]));
+            TC_CLK(c4);
+            TC_ACC(3, c3, c4);
         }
+#ifdef EXL3_TC_TRACE
+        const long long tc_loop_end = clock64();
+#endif
 
         // ---------------- epilogue: TMEM -> fp16 -> y[token][oc]
         ok = mbar_wait(s32(&S.acc_full), 0, 200) && ok;
+#ifdef EXL3_TC_TRACE
+        if (lane == 0 && blockIdx.y == 0) {
+            const int cta = blockIdx.x + gridDim.x * blockIdx.z;
+            if (cta < 4096) {
+                for (int i = 0; i < 4; ++i) g_tc_trace[cta][warp][i] = tc_acc[i];
+                g_tc_trace[cta][warp][4] = (unsigned long long)(tc_loop_end - tc_begin);
+                g_tc_trace[cta][warp][5] = (unsigned long long)(clock64() - tc_loop_end);
+            }
+        }
+#endif
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
         const int oc_row = ob * kBM + 32 * quad + lane;
@@ -491,6 +527,8 @@ static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
 }  // namespace tc
 }  // namespace exl3
 
+#include "exl3_gemm_ts.cuh"
+
 extern "C" int exl3_had_r_128(const void *in, void *out, const void *pre, const void *post, float scale, int rows,
                               int n, void *stream);
 
@@ -516,6 +554,7 @@ static size_t xh_bytes(int rows, int ic) { return (((size_t)rows * ic * 2) + 255
 
 extern "C" size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc) {
     if (rows < 1 || ic <= 0 || oc <= 0) return 0;
+    if (exl3::ts::eligible(rows, ic, oc)) return exl3::ts::scratch_bytes(rows, ic, oc);
     const int sk = exl3::tc::choose_splitk(rows, ic, oc);
     return exl3::tc::xh_bytes(rows, ic) + (sk > 1 ? (size_t)sk * rows * oc * 4 : 0);
 }
@@ -535,10 +574,54 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
         !aligned(svh, 8))
         return EXL3_E_ALIGN;
     if (scratch_bytes < exl3_gemm_tc_scratch_bytes(rows, ic, oc)) return EXL3_E_WORKSPACE;
-    const int splitk = choose_splitk(rows, ic, oc);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     EncodeTiledFn enc = encode_fn();
     if (!enc) return EXL3_E_LAUNCH;
+
+    if (ts::eligible(rows, ic, oc)) {
+        // ---- up to 128 rows: codewords go from registers to tensor memory (exl3_gemm_ts.cuh)
+        const int sk = ts::choose_splitk(ic, oc);
+        const long long nblocks = (long long)rows * (ic / 128);
+        const unsigned g1 = (unsigned)((nblocks + 7) / 8);
+        if (x_is_bf16)
+            xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(scratch), nblocks, ic / 128);
+        else
+            xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(scratch), nblocks, ic / 128);
+        if (cudaGetLastError() != cudaSuccess) return EXL3_E_LAUNCH;
+        ts::Params P;
+        P.trellis = static_cast<const uint32_t *>(trellis);
+        P.y = static_cast<__half *>(y);
+        P.tokens = rows; P.npad = (rows + 15) & ~15;
+        P.ic = ic; P.oc = oc; P.ldy = oc; P.tiles_j = oc / 16; P.splitk = sk; P.one = 1u;
+        P.b_slot_bytes = (P.npad * 128 + 1023) & ~1023;
+        P.partial = sk > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + ts::xh_bytes(rows, ic)) : nullptr;
+        CUtensorMap map;
+        const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
+        const cuuint64_t gstr[1] = {(cuuint64_t)ic * 2};
+        const cuuint32_t box[2] = {64u, (cuuint32_t)P.npad};
+        const cuuint32_t estr[2] = {1, 1};
+        if (enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, scratch, gdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return EXL3_E_LAUNCH;
+        int rc;
+        switch (K) {
+            case 1: rc = ts::launch<1>(map, P, st); break;
+            case 2: rc = ts::launch<2>(map, P, st); break;
+            case 3: rc = ts::launch<3>(map, P, st); break;
+            case 4: rc = ts::launch<4>(map, P, st); break;
+            case 5: rc = ts::launch<5>(map, P, st); break;
+            case 6: rc = ts::launch<6>(map, P, st); break;
+            case 7: rc = ts::launch<7>(map, P, st); break;
+            default: rc = ts::launch<8>(map, P, st); break;
+        }
+        if (rc != EXL3_OK) return rc;
+        if (sk == 1) return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
+        const long long nb = (long long)rows * (oc / 128);
+        reduce_had_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(P.partial, sk, static_cast<const __half *>(svh),
+                                                                   static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc);
+        return launch_status();
+    }
+    const int splitk = choose_splitk(rows, ic, oc);
 
     // 1. rotate and permute the activations
     const long long nblocks = (long long)rows * (ic / 128);

@@ -1,0 +1,316 @@
+// EXL3 GEMM for a few dozen rows (17 .. 128): the decoded weights never touch shared memory.
+//
+//     Yt[tokens][oc] = Xh[tokens][ic] . W(trellis)[ic][oc]          (fp16 in, fp32 accumulate)
+//
+// Decode warps turn the packed trellis into fp16 weights in registers exactly as the decode GEMV
+// reads it (one 32-weight chunk per lane, four tiles side by side per warp; weight = sum of the
+// codeword's two halves, the same rounding as reconstruct) and store them with tcgen05.st straight
+// into TENSOR MEMORY, where tcgen05.mma reads them as its A operand; the activations (B operand)
+// come from shared memory, loaded by TMA.  The registers of an mma.sync A fragment are what
+// tcgen05.st.16x256b writes as a 16-row x 8-column block, so the chunk layout of the packed format
+// maps onto tensor memory without any shuffle: per chunk two stores of eight registers.
+//
+// Issuing a tcgen05 instruction costs the issuing thread about 55 cycles (measured), so the loop
+// is organised to need few of them: a ROUND is four tile rows (64 input channels, one tile row per
+// decode group), and costs one fence, eight MMAs and one commit.
+//
+// CTA = 256 output channels x a slice of the input channels x up to 128 tokens, one CTA per SM:
+//   warp 0        lanes 0..3: packed trellis of the four decode groups (1-D bulk copies into
+//                 per-group rings); lane 4: activation tiles (2-D tiled TMA, 128-byte swizzle), one
+//                 per round
+//   warp 1        allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
+//   warps 2..17   four decode groups of four warps (one warp per TMEM lane quarter = 64 output
+//                 channels); group g takes the tile rows g, g+4, ... of the slice; afterwards the
+//                 epilogue (tcgen05.ld, fp32 partial sums or fp16 outputs)
+// Tensor memory: accumulators X and Y (rows a = 0,1 and a = 2,3 of every four-tile span) in columns
+// [0, 2 npad), then kBufs A buffers of 64 columns (16 per group: 8 for X, 8 for Y).
+// The K order inside a tile row is k = 4 (ic & 3) + 2 (ic >> 3) + ((ic >> 2) & 1), the order in which
+// a lane's registers hold it; the activation pre-pass writes the same order.
+// Every wait is bounded; a wait that runs out sets the status word and the kernel still frees its
+// tensor memory and exits.
+#pragma once
+#include "exl3_tcgen05.cuh"
+
+namespace exl3 {
+namespace ts {
+using namespace t5;
+
+constexpr int kOcCta = 256;
+constexpr int kGroups = 4;
+constexpr int kDecodeWarps = 4 * kGroups;
+constexpr int kThreads = 32 * (2 + kDecodeWarps);
+constexpr int kBufs = 4;                // rounds in flight: A buffers in tensor memory = activation tiles in shared memory
+constexpr int kRawDepth = 4;            // packed tile rows in flight per group
+constexpr int kMaxTokens = 128;
+constexpr int kTmemCols = 512;
+
+struct Params {
+    const uint32_t *trellis;
+    __half *y;             // [tokens][ldy]
+    float *partial;        // [splitk][tokens][oc] fp32 when splitk > 1
+    int tokens, npad;      // npad: tokens rounded up to 16 (MMA N, TMA box rows)
+    int ic, oc, ldy, tiles_j, splitk;
+    int b_slot_bytes;      // npad * 128, rounded up to 1024
+    uint32_t one;
+};
+
+struct Barriers {
+    uint64_t raw_full[kGroups][kRawDepth], raw_empty[kGroups][kRawDepth];
+    uint64_t a_full[kBufs];      // all sixteen decode warps have stored their chunk of the round
+    uint64_t b_full[kBufs];      // the round's activation tile has landed
+    uint64_t empty[kBufs];       // the round's MMAs are done: A buffer and activation tile are free
+    uint64_t acc_full;
+    uint32_t tmem_base;
+};
+
+template <int K>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char *smem = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);
+    constexpr int kRawWords = 16 * 8 * K;                  // one tile row of the CTA's sixteen tiles
+    constexpr uint32_t kRawBytes = kRawWords * 4;
+    unsigned char *const smB = smem;
+    Barriers &S = *reinterpret_cast<Barriers *>(smB + (size_t)kBufs * P.b_slot_bytes);
+    uint32_t *const raw = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(&S) + 1024);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned *const status = &tc::g_tc_status;
+    // slice of the input dimension, in units of four tile rows (one per decode group)
+    const int units = P.ic / 64;
+    const int u0 = (int)((long long)blockIdx.y * units / P.splitk);
+    const int u1 = (int)((long long)(blockIdx.y + 1) * units / P.splitk);
+    const int r0 = 4 * u0;                 // first tile row
+    const int nper = u1 - u0;              // rounds = tile rows per group
+
+    if (threadIdx.x == 0) {
+        for (int g = 0; g < kGroups; ++g) {
+            for (int s = 0; s < kRawDepth; ++s) { mbar_init(s32(&S.raw_full[g][s]), 1); mbar_init(s32(&S.raw_empty[g][s]), 4); }
+        }
+        for (int s = 0; s < kBufs; ++s) { mbar_init(s32(&S.a_full[s]), kDecodeWarps); mbar_init(s32(&S.b_full[s]), 1); mbar_init(s32(&S.empty[s]), 1); }
+        mbar_init(s32(&S.acc_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(s32(&S.tmem_base), kTmemCols);
+    fence_before_sync();
+    __syncthreads();
+    fence_after_sync();
+    const uint32_t tmem = S.tmem_base;
+    const uint32_t d_x = tmem, d_y = tmem + (uint32_t)P.npad;
+    const uint32_t a_cols = tmem + 2u * (uint32_t)P.npad;       // A buffer b, group g: X at a_cols + 64 b + 16 g, Y 8 columns further
+
+    if (warp == 0) {
+        if (lane < kGroups) {
+            // ---------------- packed trellis of group `lane`: tile rows r0 + lane, r0 + lane + 4, ...
+            const int g = lane;
+            const uint32_t *src = P.trellis + ((size_t)(r0 + g) * P.tiles_j + (size_t)blockIdx.x * 16) * (size_t)(8 * K);
+            const size_t src_step = (size_t)4 * P.tiles_j * (8 * K);
+            bool ok = true;
+            Cursor rc(0, kRawDepth);
+            for (int s = 0; s < nper && ok; ++s, rc.advance(1)) {
+                if (rc.wrapped) ok = mbar_wait(s32(&S.raw_empty[g][rc.idx]), rc.phase ^ 1u, status, 100);
+                if (!ok) break;
+                const uint32_t bar = s32(&S.raw_full[g][rc.idx]);
+                mbar_expect_tx(bar, kRawBytes);
+                bulk_g2s(s32(raw + (size_t)(g * kRawDepth + rc.idx) * kRawWords), src + (size_t)s * src_step, kRawBytes, bar);
+            }
+        } else if (lane == kGroups) {
+            // ---------------- activation tiles: one per round (64 input channels)
+            const uint32_t box_bytes = (uint32_t)P.npad * 128u;
+            bool ok = true;
+            Cursor bc(0, kBufs);
+            for (int j = 0; j < nper && ok; ++j, bc.advance(1)) {
+                if (bc.wrapped) ok = mbar_wait(s32(&S.empty[bc.idx]), bc.phase ^ 1u, status, 100);
+                if (!ok) break;
+                const uint32_t bar = s32(&S.b_full[bc.idx]);
+                mbar_expect_tx(bar, box_bytes);
+                tma_2d(s32(smB + (size_t)bc.idx * P.b_slot_bytes), &xmap, 64 * (u0 + j), 0, bar);
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issue: per round eight MMAs (four tile rows x two accumulators), one commit
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc_f16(128, P.npad);
+            const uint64_t bdesc0 = umma_desc_sw128(s32(smB));      // activation tile 0; the others follow at b_slot_bytes
+            bool ok = true;
+            Cursor bc(0, kBufs);
+#ifdef EXL3_TC_TRACE
+            unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
+            const long long tc_begin = clock64();
+#endif
+            for (int s = 0; s < nper && ok; ++s, bc.advance(1)) {
+                TC_CLK(m0);
+                ok = mbar_wait(s32(&S.a_full[bc.idx]), bc.phase, status, 0);
+                TC_CLK(m1);
+                TC_ACC(0, m0, m1);
+                if (ok) ok = mbar_wait(s32(&S.b_full[bc.idx]), bc.phase, status, 0);
+                TC_CLK(m2);
+                TC_ACC(1, m1, m2);
+                if (!ok) break;
+                fence_after_sync();
+                const uint32_t a = a_cols + 64u * (uint32_t)bc.idx;
+                const uint64_t bk = bdesc0 + (uint64_t)((uint32_t)bc.idx * (uint32_t)P.b_slot_bytes >> 4);
+                // descriptor start addresses are in 16-byte units: tile row g of the round is 32 bytes further
+                umma_f16_ts(d_x, a, bk, idesc, s ? 1u : 0u);
+                umma_f16_ts(d_x, a + 16u, bk + 2u, idesc, 1u);
+                umma_f16_ts(d_x, a + 32u, bk + 4u, idesc, 1u);
+                umma_f16_ts(d_x, a + 48u, bk + 6u, idesc, 1u);
+                umma_f16_ts(d_y, a + 8u, bk, idesc, s ? 1u : 0u);
+                umma_f16_ts(d_y, a + 24u, bk + 2u, idesc, 1u);
+                umma_f16_ts(d_y, a + 40u, bk + 4u, idesc, 1u);
+                umma_f16_ts(d_y, a + 56u, bk + 6u, idesc, 1u);
+                umma_commit(s32(&S.empty[bc.idx]));
+                TC_CLK(m3);
+                TC_ACC(2, m2, m3);
+            }
+            umma_commit(s32(&S.acc_full));
+#ifdef EXL3_TC_TRACE
+            {
+                const int cta = blockIdx.x + gridDim.x * blockIdx.y;
+                if (cta < 4096) {
+                    for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][1][i] = tc_acc[i];
+                    tc::g_tc_trace[cta][1][4] = (unsigned long long)(clock64() - tc_begin);
+                }
+            }
+#endif
+        }
+    } else {
+        // ---------------- decode warps
+        const int dw = warp - 2;
+        const int g = dw >> 2;
+        const int quad = warp & 3;                 // TMEM lanes 32 quad .. +31 <-> tiles 4 quad .. +3 of the CTA's sixteen
+        const DecodeConsts dc(P.one);
+        const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
+        const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
+        bool ok = true;
+        Cursor rc(0, kRawDepth), ac(0, kBufs);
+#ifdef EXL3_TC_TRACE
+        unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
+        const long long tc_begin = clock64();
+#endif
+        for (int s = 0; s < nper && ok; ++s, rc.advance(1), ac.advance(1)) {
+            TC_CLK(c0);
+            ok = mbar_wait(s32(&S.raw_full[g][rc.idx]), rc.phase, status, 40);
+            TC_CLK(c1);
+            TC_ACC(0, c0, c1);
+            if (!ok) break;
+            uint32_t wd[K + 1];
+            load_words<K>(raw + (size_t)(g * kRawDepth + rc.idx) * kRawWords + quad * (32 * K) + lane * K, wd);
+            wd[K] = __shfl_sync(0xffffffffu, wd[0], nxt_lane);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s32(&S.raw_empty[g][rc.idx]));
+            uint32_t z[32];
+            decode_chunk_fast<K>(wd, z, dc);
+            // fp16 weights, two per register.  Fragment (a, b) = codewords z[8a + 4b ..+3]: output rows
+            // r and r+8 (codewords 0/2 and 1/3) at input channels 8b + q (0, 1) and 8b + 4 + q (2, 3).
+            // Register (a, b, row half) holds the two input channels of one row; the store puts b = 0, 1
+            // side by side, so column 2q + b of the row carries K elements 4q + 2b and 4q + 2b + 1.
+            uint32_t wreg[16];
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int hr = 0; hr < 2; ++hr)
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        const uint32_t z0 = z[8 * a + 4 * b + hr], z1 = z[8 * a + 4 * b + 2 + hr];
+                        const __half2 w0 = __hadd2(__low2half2(*reinterpret_cast<const __half2 *>(&z0)),
+                                                   __high2half2(*reinterpret_cast<const __half2 *>(&z0)));
+                        const __half2 w1 = __hadd2(__low2half2(*reinterpret_cast<const __half2 *>(&z1)),
+                                                   __high2half2(*reinterpret_cast<const __half2 *>(&z1)));
+                        const __half2 pk = __lows2half2(w0, w1);
+                        // order of the stores below: [a&1 selects the store][a>>1: X then Y][row half][b]
+                        wreg[8 * (a & 1) + 4 * (a >> 1) + 2 * hr + b] = *reinterpret_cast<const uint32_t *>(&pk);
+                    }
+            TC_CLK(c2);
+            TC_ACC(1, c1, c2);
+            if (ac.wrapped) ok = mbar_wait(s32(&S.empty[ac.idx]), ac.phase ^ 1u, status, 40);
+            TC_CLK(c3);
+            TC_ACC(2, c2, c3);
+            if (!ok) break;
+            fence_after_sync();
+            const uint32_t t0 = a_cols + lane_base + 64u * (uint32_t)ac.idx + 16u * (uint32_t)g;
+            tmem_st_16x256b_x2(t0, wreg[0], wreg[1], wreg[2], wreg[3], wreg[4], wreg[5], wreg[6], wreg[7]);
+            tmem_st_16x256b_x2(t0 + (16u << 16), wreg[8], wreg[9], wreg[10], wreg[11], wreg[12], wreg[13], wreg[14], wreg[15]);
+            tmem_wait_st();
+            fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s32(&S.a_full[ac.idx]));
+            TC_CLK(c4);
+            TC_ACC(3, c3, c4);
+        }
+#ifdef EXL3_TC_TRACE
+        if (lane == 0) {
+            const int cta = blockIdx.x + gridDim.x * blockIdx.y;
+            if (cta < 4096) {
+                for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][warp][i] = tc_acc[i];
+                tc::g_tc_trace[cta][warp][4] = (unsigned long long)(clock64() - tc_begin);
+            }
+        }
+#endif
+
+        // ---------------- epilogue: accumulators -> fp32 partial sums or fp16 outputs
+        ok = mbar_wait(s32(&S.acc_full), 0, status, 200) && ok;
+        fence_after_sync();
+        const int n16 = P.npad / 16;
+        const int i16 = lane & 15, gg = i16 & 7, hi8 = i16 >> 3;
+        for (int o = g; o < 2 * n16; o += kGroups) {
+            const int R = o / n16, c0 = (o - R * n16) * 16;
+            uint32_t v[16];
+            tmem_ld_32x32b_x16(tmem + lane_base + (uint32_t)(R * P.npad + c0), v);
+            const int a = 2 * R + (lane >> 4);
+            const int oc_idx = blockIdx.x * kOcCta + 64 * quad + 16 * (gg >> 1) + 4 * a + 2 * hi8 + (gg & 1);
+            if (ok) {
+#pragma unroll
+                for (int j = 0; j < 16; ++j) {
+                    const int tok = c0 + j;
+                    if (tok < P.tokens) {
+                        if (P.splitk > 1)
+                            P.partial[((size_t)blockIdx.y * P.tokens + tok) * P.oc + oc_idx] = __uint_as_float(v[j]);
+                        else
+                            P.y[(size_t)tok * P.ldy + oc_idx] = __float2half_rn(__uint_as_float(v[j]));
+                    }
+                }
+            }
+        }
+    }
+
+    fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        fence_after_sync();
+        tmem_dealloc(tmem, kTmemCols);
+    }
+}
+
+template <int K>
+static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
+    const size_t raw = (size_t)kGroups * kRawDepth * (16 * 8 * K) * 4;
+    const size_t smem = (size_t)kBufs * P.b_slot_bytes + 1024 /*barriers*/ + raw + 1024 /*alignment*/;
+    if (smem > 226 * 1024) return EXL3_E_SHAPE;
+    if (cudaFuncSetAttribute(gemm_ts_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    dim3 grid(P.oc / kOcCta, P.splitk);
+    gemm_ts_kernel<K><<<grid, kThreads, smem, st>>>(map, P);
+    return launch_status();
+}
+
+// the shapes this path takes; everything else stays on the shared-memory kernel
+static bool eligible(int rows, int ic, int oc) { return rows <= kMaxTokens && (oc % kOcCta) == 0 && (ic % 128) == 0; }
+
+static int choose_splitk(int ic, int oc) {
+    const int ctas = oc / kOcCta, units = ic / 64;
+    int sk = (148 + ctas / 2) / ctas;
+    if (sk > units / 4) sk = units / 4;
+    return sk < 1 ? 1 : sk;
+}
+static size_t xh_bytes(int rows, int ic) { return (((size_t)rows * ic * 2) + 255) & ~(size_t)255; }
+static size_t scratch_bytes(int rows, int ic, int oc) {
+    const int sk = choose_splitk(ic, oc);
+    return xh_bytes(rows, ic) + (sk > 1 ? (size_t)sk * rows * oc * 4 : 0);
+}
+
+}  // namespace ts
+}  // namespace exl3

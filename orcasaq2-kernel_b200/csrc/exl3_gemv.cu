@@ -125,6 +125,27 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t *a, uint3
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
+// Phase timestamps of every CTA (start, after the dependency wait, activations landed, main loop
+// done, partial sums stored, ticket taken, end), compiled in only for timing studies.
+#ifdef EXL3_GEMV_TRACE
+__device__ unsigned long long g_gemv_trace[8192][8];
+#define EXL3_TRACE(slot)                                                                       \
+    do {                                                                                       \
+        if (threadIdx.x == 0) {                                                                \
+            unsigned long long t_;                                                             \
+            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                             \
+            g_gemv_trace[blockIdx.x][slot] = t_;                                               \
+            if (slot == 0) {                                                                   \
+                unsigned sm_;                                                                  \
+                asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));                               \
+                g_gemv_trace[blockIdx.x][7] = sm_;                                             \
+            }                                                                                  \
+        }                                                                                      \
+    } while (0)
+#else
+#define EXL3_TRACE(slot) do { } while (0)
+#endif
+
 // ---------------------------------------------------------------------------------------------
 template <int K, int NT>
 __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev &S, int local,
@@ -139,6 +160,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     const int g = lane >> 2, q = lane & 3;
     const int NB = P.nb;
     const DecodeConsts dc(P.one);
+    EXL3_TRACE(0);
 
     const int ob = local / S.splitk, ks = local - ob * S.splitk;
     const int kb0 = (int)((long long)ks * P.kblocks / S.splitk);
@@ -199,6 +221,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     // finish, and let the grid after this one begin its own weight prefetch.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
+    EXL3_TRACE(1);
 
     for (int b0 = 0; b0 < nblk; b0 += sub_max) {
         const int nb_sub = min(sub_max, nblk - b0);
@@ -211,6 +234,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         }
         ok = mbar_wait(xbar, xphase, P.status) && ok;
         xphase ^= 1u;
+        if (b0 == 0) EXL3_TRACE(2);
 
         // ---- stream, decode, multiply
         const uint32_t *xfp = xf_lane;
@@ -255,6 +279,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         }
     }
     __syncthreads();   // every warp is done with its ring: the region is reused below
+    EXL3_TRACE(3);
 
     // ---- reduce the eight warps
     float *red = reinterpret_cast<float *>(region);                  // [8][NT*8][128]
@@ -287,6 +312,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
     }
 
+    EXL3_TRACE(4);
     if (S.splitk > 1) {
         __shared__ unsigned s_last;
         __threadfence();
@@ -297,6 +323,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             if (s_last) P.tickets[unit] = 0u;   // ready for the next launch
         }
         __syncthreads();
+        EXL3_TRACE(5);
         if (!s_last) return;
         __threadfence();
         for (int n = tid >> 7; n < P.rows; n += 2) {
@@ -340,6 +367,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         o.y = *reinterpret_cast<const uint32_t *>(&o23);
         *reinterpret_cast<uint2 *>(P.y + (size_t)n * P.ldy + ocol) = o;
     }
+    EXL3_TRACE(6);
 }
 
 // Pre-pass: H128(x * suh) of every shard, rounded to fp16 once, written in the order the GEMV's

@@ -31,7 +31,22 @@ def test_gemm_tc_vs_oracle(ext, coracle, K, rows, ic, oc):
     assert rel <= MAX_REL_ERR and cos >= MIN_COSINE, (rel, cos)
 
 
+@pytest.mark.parametrize("K", [1, 2, 3, 4, 5, 6, 7, 8])
+@pytest.mark.parametrize("rows,ic,oc", [(1, 128, 256), (17, 256, 256), (32, 512, 512), (100, 384, 256), (128, 1024, 768)])
+def test_gemm_tmem_operand_path_vs_oracle(ext, coracle, K, rows, ic, oc):
+    """Up to 128 rows and a multiple of 256 output channels: the kernel that stores the decoded
+    codewords into tensor memory and reads them as the A operand of tcgen05.mma."""
+    tr, suh, svh, x, y = _run(ext, ic, oc, K, rows, 31 * K + rows)
+    w = coracle.reconstruct(tr.numpy())
+    ref = coracle.layer(x.numpy(), w, suh.numpy(), svh.numpy())
+    got = y.float().cpu().numpy().astype(np.float64)
+    rel = np.abs(got - ref).max() / np.abs(ref).max()
+    cos = float((got * ref).sum() / np.linalg.norm(got) / np.linalg.norm(ref))
+    assert rel <= MAX_REL_ERR and cos >= MIN_COSINE, (rel, cos)
+
+
 @pytest.mark.parametrize("rows,ic,oc,K,dtype", [
+    (32, 5120, 1024, 3, torch.float16), (64, 17408, 512, 4, torch.bfloat16), (128, 2048, 5120, 5, torch.float16),
     (512, 5120, 1024, 3, torch.bfloat16), (700, 2048, 5120, 4, torch.float16), (2048, 1024, 2048, 4, torch.bfloat16),
 ])
 def test_gemm_tc_vs_reconstruct_route(ext, rows, ic, oc, K, dtype):
