@@ -422,6 +422,10 @@ template <bool BF16>
 __global__ void __launch_bounds__(256)
 xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __half *__restrict__ xh,
                   long long nblocks, int blocks_per_row) {
+    // no-ops unless launched with programmatic stream serialization: x and the scratch may still be
+    // in use by the kernels before this one
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (wid >= nblocks) return;
@@ -454,6 +458,8 @@ xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __
 __global__ void __launch_bounds__(256)
 reduce_had_kernel(const float *__restrict__ partial, int splitk, const __half *__restrict__ svh,
                   __half *__restrict__ y, long long nblocks, int blocks_per_row, size_t slice_elems) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     const int lane = threadIdx.x & 31;
     const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (wid >= nblocks) return;
@@ -583,17 +589,20 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
         const int sk = ts::choose_splitk(ic, oc);
         const long long nblocks = (long long)rows * (ic / 128);
         const unsigned g1 = (unsigned)((nblocks + 7) / 8);
-        if (x_is_bf16)
-            xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(scratch), nblocks, ic / 128);
-        else
-            xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(scratch), nblocks, ic / 128);
-        if (cudaGetLastError() != cudaSuccess) return EXL3_E_LAUNCH;
+        const cudaError_t e1 =
+            x_is_bf16 ? launch_pdl(xh_permute_kernel<true>, dim3(g1), dim3(256), 0, st, x, static_cast<const __half *>(suh),
+                                   static_cast<__half *>(scratch), nblocks, ic / 128)
+                      : launch_pdl(xh_permute_kernel<false>, dim3(g1), dim3(256), 0, st, x, static_cast<const __half *>(suh),
+                                   static_cast<__half *>(scratch), nblocks, ic / 128);
+        if (e1 != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
         ts::Params P;
         P.trellis = static_cast<const uint32_t *>(trellis);
         P.y = static_cast<__half *>(y);
         P.tokens = rows; P.npad = (rows + 15) & ~15;
         P.ic = ic; P.oc = oc; P.ldy = oc; P.tiles_j = oc / 16; P.splitk = sk; P.one = 1u;
         P.b_slot_bytes = (P.npad * 128 + 1023) & ~1023;
+        P.bufs = (ts::kTmemCols - 2 * P.npad) / 64;
+        if (P.bufs > ts::kMaxBufs) P.bufs = ts::kMaxBufs;
         P.partial = sk > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + ts::xh_bytes(rows, ic)) : nullptr;
         CUtensorMap map;
         const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
@@ -617,9 +626,12 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
         if (rc != EXL3_OK) return rc;
         if (sk == 1) return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
         const long long nb = (long long)rows * (oc / 128);
-        reduce_had_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(P.partial, sk, static_cast<const __half *>(svh),
-                                                                   static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc);
-        return launch_status();
+        if (launch_pdl(reduce_had_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, st, (const float *)P.partial, sk,
+                       static_cast<const __half *>(svh), static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc) != cudaSuccess) {
+            cudaGetLastError();
+            return EXL3_E_LAUNCH;
+        }
+        return EXL3_OK;
     }
     const int splitk = choose_splitk(rows, ic, oc);
 

@@ -12,18 +12,19 @@
 //
 // Issuing a tcgen05 instruction costs the issuing thread about 55 cycles (measured), so the loop
 // is organised to need few of them: a ROUND is four tile rows (64 input channels, one tile row per
-// decode group), and costs one fence, eight MMAs and one commit.
+// decode group), and costs each of the two issuing threads one wait, one fence, four MMAs and one commit.
 //
 // CTA = 256 output channels x a slice of the input channels x up to 128 tokens, one CTA per SM:
 //   warp 0        lanes 0..3: packed trellis of the four decode groups (1-D bulk copies into
 //                 per-group rings); lane 4: activation tiles (2-D tiled TMA, 128-byte swizzle), one
 //                 per round
-//   warp 1        allocates tensor memory, issues tcgen05.mma (one lane), commits to mbarriers
+//   warps 1, 18   issue tcgen05.mma (one lane each: accumulator X and accumulator Y) and commit to
+//                 mbarriers; warp 1 also allocates and frees the tensor memory
 //   warps 2..17   four decode groups of four warps (one warp per TMEM lane quarter = 64 output
 //                 channels); group g takes the tile rows g, g+4, ... of the slice; afterwards the
 //                 epilogue (tcgen05.ld, fp32 partial sums or fp16 outputs)
 // Tensor memory: accumulators X and Y (rows a = 0,1 and a = 2,3 of every four-tile span) in columns
-// [0, 2 npad), then kBufs A buffers of 64 columns (16 per group: 8 for X, 8 for Y).
+// [0, 2 npad), then 4 .. 7 A buffers of 64 columns (16 per group: 8 for X, 8 for Y).
 // The K order inside a tile row is k = 4 (ic & 3) + 2 (ic >> 3) + ((ic >> 2) & 1), the order in which
 // a lane's registers hold it; the activation pre-pass writes the same order.
 // Every wait is bounded; a wait that runs out sets the status word and the kernel still frees its
@@ -38,9 +39,14 @@ using namespace t5;
 constexpr int kOcCta = 256;
 constexpr int kGroups = 4;
 constexpr int kDecodeWarps = 4 * kGroups;
-constexpr int kThreads = 32 * (2 + kDecodeWarps);
-constexpr int kBufs = 4;                // rounds in flight: A buffers in tensor memory = activation tiles in shared memory
-constexpr int kRawDepth = 4;            // packed tile rows in flight per group
+constexpr int kThreads = 32 * (3 + kDecodeWarps);   // + trellis/activation producer, two MMA issuers
+constexpr int kWarpMmaY = 2 + kDecodeWarps;         // warp 1 issues for accumulator X, this one for Y
+constexpr int kMaxBufs = 7;             // rounds in flight (A buffers in tensor memory = activation tiles in shared
+                                        // memory): as many as the 512 columns allow, (512 - 2 npad) / 64
+// Packed tile rows in flight per group: about 12 KB per group (48 KB per SM) keeps the stream ahead of
+// the decode warps; a tile row of the CTA's sixteen tiles is 512 K bytes.
+__host__ __device__ constexpr int raw_depth(int K) { return K <= 2 ? 12 : K == 3 ? 8 : K == 4 ? 6 : K == 5 ? 5 : 4; }
+constexpr int kMaxRawDepth = 12;
 constexpr int kMaxTokens = 128;
 constexpr int kTmemCols = 512;
 
@@ -51,14 +57,15 @@ struct Params {
     int tokens, npad;      // npad: tokens rounded up to 16 (MMA N, TMA box rows)
     int ic, oc, ldy, tiles_j, splitk;
     int b_slot_bytes;      // npad * 128, rounded up to 1024
+    int bufs;              // rounds in flight, 4 .. kMaxBufs
     uint32_t one;
 };
 
 struct Barriers {
-    uint64_t raw_full[kGroups][kRawDepth], raw_empty[kGroups][kRawDepth];
-    uint64_t a_full[kBufs];      // all sixteen decode warps have stored their chunk of the round
-    uint64_t b_full[kBufs];      // the round's activation tile has landed
-    uint64_t empty[kBufs];       // the round's MMAs are done: A buffer and activation tile are free
+    uint64_t raw_full[kGroups][kMaxRawDepth], raw_empty[kGroups][kMaxRawDepth];
+    uint64_t full[kMaxBufs];        // all sixteen decode warps have stored their chunk of the round AND its
+                                    // activation tile has landed (sixteen arrivals + the producer's, with the bytes)
+    uint64_t empty[kMaxBufs];       // both issuers' MMAs of the round are done: A buffer and activation tile are free
     uint64_t acc_full;
     uint32_t tmem_base;
 };
@@ -70,8 +77,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     unsigned char *smem = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);
     constexpr int kRawWords = 16 * 8 * K;                  // one tile row of the CTA's sixteen tiles
     constexpr uint32_t kRawBytes = kRawWords * 4;
+    constexpr int kRawDepth = raw_depth(K);
     unsigned char *const smB = smem;
-    Barriers &S = *reinterpret_cast<Barriers *>(smB + (size_t)kBufs * P.b_slot_bytes);
+    Barriers &S = *reinterpret_cast<Barriers *>(smB + (size_t)P.bufs * P.b_slot_bytes);
     uint32_t *const raw = reinterpret_cast<uint32_t *>(reinterpret_cast<unsigned char *>(&S) + 1024);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -87,8 +95,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         for (int g = 0; g < kGroups; ++g) {
             for (int s = 0; s < kRawDepth; ++s) { mbar_init(s32(&S.raw_full[g][s]), 1); mbar_init(s32(&S.raw_empty[g][s]), 4); }
         }
-        for (int s = 0; s < kBufs; ++s) { mbar_init(s32(&S.a_full[s]), kDecodeWarps); mbar_init(s32(&S.b_full[s]), 1); mbar_init(s32(&S.empty[s]), 1); }
-        mbar_init(s32(&S.acc_full), 1);
+        for (int s = 0; s < P.bufs; ++s) { mbar_init(s32(&S.full[s]), kDecodeWarps + 1); mbar_init(s32(&S.empty[s]), 2); }
+        mbar_init(s32(&S.acc_full), 2);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -98,6 +106,9 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     fence_after_sync();
     const uint32_t tmem = S.tmem_base;
     const uint32_t d_x = tmem, d_y = tmem + (uint32_t)P.npad;
+    // Everything above touched only this CTA's own state; the packed trellis is constant.  Whoever
+    // reads the rotated activations or writes results waits for the kernels before this one first.
+    asm volatile("griddepcontrol.launch_dependents;");
     const uint32_t a_cols = tmem + 2u * (uint32_t)P.npad;       // A buffer b, group g: X at a_cols + 64 b + 16 g, Y 8 columns further
 
     if (warp == 0) {
@@ -109,7 +120,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             bool ok = true;
             Cursor rc(0, kRawDepth);
             for (int s = 0; s < nper && ok; ++s, rc.advance(1)) {
-                if (rc.wrapped) ok = mbar_wait(s32(&S.raw_empty[g][rc.idx]), rc.phase ^ 1u, status, 100);
+                if (rc.wrapped) ok = mbar_wait(s32(&S.raw_empty[g][rc.idx]), rc.phase ^ 1u, status, 40);
                 if (!ok) break;
                 const uint32_t bar = s32(&S.raw_full[g][rc.idx]);
                 mbar_expect_tx(bar, kRawBytes);
@@ -118,55 +129,51 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         } else if (lane == kGroups) {
             // ---------------- activation tiles: one per round (64 input channels)
             const uint32_t box_bytes = (uint32_t)P.npad * 128u;
+            asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
-            Cursor bc(0, kBufs);
+            Cursor bc(0, P.bufs);
             for (int j = 0; j < nper && ok; ++j, bc.advance(1)) {
                 if (bc.wrapped) ok = mbar_wait(s32(&S.empty[bc.idx]), bc.phase ^ 1u, status, 100);
                 if (!ok) break;
-                const uint32_t bar = s32(&S.b_full[bc.idx]);
+                const uint32_t bar = s32(&S.full[bc.idx]);
                 mbar_expect_tx(bar, box_bytes);
                 tma_2d(s32(smB + (size_t)bc.idx * P.b_slot_bytes), &xmap, 64 * (u0 + j), 0, bar);
             }
         }
-    } else if (warp == 1) {
-        // ---------------- MMA issue: per round eight MMAs (four tile rows x two accumulators), one commit
+    } else if (warp == 1 || warp == kWarpMmaY) {
+        // ---------------- MMA issue: per round four MMAs (four tile rows) into this issuer's accumulator, one commit
         if (lane == 0) {
             const uint32_t idesc = umma_idesc_f16(128, P.npad);
             const uint64_t bdesc0 = umma_desc_sw128(s32(smB));      // activation tile 0; the others follow at b_slot_bytes
+            const uint32_t d_acc = warp == 1 ? d_x : d_y;
+            const uint32_t a_off = warp == 1 ? 0u : 8u;
             bool ok = true;
-            Cursor bc(0, kBufs);
+            Cursor bc(0, P.bufs);
 #ifdef EXL3_TC_TRACE
             unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
             const long long tc_begin = clock64();
 #endif
             for (int s = 0; s < nper && ok; ++s, bc.advance(1)) {
                 TC_CLK(m0);
-                ok = mbar_wait(s32(&S.a_full[bc.idx]), bc.phase, status, 0);
+                ok = mbar_wait(s32(&S.full[bc.idx]), bc.phase, status, 0);
                 TC_CLK(m1);
                 TC_ACC(0, m0, m1);
-                if (ok) ok = mbar_wait(s32(&S.b_full[bc.idx]), bc.phase, status, 0);
-                TC_CLK(m2);
-                TC_ACC(1, m1, m2);
                 if (!ok) break;
                 fence_after_sync();
-                const uint32_t a = a_cols + 64u * (uint32_t)bc.idx;
-                const uint64_t bk = bdesc0 + (uint64_t)((uint32_t)bc.idx * (uint32_t)P.b_slot_bytes >> 4);
+                const uint32_t a = a_cols + 64u * (uint32_t)bc.idx + a_off;
                 // descriptor start addresses are in 16-byte units: tile row g of the round is 32 bytes further
-                umma_f16_ts(d_x, a, bk, idesc, s ? 1u : 0u);
-                umma_f16_ts(d_x, a + 16u, bk + 2u, idesc, 1u);
-                umma_f16_ts(d_x, a + 32u, bk + 4u, idesc, 1u);
-                umma_f16_ts(d_x, a + 48u, bk + 6u, idesc, 1u);
-                umma_f16_ts(d_y, a + 8u, bk, idesc, s ? 1u : 0u);
-                umma_f16_ts(d_y, a + 24u, bk + 2u, idesc, 1u);
-                umma_f16_ts(d_y, a + 40u, bk + 4u, idesc, 1u);
-                umma_f16_ts(d_y, a + 56u, bk + 6u, idesc, 1u);
+                const uint64_t bk = bdesc0 + (uint64_t)((uint32_t)bc.idx * (uint32_t)P.b_slot_bytes >> 4);
+                umma_f16_ts(d_acc, a, bk, idesc, s ? 1u : 0u);
+                umma_f16_ts(d_acc, a + 16u, bk + 2u, idesc, 1u);
+                umma_f16_ts(d_acc, a + 32u, bk + 4u, idesc, 1u);
+                umma_f16_ts(d_acc, a + 48u, bk + 6u, idesc, 1u);
                 umma_commit(s32(&S.empty[bc.idx]));
                 TC_CLK(m3);
-                TC_ACC(2, m2, m3);
+                TC_ACC(2, m1, m3);
             }
             umma_commit(s32(&S.acc_full));
 #ifdef EXL3_TC_TRACE
-            {
+            if (warp == 1) {
                 const int cta = blockIdx.x + gridDim.x * blockIdx.y;
                 if (cta < 4096) {
                     for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][1][i] = tc_acc[i];
@@ -184,7 +191,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
         const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
         bool ok = true;
-        Cursor rc(0, kRawDepth), ac(0, kBufs);
+        Cursor rc(0, kRawDepth), ac(0, P.bufs);
 #ifdef EXL3_TC_TRACE
         unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
         const long long tc_begin = clock64();
@@ -235,7 +242,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             tmem_wait_st();
             fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(s32(&S.a_full[ac.idx]));
+            if (lane == 0) mbar_arrive(s32(&S.full[ac.idx]));
             TC_CLK(c4);
             TC_ACC(3, c3, c4);
         }
@@ -252,6 +259,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         // ---------------- epilogue: accumulators -> fp32 partial sums or fp16 outputs
         ok = mbar_wait(s32(&S.acc_full), 0, status, 200) && ok;
         fence_after_sync();
+        asm volatile("griddepcontrol.wait;" ::: "memory");
         const int n16 = P.npad / 16;
         const int i16 = lane & 15, gg = i16 & 7, hi8 = i16 >> 3;
         for (int o = g; o < 2 * n16; o += kGroups) {
@@ -285,16 +293,19 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
 
 template <int K>
 static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
-    const size_t raw = (size_t)kGroups * kRawDepth * (16 * 8 * K) * 4;
-    const size_t smem = (size_t)kBufs * P.b_slot_bytes + 1024 /*barriers*/ + raw + 1024 /*alignment*/;
+    const size_t raw = (size_t)kGroups * raw_depth(K) * (16 * 8 * K) * 4;
+    const size_t smem = (size_t)P.bufs * P.b_slot_bytes + 1024 /*barriers*/ + raw + 1024 /*alignment*/;
     if (smem > 226 * 1024) return EXL3_E_SHAPE;
     if (cudaFuncSetAttribute(gemm_ts_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
     }
     dim3 grid(P.oc / kOcCta, P.splitk);
-    gemm_ts_kernel<K><<<grid, kThreads, smem, st>>>(map, P);
-    return launch_status();
+    if (launch_pdl(gemm_ts_kernel<K>, grid, dim3(kThreads), smem, st, map, P) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    return EXL3_OK;
 }
 
 // the shapes this path takes; everything else stays on the shared-memory kernel
