@@ -16,8 +16,8 @@
 //
 // CTA = 256 output channels x a slice of the input channels x up to 128 tokens, one CTA per SM:
 //   warp 0        lanes 0..3: packed trellis of the four decode groups (1-D bulk copies into
-//                 per-group rings); lane 4: activation tiles (2-D tiled TMA, 128-byte swizzle), one
-//                 per round
+//                 per-group rings)
+//   warp 19       activation tiles (2-D tiled TMA, 128-byte swizzle), one per round
 //   warps 1, 18   issue tcgen05.mma (one lane each: accumulator X and accumulator Y) and commit to
 //                 mbarriers; warp 1 also allocates and frees the tensor memory
 //   warps 2..17   four decode groups of four warps (one warp per TMEM lane quarter = 64 output
@@ -39,8 +39,9 @@ using namespace t5;
 constexpr int kOcCta = 256;
 constexpr int kGroups = 4;
 constexpr int kDecodeWarps = 4 * kGroups;
-constexpr int kThreads = 32 * (3 + kDecodeWarps);   // + trellis/activation producer, two MMA issuers
+constexpr int kThreads = 32 * (4 + kDecodeWarps);   // + trellis producer, activation producer, two MMA issuers
 constexpr int kWarpMmaY = 2 + kDecodeWarps;         // warp 1 issues for accumulator X, this one for Y
+constexpr int kWarpActs = 3 + kDecodeWarps;         // activation tiles
 constexpr int kMaxBufs = 7;             // rounds in flight (A buffers in tensor memory = activation tiles in shared
                                         // memory): as many as the 512 columns allow, (512 - 2 npad) / 64
 // Packed tile rows in flight per group: about 12 KB per group (48 KB per SM) keeps the stream ahead of
@@ -69,6 +70,32 @@ struct Barriers {
     uint64_t acc_full;
     uint32_t tmem_base;
 };
+
+// One chunk: packed words -> 3INST codewords -> fp16 weights, two per register, in the order of the two
+// tensor-memory stores.  Fragment (a, b) = codewords z[8a + 4b ..+3]: output rows r and r+8 (codewords
+// 0/2 and 1/3) at input channels 8b + q (0, 1) and 8b + 4 + q (2, 3).  Register (a, b, row half) holds
+// the two input channels of one row; the store puts b = 0, 1 side by side, so column 2q + b of the row
+// carries K elements 4q + 2b and 4q + 2b + 1.
+template <int K>
+__device__ __forceinline__ void decode_pack(const uint32_t (&wd)[K + 1], uint32_t (&wreg)[16], const DecodeConsts &dc) {
+    uint32_t z[32];
+    decode_chunk_fast<K>(wd, z, dc);
+#pragma unroll
+    for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int hr = 0; hr < 2; ++hr)
+#pragma unroll
+            for (int b = 0; b < 2; ++b) {
+                const uint32_t z0 = z[8 * a + 4 * b + hr], z1 = z[8 * a + 4 * b + 2 + hr];
+                const __half2 w0 = __hadd2(__low2half2(*reinterpret_cast<const __half2 *>(&z0)),
+                                           __high2half2(*reinterpret_cast<const __half2 *>(&z0)));
+                const __half2 w1 = __hadd2(__low2half2(*reinterpret_cast<const __half2 *>(&z1)),
+                                           __high2half2(*reinterpret_cast<const __half2 *>(&z1)));
+                const __half2 pk = __lows2half2(w0, w1);
+                // [a & 1 selects the store][a >> 1: accumulator X then Y][row half][b]
+                wreg[8 * (a & 1) + 4 * (a >> 1) + 2 * hr + b] = *reinterpret_cast<const uint32_t *>(&pk);
+            }
+}
 
 template <int K>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -112,22 +139,29 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     const uint32_t a_cols = tmem + 2u * (uint32_t)P.npad;       // A buffer b, group g: X at a_cols + 64 b + 16 g, Y 8 columns further
 
     if (warp == 0) {
-        if (lane < kGroups) {
-            // ---------------- packed trellis of group `lane`: tile rows r0 + lane, r0 + lane + 4, ...
-            const int g = lane;
-            const uint32_t *src = P.trellis + ((size_t)(r0 + g) * P.tiles_j + (size_t)blockIdx.x * 16) * (size_t)(8 * K);
-            const size_t src_step = (size_t)4 * P.tiles_j * (8 * K);
-            bool ok = true;
-            Cursor rc(0, kRawDepth);
-            for (int s = 0; s < nper && ok; ++s, rc.advance(1)) {
-                if (rc.wrapped) ok = mbar_wait(s32(&S.raw_empty[g][rc.idx]), rc.phase ^ 1u, status, 40);
-                if (!ok) break;
+        // ---------------- packed trellis: lane g feeds decode group g (tile rows r0 + g, r0 + g + 4, ...).
+        // The four lanes stay in ONE loop and issue their copies with one instruction: issuing a bulk
+        // copy holds the warp for about a quarter of a microsecond, and four diverged lanes would pay it
+        // four times per round (measured: that alone bounded the kernel at ~1500 cycles per round).
+        const int g = lane & 3;
+        const uint32_t *src = P.trellis + ((size_t)(r0 + g) * P.tiles_j + (size_t)blockIdx.x * 16) * (size_t)(8 * K);
+        const size_t src_step = (size_t)4 * P.tiles_j * (8 * K);
+        bool ok = true;
+        Cursor rc(0, kRawDepth);
+        for (int s = 0; s < nper; ++s, rc.advance(1)) {
+            if (lane < kGroups && rc.wrapped) ok = mbar_wait(s32(&S.raw_empty[g][rc.idx]), rc.phase ^ 1u, status, 40);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane < kGroups) {
                 const uint32_t bar = s32(&S.raw_full[g][rc.idx]);
                 mbar_expect_tx(bar, kRawBytes);
                 bulk_g2s(s32(raw + (size_t)(g * kRawDepth + rc.idx) * kRawWords), src + (size_t)s * src_step, kRawBytes, bar);
             }
-        } else if (lane == kGroups) {
-            // ---------------- activation tiles: one per round (64 input channels)
+        }
+    } else if (warp == kWarpActs) {
+        // ---------------- activation tiles: one per round (64 input channels), a warp of its own so that
+        // its waits do not hold back the trellis stream
+        if (lane == 0) {
             const uint32_t box_bytes = (uint32_t)P.npad * 128u;
             asm volatile("griddepcontrol.wait;" ::: "memory");
             bool ok = true;
@@ -196,56 +230,83 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
         const long long tc_begin = clock64();
 #endif
-        for (int s = 0; s < nper && ok; ++s, rc.advance(1), ac.advance(1)) {
+        // Two rounds per iteration: the sixteen decode warps move in lock step (a round's MMAs need all of
+        // them), so within one warp the barrier polls, shared-memory loads, shuffles and tensor-memory
+        // stores of a single chunk are a chain of exposed latencies.  Two independent chunks halve them.
+        // The completion of a pair's stores is awaited, and announced, after the next pair is decoded.
+        int pending[2] = {-1, -1};
+        auto announce = [&]() {
+            if (pending[0] >= 0) {
+                tmem_wait_st();
+                fence_before_sync();
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(s32(&S.full[pending[0]]));
+                    if (pending[1] >= 0) mbar_arrive(s32(&S.full[pending[1]]));
+                }
+                pending[0] = pending[1] = -1;
+            }
+        };
+        for (int s = 0; s < nper && ok; s += 2) {
+            const bool two = s + 1 < nper;
             TC_CLK(c0);
-            ok = mbar_wait(s32(&S.raw_full[g][rc.idx]), rc.phase, status, 40);
+            const int ri0 = rc.idx;
+            const uint32_t rp0 = rc.phase;
+            rc.advance(1);
+            const int ri1 = rc.idx;
+            const uint32_t rp1 = rc.phase;
+            if (two) rc.advance(1);
+            ok = mbar_wait(s32(&S.raw_full[g][ri0]), rp0, status, 40);
+            if (ok && two) ok = mbar_wait(s32(&S.raw_full[g][ri1]), rp1, status, 40);
             TC_CLK(c1);
             TC_ACC(0, c0, c1);
             if (!ok) break;
-            uint32_t wd[K + 1];
-            load_words<K>(raw + (size_t)(g * kRawDepth + rc.idx) * kRawWords + quad * (32 * K) + lane * K, wd);
-            wd[K] = __shfl_sync(0xffffffffu, wd[0], nxt_lane);
+            uint32_t wd0[K + 1], wd1[K + 1];
+            const uint32_t *wsrc = raw + (size_t)(g * kRawDepth) * kRawWords + quad * (32 * K) + lane * K;
+            load_words<K>(wsrc + (size_t)ri0 * kRawWords, wd0);
+            if (two) load_words<K>(wsrc + (size_t)ri1 * kRawWords, wd1);
+            else {
+#pragma unroll
+                for (int k = 0; k < K; ++k) wd1[k] = 0u;
+            }
+            wd0[K] = __shfl_sync(0xffffffffu, wd0[0], nxt_lane);
+            wd1[K] = __shfl_sync(0xffffffffu, wd1[0], nxt_lane);
             __syncwarp();
-            if (lane == 0) mbar_arrive(s32(&S.raw_empty[g][rc.idx]));
-            uint32_t z[32];
-            decode_chunk_fast<K>(wd, z, dc);
-            // fp16 weights, two per register.  Fragment (a, b) = codewords z[8a + 4b ..+3]: output rows
-            // r and r+8 (codewords 0/2 and 1/3) at input channels 8b + q (0, 1) and 8b + 4 + q (2, 3).
-            // Register (a, b, row half) holds the two input channels of one row; the store puts b = 0, 1
-            // side by side, so column 2q + b of the row carries K elements 4q + 2b and 4q + 2b + 1.
-            uint32_t wreg[16];
-#pragma unroll
-            for (int a = 0; a < 4; ++a)
-#pragma unroll
-                for (int hr = 0; hr < 2; ++hr)
-#pragma unroll
-                    for (int b = 0; b < 2; ++b) {
-                        const uint32_t z0 = z[8 * a + 4 * b + hr], z1 = z[8 * a + 4 * b + 2 + hr];
-                        const __half2 w0 = __hadd2(__low2half2(*reinterpret_cast<const __half2 *>(&z0)),
-                                                   __high2half2(*reinterpret_cast<const __half2 *>(&z0)));
-                        const __half2 w1 = __hadd2(__low2half2(*reinterpret_cast<const __half2 *>(&z1)),
-                                                   __high2half2(*reinterpret_cast<const __half2 *>(&z1)));
-                        const __half2 pk = __lows2half2(w0, w1);
-                        // order of the stores below: [a&1 selects the store][a>>1: X then Y][row half][b]
-                        wreg[8 * (a & 1) + 4 * (a >> 1) + 2 * hr + b] = *reinterpret_cast<const uint32_t *>(&pk);
-                    }
+            if (lane == 0) {
+                mbar_arrive(s32(&S.raw_empty[g][ri0]));
+                if (two) mbar_arrive(s32(&S.raw_empty[g][ri1]));
+            }
+            uint32_t wreg0[16], wreg1[16];
+            decode_pack<K>(wd0, wreg0, dc);
+            if (two) decode_pack<K>(wd1, wreg1, dc);
             TC_CLK(c2);
             TC_ACC(1, c1, c2);
-            if (ac.wrapped) ok = mbar_wait(s32(&S.empty[ac.idx]), ac.phase ^ 1u, status, 40);
+            announce();                            // the previous pair's stores have had two decodes to land
+            const int ai0 = ac.idx;
+            if (ac.wrapped) ok = mbar_wait(s32(&S.empty[ai0]), ac.phase ^ 1u, status, 40);
+            ac.advance(1);
+            const int ai1 = ac.idx;
+            if (two) {
+                if (ok && ac.wrapped) ok = mbar_wait(s32(&S.empty[ai1]), ac.phase ^ 1u, status, 40);
+                ac.advance(1);
+            }
             TC_CLK(c3);
             TC_ACC(2, c2, c3);
             if (!ok) break;
             fence_after_sync();
-            const uint32_t t0 = a_cols + lane_base + 64u * (uint32_t)ac.idx + 16u * (uint32_t)g;
-            tmem_st_16x256b_x2(t0, wreg[0], wreg[1], wreg[2], wreg[3], wreg[4], wreg[5], wreg[6], wreg[7]);
-            tmem_st_16x256b_x2(t0 + (16u << 16), wreg[8], wreg[9], wreg[10], wreg[11], wreg[12], wreg[13], wreg[14], wreg[15]);
-            tmem_wait_st();
-            fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s32(&S.full[ac.idx]));
+            const uint32_t tg = a_cols + lane_base + 16u * (uint32_t)g;
+            tmem_st_16x256b_x2(tg + 64u * (uint32_t)ai0, wreg0[0], wreg0[1], wreg0[2], wreg0[3], wreg0[4], wreg0[5], wreg0[6], wreg0[7]);
+            tmem_st_16x256b_x2(tg + 64u * (uint32_t)ai0 + (16u << 16), wreg0[8], wreg0[9], wreg0[10], wreg0[11], wreg0[12], wreg0[13], wreg0[14], wreg0[15]);
+            pending[0] = ai0;
+            if (two) {
+                tmem_st_16x256b_x2(tg + 64u * (uint32_t)ai1, wreg1[0], wreg1[1], wreg1[2], wreg1[3], wreg1[4], wreg1[5], wreg1[6], wreg1[7]);
+                tmem_st_16x256b_x2(tg + 64u * (uint32_t)ai1 + (16u << 16), wreg1[8], wreg1[9], wreg1[10], wreg1[11], wreg1[12], wreg1[13], wreg1[14], wreg1[15]);
+                pending[1] = ai1;
+            }
             TC_CLK(c4);
             TC_ACC(3, c3, c4);
         }
+        announce();
 #ifdef EXL3_TC_TRACE
         if (lane == 0) {
             const int cta = blockIdx.x + gridDim.x * blockIdx.y;

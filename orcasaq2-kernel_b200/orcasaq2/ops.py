@@ -6,9 +6,10 @@ used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, wr
 into the concatenated output.
 
 Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
-streaming of the packed trellis).  17 rows up to TC_MAX_ROWS: the tcgen05 kernel that decodes the
-trellis into shared-memory tiles inside the GEMM (one pass over the weights, no dense copy in
-memory).  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
+streaming of the packed trellis).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
+packed weights with no dense copy in memory -- up to 128 rows (and a multiple of 256 output
+channels) the decoded weights go from registers into tensor memory and are the A operand of
+tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
 weight once into a scratch buffer, dense library GEMM, rotate back.  GEMM_MAX_ROWS keeps the
 reference's name and default; it is the bound up to which the packed trellis is read directly
 when the tcgen05 path is switched off (ORCA_EXL3_TC=0).
