@@ -12,7 +12,8 @@ sets (3 x 134 MB) are rotated so no step finds its trellis in the 126 MB L2.
 metric  = algorithmic bytes (trellis + activations in + out) moved per second, whole job.
 value   = inputs resident in HBM, device-timed with CUDA events.
 e2e     = same metric through the plugin's custom op with HOST activations: pinned host x ->
-          device, three `orcasaq2::layer_gemm` calls, outputs back to pinned host, every step.
+          device, three `orcasaq2::layer_gemm` calls, outputs back to pinned host, every step;
+          replayed from a CUDA graph (the plugin's serving mode), the eager time is reported beside it.
 N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
           down_proj followed by an NCCL all-reduce), strong scaling: the job's total bytes are fixed.
 
@@ -287,11 +288,57 @@ def run_gpu(args):
     for i in range(args.steps):
         e2e_step(i)
     barrier()
-    e2e_s = (time.perf_counter() - t0) / args.steps
+    e2e_eager_s = (time.perf_counter() - t0) / args.steps
+    e2e_s, e2e_mode = e2e_eager_s, "eager: per layer H2D copy, plugin op, D2H copy; one sync per step"
+    if not args.no_graph:
+        # The serving mode of the plugin (the op is built to replay inside CUDA graphs): per weight set
+        # one graph of [pinned host x -> device, the three plugin ops, outputs -> pinned host]; a step
+        # rewrites the host activations, replays the graph and waits for the outputs.
+        dx = {ic: torch.empty_like(x) for ic, x in xs.items()}
+
+        def e2e_body(si):
+            for li, (name, ic_r, _, _) in enumerate(sets[si]):
+                dx[ic_r].copy_(hx[ic_r], non_blocking=True)
+                y = torch.ops.orcasaq2.layer_gemm(dx[ic_r], *lay_args[si][li])
+                if world > 1 and name == "down_proj":
+                    dist.all_reduce(y)
+                hy[li].copy_(y, non_blocking=True)
+
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        e2e_graphs = []
+        with torch.cuda.stream(side):
+            for si in range(N_SETS):
+                e2e_body(si)
+            torch.cuda.synchronize()
+            for si in range(N_SETS):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    e2e_body(si)
+                e2e_graphs.append(g)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+        def e2e_graph_step(i):
+            for h in hx.values():
+                h[0, 0] = 0.001 * (i % 7)          # the host inputs are live, not baked into the graph
+            e2e_graphs[i % N_SETS].replay()
+            torch.cuda.synchronize()
+
+        for i in range(3):
+            e2e_graph_step(i)
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e_graph_step(i)
+        barrier()
+        e2e_s = (time.perf_counter() - t0) / args.steps
+        e2e_mode = ("CUDA-graph replay per step of [pinned host x -> device, three orcasaq2::layer_gemm ops, "
+                    "outputs -> pinned host], host inputs rewritten before and one sync after every replay")
     if world > 1:
-        t = torch.tensor([e2e_s], device=dev)
+        t = torch.tensor([e2e_s, e2e_eager_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+        e2e_s, e2e_eager_s = float(t[0].item()), float(t[1].item())
     h2d = sum(rows * ic_r * 2 for (_, ic_r, _, _) in sets[0])
     d2h = sum(rows * tot * 2 for (_, _, _, tot) in sets[0])
 
@@ -339,7 +386,8 @@ def run_gpu(args):
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
                    "pct_of_8TBs_nominal": round(value / 8000.0 * 100, 2)},
         "e2e": {"value": round(full_bytes / e2e_s / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 5)},
+                "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 5), "mode": e2e_mode,
+                "eager_ms_per_step": round(e2e_eager_s * 1e3, 5)},
         # every fused layer is two kernels of this library: the activation pre-pass and the GEMV
         "gpu_launches": timed_steps * len(LAYERS) * 2, "cuda_graph": graph is not None,
         "clocks": clocks, "roofline": roof,
