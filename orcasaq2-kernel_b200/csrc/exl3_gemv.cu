@@ -281,35 +281,38 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     __syncthreads();   // every warp is done with its ring: the region is reused below
     EXL3_TRACE(3);
 
-    // ---- reduce the eight warps
-    float *red = reinterpret_cast<float *>(region);                  // [8][NT*8][128]
-    float *fin = red + kWarps * (NT * 8) * 128;                      // [NT*8][128]
-    {
-        const int u = g >> 1, p = g & 1;
+    // ---- reduce the eight warps, eight rows (one accumulator tile) per pass: the staging buffer stays
+    // small enough for two CTAs per SM also with sixteen rows
+    float *red = reinterpret_cast<float *>(region);                  // [8 warps][8 rows][128]
+    float *fin = red + kWarps * 8 * 128;                             // [NT*8][128]
+    const int unit = S.unit_begin + ob;
+    const int ocl = tid & 127;
+    float *part = P.partial + S.partial_off + (size_t)ob * S.splitk * P.rows * 128;
 #pragma unroll
-        for (int t = 0; t < NT; ++t)
+    for (int t = 0; t < NT; ++t) {
+        if (t) __syncthreads();                                      // the previous pass has been summed
+        {
+            const int u = g >> 1, p = g & 1;
 #pragma unroll
             for (int h = 0; h < 2; ++h)
 #pragma unroll
                 for (int a = 0; a < 4; ++a) {
                     const int oc_lo = 64 * h + 16 * u + 4 * a + p;
                     const int n0 = 8 * t + 2 * q;
-                    float *r0 = red + ((size_t)(warp * (NT * 8) + n0)) * 128 + oc_lo;
+                    float *r0 = red + ((size_t)(warp * 8 + 2 * q)) * 128 + oc_lo;
                     if (n0 < P.rows) { r0[0] = acc[t][h][a][0]; r0[2] = acc[t][h][a][2]; }
                     if (n0 + 1 < P.rows) { r0[128] = acc[t][h][a][1]; r0[130] = acc[t][h][a][3]; }
                 }
-    }
-    __syncthreads();
-
-    const int unit = S.unit_begin + ob;
-    const int ocl = tid & 127;
-    float *part = P.partial + S.partial_off + (size_t)ob * S.splitk * P.rows * 128;
-    for (int n = tid >> 7; n < P.rows; n += 2) {
-        float v = 0.f;
+        }
+        __syncthreads();
+        for (int nl = tid >> 7; nl < 8 && 8 * t + nl < P.rows; nl += 2) {
+            const int n = 8 * t + nl;
+            float v = 0.f;
 #pragma unroll
-        for (int r = 0; r < kWarps; ++r) v += red[((size_t)(r * (NT * 8) + n)) * 128 + ocl];
-        if (S.splitk == 1) fin[n * 128 + ocl] = v;
-        else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
+            for (int r = 0; r < kWarps; ++r) v += red[((size_t)(r * 8 + nl)) * 128 + ocl];
+            if (S.splitk == 1) fin[n * 128 + ocl] = v;
+            else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
+        }
     }
 
     EXL3_TRACE(4);
@@ -531,7 +534,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     }
     pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
     pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
-    const int red = (kWarps + 1) * pl.nt * 8 * 128 * 4;
+    const int red = (kWarps * 8 + pl.nt * 8) * 128 * 4;           // staging of one pass + the summed rows
     pl.region_bytes = ring > red ? ring : red;
     return EXL3_OK;
 }
