@@ -115,3 +115,73 @@ def test_int8_embedding_table_module(ext, coracle):
     out = tab(ids)
     ref = coracle.int8_embed(q.numpy(), s.view(torch.int16).numpy().view(np.uint16), ids.cpu().numpy(), False)
     assert np.array_equal(out.view(torch.int16).cpu().numpy().view(np.uint16), ref)
+
+
+# ---- the same flow on vLLM's own layer classes (reference callers: vllm linear.py:585, 1556) ----------
+@pytest.fixture(scope="module")
+def vllm_layers(cfg):
+    """A vLLM config context and a one-rank model-parallel state, so that vLLM's own linear layers
+    can be constructed with this plugin's quantization config.  Anything vLLM refuses to set up
+    outside an engine skips these tests instead of failing them."""
+    import socket
+    ctx = None
+    try:
+        from vllm.config import VllmConfig, set_current_vllm_config
+        from vllm.distributed import parallel_state as ps
+        ctx = set_current_vllm_config(VllmConfig())
+        ctx.__enter__()
+        if not ps.model_parallel_is_initialized():
+            with socket.socket() as s:
+                s.bind(("127.0.0.1", 0))
+                port = s.getsockname()[1]
+            ps.init_distributed_environment(world_size=1, rank=0, local_rank=0, backend="gloo",
+                                            distributed_init_method=f"tcp://127.0.0.1:{port}")
+            ps.initialize_model_parallel(1, 1)
+        from vllm.model_executor.layers import linear
+    except Exception as e:                                            # noqa: BLE001
+        if ctx is not None:
+            ctx.__exit__(None, None, None)
+        pytest.skip(f"vLLM layers cannot be constructed outside an engine here: {type(e).__name__}: {e}")
+    yield linear
+    ctx.__exit__(None, None, None)
+
+
+def _load(layer, specs, ic, seed):
+    """Hand every shard to the parameters' own weight_loader, as vLLM's model loaders do."""
+    refs = []
+    for i, (sid, oc, K) in enumerate(specs):
+        tr, suh, svh, _ = R.make_layer(seed + i, ic, oc, K, 1)
+        for name, t in (("trellis", tr), ("suh", suh), ("svh", svh)):
+            p = getattr(layer, name)
+            p.weight_loader(p, t, sid)
+        refs.append((tr, suh, svh))
+    return refs
+
+
+@pytest.mark.parametrize("rows", [1, 24])
+def test_vllm_qkv_merged_and_row_parallel_layers(vllm_layers, cfg, coracle, rows):
+    L = vllm_layers
+    qc = cfg.Exl3Config.from_config({})
+    hidden, head, ffn = 256, 128, 384
+    qkv = L.QKVParallelLinear(hidden, head, 3, 1, bias=False, quant_config=qc, params_dtype=torch.bfloat16,
+                              prefix="model.layers.0.self_attn.qkv_proj")
+    gate_up = L.MergedColumnParallelLinear(hidden, [ffn, ffn], bias=False, quant_config=qc, params_dtype=torch.bfloat16,
+                                           prefix="model.layers.0.mlp.gate_up_proj")
+    down = L.RowParallelLinear(ffn, hidden, bias=False, quant_config=qc, params_dtype=torch.bfloat16,
+                               prefix="model.layers.0.mlp.down_proj")
+    for layer in (qkv, gate_up, down):
+        assert isinstance(layer.quant_method, cfg.Exl3LinearMethod)
+    cases = [(qkv, [("q", 3 * head, 4), ("k", head, 5), ("v", head, 6)], hidden),
+             (gate_up, [(0, ffn, 3), (1, ffn, 3)], hidden),
+             (down, [(None, hidden, 4)], ffn)]
+    for li, (layer, specs, ic) in enumerate(cases):
+        refs = _load(layer, specs, ic, 900 + 10 * li)
+        layer.quant_method.process_weights_after_loading(layer)
+        x = torch.randn((rows, ic), generator=torch.Generator().manual_seed(li + rows)).to(torch.bfloat16)
+        out = layer(x.cuda())
+        y = out[0] if isinstance(out, tuple) else out
+        xf = x.half().numpy()
+        ref = np.concatenate([coracle.layer(xf, coracle.reconstruct(tr.numpy()), suh.numpy(), svh.numpy())
+                              for tr, suh, svh in refs], 1)
+        assert y.shape == (rows, sum(oc for _, oc, _ in specs)) and y.dtype == torch.bfloat16
+        _close(y, ref, tol=2e-2)
