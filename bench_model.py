@@ -56,22 +56,19 @@ class Linear:
 
     def __call__(self, x, in_mode=0, residual=None, out=None):
         """in_mode: 0 plain, 1 RMSNorm(x), 2 silu(x[:, :ic]) * x[:, ic:]; `residual` is added to the
-        result (both fused into the GEMV for <= 16 rows, separate torch ops above that)."""
+        result (fused into the GEMV for <= 16 rows, into the pre- and post-pass of the tcgen05 path above)."""
         if self.rows <= self.ext.GEMV_MAX_ROWS:
             out = self.out if out is None else out
             self.ext.gemv_grouped(x, self.shards, out, in_mode=in_mode, residual=residual)
             return out
-        if in_mode == 1:
-            x = rms(x)
-        elif in_mode == 2:
-            half = x.shape[1] // 2
-            x = F.silu(x[:, :half]) * x[:, half:]
-        if True:
-            for s in self.shards:                       # many rows: tcgen05 path, shard by shard
-                y = torch.empty((self.rows, s["oc"]), dtype=torch.half, device=x.device)
-                self.ext.gemm_tc(x, s["trellis"], y, s["suh"], s["svh"])
-                self.out[:, s["out_col"]:s["out_col"] + s["oc"]] = y
-        return self.out if residual is None else residual + self.out
+        # many rows: the tcgen05 path, shard by shard, each writing its column block; the norm / gated
+        # activation rides in its activation pre-pass, the residual add in its post-pass
+        out = self.out if out is None else out
+        for s in self.shards:
+            c0 = s["out_col"]
+            self.ext.gemm_tc(x, s["trellis"], out[:, c0:c0 + s["oc"]], s["suh"], s["svh"], in_mode=in_mode,
+                             residual=None if residual is None else residual[:, c0:c0 + s["oc"]])
+        return out
 
 
 def rms(x, eps=1e-6):

@@ -139,6 +139,19 @@ size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc);
 int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
                  void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
                  int mul1, int x_is_bf16, void *stream);
+/*
+ * exl3_gemm_tc with the elementwise neighbours of the layer folded in, as exl3_gemv_grouped_ex does
+ * for few rows (no counterpart in the reference plugin): the input transform (fusion->in_mode, see
+ * exl3_gemv_fusion) runs inside the activation pre-pass, the residual add inside the output
+ * post-pass, and y may be a column block of a wider matrix: row pitch ldy >= oc elements, a multiple
+ * of 4 (this is what removes the torch.cat of orcasaq2/config.py:236-242 for fused layers).
+ * fusion == NULL and ldy == oc is exl3_gemm_tc.  Up to 128 rows with oc a multiple of 256 every
+ * combination is served; beyond that a pitch or a residual is refused with EXL3_E_UNSUPPORTED when
+ * the shape runs unsplit (the caller then applies them itself).
+ */
+int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
+                    void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
+                    int mul1, int x_is_bf16, int ldy, const exl3_gemv_fusion *fusion, void *stream);
 unsigned exl3_gemm_tc_status(void);
 
 /*

@@ -415,13 +415,38 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     }
 }
 
+// The elementwise neighbours of the layer that the pre-pass can absorb (see exl3_gemv_fusion).
+struct XhFusion {
+    int in_mode;            // 0 plain, 1 RMSNorm, 2 silu(x[:, :ic]) * x[:, ic:]
+    const __half *norm_w;   // RMSNorm weight or null
+    float eps;
+    int ldx;                // row pitch of x in elements
+    int ic;
+};
+// four consecutive activations as floats; bf16 is narrowed to fp16 first (the reference casts
+// activations to fp16: config.py:233)
+template <bool BF16>
+__device__ __forceinline__ void load4(const void *x, size_t off, float (&v)[4]) {
+    if (BF16) {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(x) + off);
+        v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
+        v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k]));
+    } else {
+        const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __half *>(x) + off);
+        const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
+        v[0] = __low2float(h01); v[1] = __high2float(h01); v[2] = __low2float(h23); v[3] = __high2float(h23);
+    }
+}
+
 // Pre-pass: Xh = H128(x * suh) as fp16, with the K order permuted inside every 16-channel tile
 // (channel 8b + 4h + q is stored at 4q + 2b + h) to match the A tiles written by the decode warps.
 // x may be fp16 or bf16 (the reference casts activations to fp16 first: config.py:233).
 template <bool BF16>
 __global__ void __launch_bounds__(256)
 xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __half *__restrict__ xh,
-                  long long nblocks, int blocks_per_row) {
+                  long long nblocks, int blocks_per_row, XhFusion F) {
     // no-ops unless launched with programmatic stream serialization: x and the scratch may still be
     // in use by the kernels before this one
     asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -430,18 +455,30 @@ xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __
     const long long wid = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
     if (wid >= nblocks) return;
     const int blk = (int)(wid % blocks_per_row);
-    const size_t off = (size_t)wid * 128 + 4 * lane;
+    const long long row = wid / blocks_per_row;
+    const size_t off = (size_t)row * F.ldx + (size_t)blk * 128 + 4 * lane;
     float v[4];
-    if (BF16) {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(x) + off);
-        v[0] = __uint_as_float(raw.x << 16); v[1] = __uint_as_float(raw.x & 0xFFFF0000u);
-        v[2] = __uint_as_float(raw.y << 16); v[3] = __uint_as_float(raw.y & 0xFFFF0000u);
+    load4<BF16>(x, off, v);
+    if (F.in_mode == 1) {
+        // RMSNorm folded in: the row is short and sits in L2, every warp reduces it itself
+        float ss = 0.f;
+        for (int c = 4 * lane; c < F.ic; c += 128) {
+            float t[4];
+            load4<BF16>(x, (size_t)row * F.ldx + c, t);
+            ss += t[0] * t[0] + t[1] * t[1] + t[2] * t[2] + t[3] * t[3];
+        }
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k]));      // the reference's .half()
-    } else {
-        const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __half *>(x) + off);
-        const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
-        v[0] = __low2float(h01); v[1] = __high2float(h01); v[2] = __low2float(h23); v[3] = __high2float(h23);
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rn = rsqrtf(ss / (float)F.ic + F.eps);
+        float g[4] = {1.f, 1.f, 1.f, 1.f};
+        if (F.norm_w) load4<false>(F.norm_w, (size_t)blk * 128 + 4 * lane, g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k] * rn * g[k]));     // the norm's own fp16 output
+    } else if (F.in_mode == 2) {
+        float u[4];
+        load4<BF16>(x, off + F.ic, u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k] / (1.f + __expf(-v[k])) * u[k]));
     }
     const uint2 sr = *reinterpret_cast<const uint2 *>(suh + blk * 128 + 4 * lane);
     const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x), s23 = *reinterpret_cast<const __half2 *>(&sr.y);
@@ -457,7 +494,8 @@ xh_permute_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __
 // Post-pass for split-K: sum the fp32 slices in order, H128, svh, fp16.
 __global__ void __launch_bounds__(256)
 reduce_had_kernel(const float *__restrict__ partial, int splitk, const __half *__restrict__ svh,
-                  __half *__restrict__ y, long long nblocks, int blocks_per_row, size_t slice_elems) {
+                  __half *y, long long nblocks, int blocks_per_row, size_t slice_elems, int ldy,
+                  const __half *residual, int ld_res) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const int lane = threadIdx.x & 31;
@@ -475,12 +513,15 @@ reduce_had_kernel(const float *__restrict__ partial, int splitk, const __half *_
     fwht128_warp(v, lane);
     const uint2 sr = *reinterpret_cast<const uint2 *>(svh + blk * 128 + 4 * lane);
     const __half2 s01 = *reinterpret_cast<const __half2 *>(&sr.x), s23 = *reinterpret_cast<const __half2 *>(&sr.y);
-    const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * __low2float(s01), v[1] * kHadScale * __high2float(s01));
-    const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * __low2float(s23), v[3] * kHadScale * __high2float(s23));
+    const long long row = wid / blocks_per_row;
+    float r[4] = {0.f, 0.f, 0.f, 0.f};
+    if (residual) load4<false>(residual, (size_t)row * ld_res + (size_t)blk * 128 + 4 * lane, r);   // may alias y
+    const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * __low2float(s01) + r[0], v[1] * kHadScale * __high2float(s01) + r[1]);
+    const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * __low2float(s23) + r[2], v[3] * kHadScale * __high2float(s23) + r[3]);
     uint2 o;
     o.x = *reinterpret_cast<const uint32_t *>(&o01);
     o.y = *reinterpret_cast<const uint32_t *>(&o23);
-    *reinterpret_cast<uint2 *>(y + off) = o;
+    *reinterpret_cast<uint2 *>(y + (size_t)row * ldy + (size_t)blk * 128 + 4 * lane) = o;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
@@ -568,18 +609,41 @@ extern "C" size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc) {
 extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
                             void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
                             int mul1, int x_is_bf16, void *stream) {
+    return exl3_gemm_tc_ex(x, trellis, y, suh, svh, scratch, scratch_bytes, rows, ic, oc, k_times_2, mcg, mul1,
+                           x_is_bf16, oc, nullptr, stream);
+}
+
+extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
+                               void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
+                               int mul1, int x_is_bf16, int ldy, const exl3_gemv_fusion *fusion, void *stream) {
     using namespace exl3;
     using namespace exl3::tc;
     if (!x || !trellis || !y || !suh || !svh || !scratch) return EXL3_E_NULL;
     void *xh_scratch = scratch;
-    if (rows < 1 || ic <= 0 || oc <= 0 || (ic & 127) || (oc & 127) || oc / kBM > 65535) return EXL3_E_SHAPE;
+    if (rows < 1 || ic <= 0 || oc <= 0 || (ic & 127) || (oc & 127) || oc / kBM > 65535 || ldy < oc) return EXL3_E_SHAPE;
     if (mcg || mul1) return EXL3_E_UNSUPPORTED;
     const int K = integer_k(k_times_2);
     if (!K) return EXL3_E_UNSUPPORTED;
     if (!aligned(x, 8) || !aligned(y, 8) || !aligned(trellis, 16) || !aligned(scratch, 256) || !aligned(suh, 8) ||
-        !aligned(svh, 8))
+        !aligned(svh, 8) || (ldy & 3))
         return EXL3_E_ALIGN;
     if (scratch_bytes < exl3_gemm_tc_scratch_bytes(rows, ic, oc)) return EXL3_E_WORKSPACE;
+    XhFusion F;
+    F.in_mode = 0; F.norm_w = nullptr; F.eps = 0.f; F.ldx = ic; F.ic = ic;
+    const __half *residual = nullptr;
+    int ld_res = ldy;
+    if (fusion) {
+        if (fusion->in_mode < 0 || fusion->in_mode > 2) return EXL3_E_UNSUPPORTED;
+        F.in_mode = fusion->in_mode;
+        F.norm_w = static_cast<const __half *>(fusion->norm_weight);
+        F.eps = fusion->eps;
+        F.ldx = fusion->ldx > 0 ? fusion->ldx : (fusion->in_mode == 2 ? 2 * ic : ic);
+        residual = static_cast<const __half *>(fusion->residual);
+        ld_res = fusion->ld_residual > 0 ? fusion->ld_residual : ldy;
+        if ((F.ldx & 3) || (ld_res & 3) || (F.norm_w && !aligned(F.norm_w, 8)) || (residual && !aligned(residual, 8)))
+            return EXL3_E_ALIGN;
+        if (F.ldx < (F.in_mode == 2 ? 2 * ic : ic) || ld_res < oc) return EXL3_E_SHAPE;
+    }
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     EncodeTiledFn enc = encode_fn();
     if (!enc) return EXL3_E_LAUNCH;
@@ -591,19 +655,20 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
         const unsigned g1 = (unsigned)((nblocks + 7) / 8);
         const cudaError_t e1 =
             x_is_bf16 ? launch_pdl(xh_permute_kernel<true>, dim3(g1), dim3(256), 0, st, x, static_cast<const __half *>(suh),
-                                   static_cast<__half *>(scratch), nblocks, ic / 128)
+                                   static_cast<__half *>(scratch), nblocks, ic / 128, F)
                       : launch_pdl(xh_permute_kernel<false>, dim3(g1), dim3(256), 0, st, x, static_cast<const __half *>(suh),
-                                   static_cast<__half *>(scratch), nblocks, ic / 128);
+                                   static_cast<__half *>(scratch), nblocks, ic / 128, F);
         if (e1 != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
         ts::Params P;
         P.trellis = static_cast<const uint32_t *>(trellis);
-        P.y = static_cast<__half *>(y);
         P.tokens = rows; P.npad = (rows + 15) & ~15;
-        P.ic = ic; P.oc = oc; P.ldy = oc; P.tiles_j = oc / 16; P.splitk = sk; P.one = 1u;
+        P.ic = ic; P.oc = oc; P.tiles_j = oc / 16; P.splitk = sk; P.one = 1u;
         P.b_slot_bytes = (P.npad * 128 + 1023) & ~1023;
         P.bufs = (ts::kTmemCols - 2 * P.npad) / 64;
         if (P.bufs > ts::kMaxBufs) P.bufs = ts::kMaxBufs;
-        P.partial = sk > 1 ? reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + ts::xh_bytes(rows, ic)) : nullptr;
+        // always through fp32 partial sums (one slice at least): the post-pass then carries the output
+        // pitch and the residual
+        P.partial = reinterpret_cast<float *>(static_cast<unsigned char *>(scratch) + ts::xh_bytes(rows, ic));
         CUtensorMap map;
         const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
         const cuuint64_t gstr[1] = {(cuuint64_t)ic * 2};
@@ -624,24 +689,26 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
             default: rc = ts::launch<8>(map, P, st); break;
         }
         if (rc != EXL3_OK) return rc;
-        if (sk == 1) return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
         const long long nb = (long long)rows * (oc / 128);
         if (launch_pdl(reduce_had_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, st, (const float *)P.partial, sk,
-                       static_cast<const __half *>(svh), static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc) != cudaSuccess) {
+                       static_cast<const __half *>(svh), static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc, ldy,
+                       residual, ld_res) != cudaSuccess) {
             cudaGetLastError();
             return EXL3_E_LAUNCH;
         }
         return EXL3_OK;
     }
     const int splitk = choose_splitk(rows, ic, oc);
+    // the unsplit shared-memory kernel writes y itself and rotates it in place: no pitch, no residual
+    if (splitk == 1 && (ldy != oc || residual)) return EXL3_E_UNSUPPORTED;
 
     // 1. rotate and permute the activations
     const long long nblocks = (long long)rows * (ic / 128);
     const unsigned g1 = (unsigned)((nblocks + 7) / 8);
     if (x_is_bf16)
-        xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(xh_scratch), nblocks, ic / 128);
+        xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(xh_scratch), nblocks, ic / 128, F);
     else
-        xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(xh_scratch), nblocks, ic / 128);
+        xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), static_cast<__half *>(xh_scratch), nblocks, ic / 128, F);
     if (cudaGetLastError() != cudaSuccess) return EXL3_E_LAUNCH;
 
     // 2. decode + tcgen05 contraction
@@ -685,6 +752,7 @@ extern "C" int exl3_gemm_tc(const void *x, const void *trellis, void *y, const v
     if (splitk == 1) return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
     const long long nb = (long long)rows * (oc / 128);
     reduce_had_kernel<<<(unsigned)((nb + 7) / 8), 256, 0, st>>>(P.partial, splitk, static_cast<const __half *>(svh),
-                                                               static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc);
+                                                               static_cast<__half *>(y), nb, oc / 128, (size_t)rows * oc, ldy,
+                                                               residual, ld_res);
     return launch_status();
 }

@@ -22,7 +22,7 @@
 //                 mbarriers; warp 1 also allocates and frees the tensor memory
 //   warps 2..17   four decode groups of four warps (one warp per TMEM lane quarter = 64 output
 //                 channels); group g takes the tile rows g, g+4, ... of the slice; afterwards the
-//                 epilogue (tcgen05.ld, fp32 partial sums or fp16 outputs)
+//                 epilogue (tcgen05.ld, fp32 partial sums)
 // Tensor memory: accumulators X and Y (rows a = 0,1 and a = 2,3 of every four-tile span) in columns
 // [0, 2 npad), then 4 .. 7 A buffers of 64 columns (16 per group: 8 for X, 8 for Y).
 // The K order inside a tile row is k = 4 (ic & 3) + 2 (ic >> 3) + ((ic >> 2) & 1), the order in which
@@ -53,10 +53,9 @@ constexpr int kTmemCols = 512;
 
 struct Params {
     const uint32_t *trellis;
-    __half *y;             // [tokens][ldy]
-    float *partial;        // [splitk][tokens][oc] fp32 when splitk > 1
+    float *partial;        // [splitk][tokens][oc] fp32: the post-pass sums the slices, rotates and writes y
     int tokens, npad;      // npad: tokens rounded up to 16 (MMA N, TMA box rows)
-    int ic, oc, ldy, tiles_j, splitk;
+    int ic, oc, tiles_j, splitk;
     int b_slot_bytes;      // npad * 128, rounded up to 1024
     int bufs;              // rounds in flight, 4 .. kMaxBufs
     uint32_t one;
@@ -317,7 +316,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         }
 #endif
 
-        // ---------------- epilogue: accumulators -> fp32 partial sums or fp16 outputs
+        // ---------------- epilogue: accumulators -> fp32 partial sums
         ok = mbar_wait(s32(&S.acc_full), 0, status, 200) && ok;
         fence_after_sync();
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -334,10 +333,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
                 for (int j = 0; j < 16; ++j) {
                     const int tok = c0 + j;
                     if (tok < P.tokens) {
-                        if (P.splitk > 1)
-                            P.partial[((size_t)blockIdx.y * P.tokens + tok) * P.oc + oc_idx] = __uint_as_float(v[j]);
-                        else
-                            P.y[(size_t)tok * P.ldy + oc_idx] = __float2half_rn(__uint_as_float(v[j]));
+                        P.partial[((size_t)blockIdx.y * P.tokens + tok) * P.oc + oc_idx] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -380,8 +376,7 @@ static int choose_splitk(int ic, int oc) {
 }
 static size_t xh_bytes(int rows, int ic) { return (((size_t)rows * ic * 2) + 255) & ~(size_t)255; }
 static size_t scratch_bytes(int rows, int ic, int oc) {
-    const int sk = choose_splitk(ic, oc);
-    return xh_bytes(rows, ic) + (sk > 1 ? (size_t)sk * rows * oc * 4 : 0);
+    return xh_bytes(rows, ic) + (size_t)choose_splitk(ic, oc) * rows * oc * 4;     // always at least one slice of partial sums
 }
 
 }  // namespace ts

@@ -71,6 +71,9 @@ def lib():
                 L.exl3_gemm_tc_scratch_bytes.restype = sz
                 L.exl3_gemm_tc_scratch_bytes.argtypes = [ci, ci, ci]
                 L.exl3_gemm_tc.restype = ci
+                L.exl3_gemm_tc_ex.argtypes = [vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ci, ci,
+                                              ctypes.POINTER(Exl3GemvFusion), vp]
+                L.exl3_gemm_tc_ex.restype = ci
                 L.exl3_gemm_tc_status.restype = ctypes.c_uint
                 L.exl3_gemv_static_capacity.restype = sz
                 L.exl3_gemv_grouped_static.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp]
@@ -307,25 +310,68 @@ def int8_head(qweight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor) -> t
     return out
 
 
+def _rows_view(t: torch.Tensor, name: str, dtype):
+    """A CUDA matrix whose rows are contiguous (it may be a column block of a wider one)."""
+    if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+        raise RuntimeError(f"{name} must be a CUDA tensor (this build has no CPU path)")
+    if t.dtype not in (dtype if isinstance(dtype, tuple) else (dtype,)):
+        raise RuntimeError(f"{name} has dtype {t.dtype}, expected {dtype}")
+    if t.dim() != 2 or (t.shape[1] > 1 and t.stride(1) != 1):
+        raise RuntimeError(f"{name} must be a matrix with contiguous rows")
+    return t
+
+
 def gemm_tc(x: torch.Tensor, trellis: torch.Tensor, y: torch.Tensor, suh: torch.Tensor, svh: torch.Tensor,
-            mcg: bool = False, mul1: bool = False) -> None:
-    """y[rows, oc] <- H(H(x*suh) W) * svh for many rows: in-kernel trellis decode into shared-memory
-    tiles feeding tcgen05.mma.  x fp16 or bf16, y fp16."""
-    _cuda(x, "x", _DT)
-    _cuda(y, "y", torch.float16)
+            mcg: bool = False, mul1: bool = False, in_mode: int = IN_PLAIN, norm_weight=None, eps: float = 1e-6,
+            residual=None) -> None:
+    """y[rows, oc] <- H(H(f(x)*suh) W) * svh (+ residual) for many rows: in-kernel trellis decode feeding
+    tcgen05.mma (operand in tensor memory up to 128 rows, in shared memory above).  x fp16 or bf16, y
+    fp16; y may be a column block of a wider matrix.  in_mode / norm_weight / eps / residual as in
+    gemv_grouped (f = identity, RMSNorm, or silu(x[:, :ic]) * x[:, ic:])."""
+    _rows_view(x, "x", _DT)
+    _rows_view(y, "y", torch.float16)
     _cuda(trellis, "trellis")
     _cuda(suh, "suh", torch.float16)
     _cuda(svh, "svh", torch.float16)
     ic, oc, kk = _trellis_dims(trellis)
     rows = x.shape[0]
-    if x.shape[1] != ic or tuple(y.shape) != (rows, oc) or suh.numel() != ic or svh.numel() != oc:
+    need = 2 * ic if in_mode == IN_SILU_MUL else ic
+    if x.shape[1] != need or tuple(y.shape) != (rows, oc) or suh.numel() != ic or svh.numel() != oc:
         raise RuntimeError("gemm_tc: shapes of x, y, suh, svh do not match the trellis")
     L = lib()
     nbytes = L.exl3_gemm_tc_scratch_bytes(rows, ic, oc)
     scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x.device)     # freed on exit, like the reference's xh / w
-    _check(L.exl3_gemm_tc(x.data_ptr(), trellis.data_ptr(), y.data_ptr(), suh.data_ptr(), svh.data_ptr(),
-                              scratch.data_ptr(), nbytes, rows, ic, oc, _k2(kk), int(bool(mcg)), int(bool(mul1)),
-                              int(x.dtype == torch.bfloat16), _stream(x)), "exl3_gemm_tc")
+    fused = in_mode != IN_PLAIN or residual is not None or not y.is_contiguous() or not x.is_contiguous()
+    if not fused:
+        _check(L.exl3_gemm_tc(x.data_ptr(), trellis.data_ptr(), y.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                                  scratch.data_ptr(), nbytes, rows, ic, oc, _k2(kk), int(bool(mcg)), int(bool(mul1)),
+                                  int(x.dtype == torch.bfloat16), _stream(x)), "exl3_gemm_tc")
+        return
+    if norm_weight is not None:
+        _cuda(norm_weight, "norm_weight", torch.float16)
+    if residual is not None:
+        _rows_view(residual, "residual", torch.float16)
+        if residual.shape != y.shape:
+            raise RuntimeError("residual must have the shape of y")
+    fus = Exl3GemvFusion(in_mode, None if norm_weight is None else norm_weight.data_ptr(), float(eps), x.stride(0),
+                         None if residual is None else residual.data_ptr(),
+                         0 if residual is None else residual.stride(0))
+    rc = L.exl3_gemm_tc_ex(x.data_ptr(), trellis.data_ptr(), y.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                           scratch.data_ptr(), nbytes, rows, ic, oc, _k2(kk), int(bool(mcg)), int(bool(mul1)),
+                           int(x.dtype == torch.bfloat16), y.stride(0), ctypes.byref(fus), _stream(x))
+    if rc == -3 and not (bool(mcg) or bool(mul1)) and (residual is not None or not y.is_contiguous()):
+        # an unsplit many-row shape: the kernel rotates y in place, so the pitch and the residual are applied here
+        tmp = torch.empty((rows, oc), dtype=torch.float16, device=x.device)
+        fus2 = Exl3GemvFusion(in_mode, fus.norm_weight, float(eps), x.stride(0), None, 0)
+        _check(L.exl3_gemm_tc_ex(x.data_ptr(), trellis.data_ptr(), tmp.data_ptr(), suh.data_ptr(), svh.data_ptr(),
+                                 scratch.data_ptr(), nbytes, rows, ic, oc, _k2(kk), 0, 0,
+                                 int(x.dtype == torch.bfloat16), oc, ctypes.byref(fus2), _stream(x)), "exl3_gemm_tc_ex")
+        if residual is not None:
+            torch.add(tmp, residual, out=y)
+        else:
+            y.copy_(tmp)
+        return
+    _check(rc, "exl3_gemm_tc_ex")
 
 
 def gemm_tc_status() -> int:

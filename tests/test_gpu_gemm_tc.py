@@ -65,3 +65,51 @@ def test_gemm_tc_vs_reconstruct_route(ext, rows, ic, oc, K, dtype):
     y3 = torch.empty_like(y)
     ext.gemm_tc(x.cuda(), tr.cuda(), y3, suh.cuda(), svh.cuda())
     assert torch.equal(y, y3)
+
+
+def _dense_ref(ext, x, tr, suh, svh, K):
+    """reconstruct + dense matmul on the GPU (the reference's own route) for fp16 activations x."""
+    xh = torch.empty_like(x)
+    ext.had_r_128(x, xh, suh, None, 1.0)
+    w = torch.empty((x.shape[1], svh.numel()), dtype=torch.half, device="cuda")
+    ext.reconstruct(w, tr, K, False, False)
+    y = (xh.float() @ w.float()).half()
+    ext.had_r_128(y, y, None, svh, 1.0)
+    return y
+
+
+@pytest.mark.parametrize("rows,ic,oc,K", [(24, 1024, 512, 4), (128, 512, 256, 3), (300, 512, 384, 5), (600, 256, 128, 4)])
+def test_gemm_tc_fused_rmsnorm_residual_and_pitch(ext, rows, ic, oc, K):
+    """RMSNorm in the activation pre-pass, residual add and a wider output matrix in the post-pass equal
+    the separate operations -- on the tensor-memory kernel (<= 128 rows, oc % 256 == 0), on the split
+    shared-memory kernel, and through the binding's own completion where the kernel runs unsplit."""
+    tr, suh, svh, x = R.make_layer(700 + rows, ic, oc, K, rows)
+    g = torch.Generator().manual_seed(5)
+    gamma = (1.0 + 0.1 * torch.randn(ic, generator=g)).half().cuda()
+    wide = torch.randn((rows, oc + 256), generator=g).half().cuda()          # residual lives in the wide matrix
+    res = wide[:, 128:128 + oc]
+    xg, trg, sug, svg = (x * 3.0).half().cuda(), tr.cuda(), suh.cuda(), svh.cuda()
+    xf = xg.float()
+    xn = (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * gamma.float()).half()
+    ref = _dense_ref(ext, xn, trg, sug, svg, K).float() + res.float()
+    out = wide.clone()
+    ext.gemm_tc(xg, trg, out[:, 128:128 + oc], sug, svg, in_mode=ext.IN_RMSNORM, norm_weight=gamma, eps=1e-5,
+                residual=out[:, 128:128 + oc])
+    torch.cuda.synchronize()
+    assert ext.gemm_tc_status() == 0
+    assert (out[:, 128:128 + oc].float() - ref).abs().max() / ref.abs().max() < 5e-3
+    # the columns beside the block are untouched
+    assert torch.equal(out[:, :128], wide[:, :128]) and torch.equal(out[:, 128 + oc:], wide[:, 128 + oc:])
+
+
+@pytest.mark.parametrize("rows,ic,oc,K", [(40, 768, 256, 3), (200, 256, 128, 6)])
+def test_gemm_tc_fused_silu_mul(ext, rows, ic, oc, K):
+    tr, suh, svh, _ = R.make_layer(800 + rows, ic, oc, K, 1)
+    gu = torch.randn((rows, 2 * ic), generator=torch.Generator().manual_seed(rows)).half().cuda()
+    trg, sug, svg = tr.cuda(), suh.cuda(), svh.cuda()
+    y = torch.empty((rows, oc), dtype=torch.half, device="cuda")
+    ext.gemm_tc(gu, trg, y, sug, svg, in_mode=ext.IN_SILU_MUL)
+    act = (torch.nn.functional.silu(gu[:, :ic].float()) * gu[:, ic:].float()).half()
+    ref = _dense_ref(ext, act, trg, sug, svg, K).float()
+    assert ext.gemm_tc_status() == 0
+    assert (y.float() - ref).abs().max() / ref.abs().max() < 5e-3
