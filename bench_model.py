@@ -121,10 +121,10 @@ def main():
     pos = torch.arange(HD // 2, device=dev).float()
     ang = ctx / (10000.0 ** (pos / (HD // 2)))
     cos, sin = torch.cos(ang).half(), torch.sin(ang).half()
+    cs, sn = torch.cat([cos, cos]), torch.cat([-sin, sin])
 
-    def rope(t):                                    # [B, heads, HD]
-        a, b = t[..., : HD // 2], t[..., HD // 2:]
-        return torch.cat([a * cos - b * sin, a * sin + b * cos], -1)
+    def rope(t):                                    # [B, heads, HD], rotate-half form in three kernels
+        return torch.addcmul(t * cs, torch.roll(t, HD // 2, -1), sn)
 
     def step():
         h = _ext.int8_embed(table, scales, ids)                           # [B, HIDDEN] (rank-local rows)
@@ -132,8 +132,8 @@ def main():
             dist.all_reduce(h)                                            # vocabulary-parallel embedding
         for qkv, o, gu, down, kc, vc in model:
             y = qkv(h, in_mode=1)
-            q = rope(y[:, : qh * HD].reshape(B, qh, HD))
-            k = rope(y[:, qh * HD:(qh + kvh) * HD].reshape(B, kvh, HD))
+            qk = rope(y[:, :(qh + kvh) * HD].reshape(B, qh + kvh, HD))    # query and key heads in one pass
+            q, k = qk[:, :qh], qk[:, qh:]
             v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
             kc[:, :, ctx] = k
             vc[:, :, ctx] = v
