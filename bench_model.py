@@ -64,6 +64,8 @@ class Linear:
         # many rows: the tcgen05 path, shard by shard, each writing its column block; the norm / gated
         # activation rides in its activation pre-pass, the residual add in its post-pass
         out = self.out if out is None else out
+        if self.ext.gemm_tc_grouped(x, self.shards, out, in_mode=in_mode, residual=residual):
+            return out                                  # one grouped launch (up to 128 rows, oc % 256 == 0)
         for s in self.shards:
             c0 = s["out_col"]
             self.ext.gemm_tc(x, s["trellis"], out[:, c0:c0 + s["oc"]], s["suh"], s["svh"], in_mode=in_mode,

@@ -152,6 +152,17 @@ int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, c
 int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
                     void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
                     int mul1, int x_is_bf16, int ldy, const exl3_gemv_fusion *fusion, void *stream);
+/*
+ * All shards of a fused layer (qkv_proj, gate_up_proj) at up to 128 rows in three launches: the
+ * grouped form of exl3_gemm_tc_ex, as exl3_gemv_grouped is of exl3_gemv.  y is [rows][ldy]; shard s
+ * writes columns out_col .. out_col + oc.  Every shard needs oc a multiple of 256; otherwise, and
+ * above 128 rows, EXL3_E_UNSUPPORTED (scratch size 0) and the caller goes shard by shard.
+ * Replaces the per-shard loop + torch.cat of orcasaq2/config.py:236-242.
+ */
+size_t exl3_gemm_tc_grouped_scratch_bytes(const exl3_shard *shards, int nshards, int rows, int ic);
+int exl3_gemm_tc_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows, int ic,
+                         int ldy, void *scratch, size_t scratch_bytes, int x_is_bf16,
+                         const exl3_gemv_fusion *fusion, void *stream);
 unsigned exl3_gemm_tc_status(void);
 
 /*

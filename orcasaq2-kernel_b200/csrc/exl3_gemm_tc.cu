@@ -524,6 +524,101 @@ reduce_had_kernel(const float *__restrict__ partial, int splitk, const __half *_
     *reinterpret_cast<uint2 *>(y + (size_t)row * ldy + (size_t)blk * 128 + 4 * lane) = o;
 }
 
+// ---- grouped forms of the two passes: every shard of a fused layer in one launch -------------
+struct XhGroup {
+    int nshards;
+    const __half *suh[EXL3_MAX_SHARDS];
+    __half *xh[EXL3_MAX_SHARDS];
+};
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+xh_permute_grouped_kernel(const void *__restrict__ x, const __grid_constant__ XhGroup G, long long nblocks,
+                          int blocks_per_row, XhFusion F) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int lane = threadIdx.x & 31;
+    const long long wall = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wall >= nblocks * G.nshards) return;
+    const int sh = (int)(wall / nblocks);
+    const long long wid = wall - (long long)sh * nblocks;
+    const int blk = (int)(wid % blocks_per_row);
+    const long long row = wid / blocks_per_row;
+    const size_t off = (size_t)row * F.ldx + (size_t)blk * 128 + 4 * lane;
+    float v[4];
+    load4<BF16>(x, off, v);
+    if (F.in_mode == 1) {
+        float ss = 0.f;
+        for (int c = 4 * lane; c < F.ic; c += 128) {
+            float t[4];
+            load4<BF16>(x, (size_t)row * F.ldx + c, t);
+            ss += t[0] * t[0] + t[1] * t[1] + t[2] * t[2] + t[3] * t[3];
+        }
+#pragma unroll
+        for (int o = 16; o; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        const float rn = rsqrtf(ss / (float)F.ic + F.eps);
+        float g[4] = {1.f, 1.f, 1.f, 1.f};
+        if (F.norm_w) load4<false>(F.norm_w, (size_t)blk * 128 + 4 * lane, g);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k] * rn * g[k]));
+    } else if (F.in_mode == 2) {
+        float u[4];
+        load4<BF16>(x, off + F.ic, u);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k] / (1.f + __expf(-v[k])) * u[k]));
+    }
+    float sg[4];
+    load4<false>(G.suh[sh], (size_t)blk * 128 + 4 * lane, sg);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) v[k] *= sg[k];
+    fwht128_warp(v, lane);
+    __half *dst = G.xh[sh] + (size_t)wid * 128 + 16 * (lane >> 2) + (lane & 3);     // same K order as xh_permute_kernel
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dst[4 * j] = __float2half_rn(v[j] * kHadScale);
+}
+
+struct ReduceGroup {
+    int nshards;
+    long long blk_begin[EXL3_MAX_SHARDS + 1];   // 128-blocks (row-major over [rows][oc / 128]) before each shard
+    const float *partial[EXL3_MAX_SHARDS];
+    const __half *svh[EXL3_MAX_SHARDS];
+    int splitk[EXL3_MAX_SHARDS], blocks_per_row[EXL3_MAX_SHARDS], out_col[EXL3_MAX_SHARDS];
+    long long slice_elems[EXL3_MAX_SHARDS];
+};
+__global__ void __launch_bounds__(256)
+reduce_had_grouped_kernel(const __grid_constant__ ReduceGroup G, __half *y, int ldy, const __half *residual, int ld_res) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int lane = threadIdx.x & 31;
+    const long long wall = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (wall >= G.blk_begin[G.nshards]) return;
+    int sh = 0;
+    while (sh + 1 < G.nshards && wall >= G.blk_begin[sh + 1]) ++sh;
+    const long long wid = wall - G.blk_begin[sh];
+    const int bpr = G.blocks_per_row[sh];
+    const int blk = (int)(wid % bpr);
+    const long long row = wid / bpr;
+    const size_t off = (size_t)wid * 128 + 4 * lane;
+    float v[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k = 0; k < G.splitk[sh]; ++k) {
+        const float4 p = *reinterpret_cast<const float4 *>(G.partial[sh] + (size_t)k * G.slice_elems[sh] + off);
+        v[0] += p.x; v[1] += p.y; v[2] += p.z; v[3] += p.w;
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = __half2float(__float2half_rn(v[j]));   // same rounding point as the single-shard path
+    fwht128_warp(v, lane);
+    float sv[4];
+    load4<false>(G.svh[sh], (size_t)blk * 128 + 4 * lane, sv);
+    const size_t col = (size_t)G.out_col[sh] + (size_t)blk * 128 + 4 * lane;
+    float r[4] = {0.f, 0.f, 0.f, 0.f};
+    if (residual) load4<false>(residual, (size_t)row * ld_res + col, r);         // may alias y
+    const __half2 o01 = __floats2half2_rn(v[0] * kHadScale * sv[0] + r[0], v[1] * kHadScale * sv[1] + r[1]);
+    const __half2 o23 = __floats2half2_rn(v[2] * kHadScale * sv[2] + r[2], v[3] * kHadScale * sv[3] + r[3]);
+    uint2 o;
+    o.x = *reinterpret_cast<const uint32_t *>(&o01);
+    o.y = *reinterpret_cast<const uint32_t *>(&o23);
+    *reinterpret_cast<uint2 *>(y + (size_t)row * ldy + col) = o;
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                   const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -756,3 +851,156 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
                                                                residual, ld_res);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------------------------
+// All shards of a fused layer (qkv_proj, gate_up_proj) at 17..128 rows: three launches in total.
+namespace exl3 { namespace ts {
+struct GroupPlan {
+    int splitk, units;
+    size_t xh_off[EXL3_MAX_SHARDS], partial_off[EXL3_MAX_SHARDS], total;
+};
+static int plan_group(const exl3_shard *sh, int n, int rows, int ic, GroupPlan &pl) {
+    if (!sh) return EXL3_E_NULL;
+    if (n < 1 || n > EXL3_MAX_SHARDS || rows < 1 || ic <= 0 || (ic & 127)) return EXL3_E_SHAPE;
+    if (rows > kMaxTokens) return EXL3_E_UNSUPPORTED;
+    int units = 0;
+    for (int i = 0; i < n; ++i) {
+        if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
+        if (sh[i].oc % kOcCta) return EXL3_E_UNSUPPORTED;
+        if (sh[i].mcg || sh[i].mul1 || !integer_k(sh[i].k_times_2)) return EXL3_E_UNSUPPORTED;
+        if (!sh[i].trellis || !sh[i].suh || !sh[i].svh) return EXL3_E_NULL;
+        if (!aligned(sh[i].trellis, 16) || !aligned(sh[i].suh, 8) || !aligned(sh[i].svh, 8)) return EXL3_E_ALIGN;
+        units += sh[i].oc / kOcCta;
+    }
+    // every shard has the same input size, hence the same work per output block: one slice count for all
+    int sk = 148 / units;
+    if (sk > ic / 64 / 4) sk = ic / 64 / 4;
+    if (sk < 1) sk = 1;
+    pl.splitk = sk;
+    pl.units = units;
+    size_t off = 0;
+    for (int i = 0; i < n; ++i) { pl.xh_off[i] = off; off += xh_bytes(rows, ic); }
+    for (int i = 0; i < n; ++i) { pl.partial_off[i] = off; off += (((size_t)sk * rows * sh[i].oc * 4) + 255) & ~(size_t)255; }
+    pl.total = off;
+    return EXL3_OK;
+}
+} }
+
+extern "C" size_t exl3_gemm_tc_grouped_scratch_bytes(const exl3_shard *shards, int nshards, int rows, int ic) {
+    exl3::ts::GroupPlan pl;
+    if (exl3::ts::plan_group(shards, nshards, rows, ic, pl) != EXL3_OK) return 0;
+    return pl.total;
+}
+
+extern "C" int exl3_gemm_tc_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows, int ic,
+                                    int ldy, void *scratch, size_t scratch_bytes, int x_is_bf16,
+                                    const exl3_gemv_fusion *fusion, void *stream) {
+    using namespace exl3;
+    using namespace exl3::tc;
+    ts::GroupPlan pl;
+    const int rcp = ts::plan_group(shards, nshards, rows, ic, pl);
+    if (rcp != EXL3_OK) return rcp;
+    if (!x || !y || !scratch) return EXL3_E_NULL;
+    if (!aligned(x, 8) || !aligned(y, 8) || !aligned(scratch, 256) || (ldy & 3)) return EXL3_E_ALIGN;
+    for (int i = 0; i < nshards; ++i)
+        if (shards[i].out_col + shards[i].oc > ldy) return EXL3_E_SHAPE;
+    if (scratch_bytes < pl.total) return EXL3_E_WORKSPACE;
+    XhFusion F;
+    F.in_mode = 0; F.norm_w = nullptr; F.eps = 0.f; F.ldx = ic; F.ic = ic;
+    const __half *residual = nullptr;
+    int ld_res = ldy;
+    if (fusion) {
+        if (fusion->in_mode < 0 || fusion->in_mode > 2) return EXL3_E_UNSUPPORTED;
+        F.in_mode = fusion->in_mode;
+        F.norm_w = static_cast<const __half *>(fusion->norm_weight);
+        F.eps = fusion->eps;
+        F.ldx = fusion->ldx > 0 ? fusion->ldx : (fusion->in_mode == 2 ? 2 * ic : ic);
+        residual = static_cast<const __half *>(fusion->residual);
+        ld_res = fusion->ld_residual > 0 ? fusion->ld_residual : ldy;
+        if ((F.ldx & 3) || (ld_res & 3) || (F.norm_w && !aligned(F.norm_w, 8)) || (residual && !aligned(residual, 8)))
+            return EXL3_E_ALIGN;
+        if (F.ldx < (F.in_mode == 2 ? 2 * ic : ic)) return EXL3_E_SHAPE;
+    }
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    EncodeTiledFn enc = encode_fn();
+    if (!enc) return EXL3_E_LAUNCH;
+    unsigned char *base = static_cast<unsigned char *>(scratch);
+
+    // 1. rotated activations of every shard
+    XhGroup XG;
+    XG.nshards = nshards;
+    for (int i = 0; i < nshards; ++i) {
+        XG.suh[i] = static_cast<const __half *>(shards[i].suh);
+        XG.xh[i] = reinterpret_cast<__half *>(base + pl.xh_off[i]);
+    }
+    const long long nblocks = (long long)rows * (ic / 128);
+    const unsigned g1 = (unsigned)((nblocks * nshards + 7) / 8);
+    const cudaError_t e1 = x_is_bf16 ? launch_pdl(xh_permute_grouped_kernel<true>, dim3(g1), dim3(256), 0, st, x, XG, nblocks, ic / 128, F)
+                                     : launch_pdl(xh_permute_grouped_kernel<false>, dim3(g1), dim3(256), 0, st, x, XG, nblocks, ic / 128, F);
+    if (e1 != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+
+    // 2. decode + contraction
+    ts::MapPack maps;
+    ts::GroupArgs G;
+    G.nshards = nshards;
+    const int npad = (rows + 15) & ~15;
+    int bufs = (ts::kTmemCols - 2 * npad) / 64;
+    if (bufs > ts::kMaxBufs) bufs = ts::kMaxBufs;
+    const int b_slot_bytes = (npad * 128 + 1023) & ~1023;
+    size_t smem = 0;
+    int ctas = 0;
+    for (int i = 0; i < nshards; ++i) {
+        ts::Params &P = G.p[i];
+        P.trellis = static_cast<const uint32_t *>(shards[i].trellis);
+        P.partial = reinterpret_cast<float *>(base + pl.partial_off[i]);
+        P.tokens = rows; P.npad = npad; P.ic = ic; P.oc = shards[i].oc; P.tiles_j = shards[i].oc / 16;
+        P.splitk = pl.splitk; P.b_slot_bytes = b_slot_bytes; P.bufs = bufs; P.one = 1u;
+        G.K[i] = integer_k(shards[i].k_times_2);
+        G.cta_begin[i] = ctas;
+        ctas += (shards[i].oc / ts::kOcCta) * pl.splitk;
+        const size_t sm = ts::smem_bytes(G.K[i], bufs, b_slot_bytes);
+        smem = sm > smem ? sm : smem;
+        const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
+        const cuuint64_t gstr[1] = {(cuuint64_t)ic * 2};
+        const cuuint32_t box[2] = {64u, (cuuint32_t)npad};
+        const cuuint32_t estr[2] = {1, 1};
+        if (enc(&maps.m[i], CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, base + pl.xh_off[i], gdim, gstr, box, estr,
+                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return EXL3_E_LAUNCH;
+    }
+    G.cta_begin[nshards] = ctas;
+    for (int i = nshards; i < EXL3_MAX_SHARDS; ++i) maps.m[i] = maps.m[0];
+    if (smem > 226 * 1024) return EXL3_E_SHAPE;
+    if (cudaFuncSetAttribute(ts::gemm_ts_grouped_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    if (launch_pdl(ts::gemm_ts_grouped_kernel, dim3((unsigned)ctas), dim3(ts::kThreads), smem, st, maps, G) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+
+    // 3. slices summed, output rotation, signs, residual, fp16 into the shards' column blocks
+    ReduceGroup RG;
+    RG.nshards = nshards;
+    long long nb = 0;
+    for (int i = 0; i < nshards; ++i) {
+        RG.blk_begin[i] = nb;
+        nb += (long long)rows * (shards[i].oc / 128);
+        RG.partial[i] = reinterpret_cast<const float *>(base + pl.partial_off[i]);
+        RG.svh[i] = static_cast<const __half *>(shards[i].svh);
+        RG.splitk[i] = pl.splitk;
+        RG.blocks_per_row[i] = shards[i].oc / 128;
+        RG.out_col[i] = shards[i].out_col;
+        RG.slice_elems[i] = (long long)rows * shards[i].oc;
+    }
+    RG.blk_begin[nshards] = nb;
+    if (launch_pdl(reduce_had_grouped_kernel, dim3((unsigned)((nb + 7) / 8)), dim3(256), 0, st, RG, static_cast<__half *>(y), ldy,
+                   residual, ld_res) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    return EXL3_OK;
+}
+

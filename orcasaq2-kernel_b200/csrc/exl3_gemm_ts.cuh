@@ -96,10 +96,10 @@ __device__ __forceinline__ void decode_pack(const uint32_t (&wd)[K + 1], uint32_
             }
 }
 
+// The work of one CTA: output block `bx` (256 channels) and input slice `by` of one shard.
 template <int K>
-__global__ void __launch_bounds__(kThreads, 1)
-gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
-    extern __shared__ unsigned char smem_dyn[];
+__device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P, const int bx, const int by,
+                                        unsigned char *smem_dyn) {
     unsigned char *smem = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);
     constexpr int kRawWords = 16 * 8 * K;                  // one tile row of the CTA's sixteen tiles
     constexpr uint32_t kRawBytes = kRawWords * 4;
@@ -112,8 +112,8 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     unsigned *const status = &tc::g_tc_status;
     // slice of the input dimension, in units of four tile rows (one per decode group)
     const int units = P.ic / 64;
-    const int u0 = (int)((long long)blockIdx.y * units / P.splitk);
-    const int u1 = (int)((long long)(blockIdx.y + 1) * units / P.splitk);
+    const int u0 = (int)((long long)by * units / P.splitk);
+    const int u1 = (int)((long long)(by + 1) * units / P.splitk);
     const int r0 = 4 * u0;                 // first tile row
     const int nper = u1 - u0;              // rounds = tile rows per group
 
@@ -143,7 +143,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         // copy holds the warp for about a quarter of a microsecond, and four diverged lanes would pay it
         // four times per round (measured: that alone bounded the kernel at ~1500 cycles per round).
         const int g = lane & 3;
-        const uint32_t *src = P.trellis + ((size_t)(r0 + g) * P.tiles_j + (size_t)blockIdx.x * 16) * (size_t)(8 * K);
+        const uint32_t *src = P.trellis + ((size_t)(r0 + g) * P.tiles_j + (size_t)bx * 16) * (size_t)(8 * K);
         const size_t src_step = (size_t)4 * P.tiles_j * (8 * K);
         bool ok = true;
         Cursor rc(0, kRawDepth);
@@ -170,7 +170,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
                 if (!ok) break;
                 const uint32_t bar = s32(&S.full[bc.idx]);
                 mbar_expect_tx(bar, box_bytes);
-                tma_2d(s32(smB + (size_t)bc.idx * P.b_slot_bytes), &xmap, 64 * (u0 + j), 0, bar);
+                tma_2d(s32(smB + (size_t)bc.idx * P.b_slot_bytes), xmap, 64 * (u0 + j), 0, bar);
             }
         }
     } else if (warp == 1 || warp == kWarpMmaY) {
@@ -207,7 +207,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             umma_commit(s32(&S.acc_full));
 #ifdef EXL3_TC_TRACE
             if (warp == 1) {
-                const int cta = blockIdx.x + gridDim.x * blockIdx.y;
+                const int cta = bx + (P.oc / kOcCta) * by;
                 if (cta < 4096) {
                     for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][1][i] = tc_acc[i];
                     tc::g_tc_trace[cta][1][4] = (unsigned long long)(clock64() - tc_begin);
@@ -308,7 +308,7 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         announce();
 #ifdef EXL3_TC_TRACE
         if (lane == 0) {
-            const int cta = blockIdx.x + gridDim.x * blockIdx.y;
+            const int cta = bx + (P.oc / kOcCta) * by;
             if (cta < 4096) {
                 for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][warp][i] = tc_acc[i];
                 tc::g_tc_trace[cta][warp][4] = (unsigned long long)(clock64() - tc_begin);
@@ -327,13 +327,13 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             uint32_t v[16];
             tmem_ld_32x32b_x16(tmem + lane_base + (uint32_t)(R * P.npad + c0), v);
             const int a = 2 * R + (lane >> 4);
-            const int oc_idx = blockIdx.x * kOcCta + 64 * quad + 16 * (gg >> 1) + 4 * a + 2 * hi8 + (gg & 1);
+            const int oc_idx = bx * kOcCta + 64 * quad + 16 * (gg >> 1) + 4 * a + 2 * hi8 + (gg & 1);
             if (ok) {
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = c0 + j;
                     if (tok < P.tokens) {
-                        P.partial[((size_t)blockIdx.y * P.tokens + tok) * P.oc + oc_idx] = __uint_as_float(v[j]);
+                        P.partial[((size_t)by * P.tokens + tok) * P.oc + oc_idx] = __uint_as_float(v[j]);
                     }
                 }
             }
@@ -348,10 +348,53 @@ gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     }
 }
 
+
+template <int K>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ts_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
+    extern __shared__ unsigned char smem_dyn[];
+    ts_body<K>(&xmap, P, blockIdx.x, blockIdx.y, smem_dyn);
+}
+
+// All shards of a fused layer in one launch: CTAs are numbered shard by shard (output block fastest),
+// every shard brings its own bitrate, tensor map (its own rotated activations) and partial sums.
+struct GroupArgs {
+    int nshards;
+    int cta_begin[EXL3_MAX_SHARDS + 1];
+    int K[EXL3_MAX_SHARDS];
+    Params p[EXL3_MAX_SHARDS];
+};
+struct MapPack {
+    CUtensorMap m[EXL3_MAX_SHARDS];
+};
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_ts_grouped_kernel(const __grid_constant__ MapPack maps, const __grid_constant__ GroupArgs G) {
+    extern __shared__ unsigned char smem_dyn[];
+    int s = 0;
+    while (s + 1 < G.nshards && (int)blockIdx.x >= G.cta_begin[s + 1]) ++s;
+    const Params &P = G.p[s];
+    const int local = blockIdx.x - G.cta_begin[s];
+    const int ux = P.oc / kOcCta;
+    const int bx = local % ux, by = local / ux;
+    switch (G.K[s]) {
+        case 1: ts_body<1>(&maps.m[s], P, bx, by, smem_dyn); break;
+        case 2: ts_body<2>(&maps.m[s], P, bx, by, smem_dyn); break;
+        case 3: ts_body<3>(&maps.m[s], P, bx, by, smem_dyn); break;
+        case 4: ts_body<4>(&maps.m[s], P, bx, by, smem_dyn); break;
+        case 5: ts_body<5>(&maps.m[s], P, bx, by, smem_dyn); break;
+        case 6: ts_body<6>(&maps.m[s], P, bx, by, smem_dyn); break;
+        case 7: ts_body<7>(&maps.m[s], P, bx, by, smem_dyn); break;
+        default: ts_body<8>(&maps.m[s], P, bx, by, smem_dyn); break;
+    }
+}
+
+__host__ __device__ constexpr size_t smem_bytes(int K, int bufs, int b_slot_bytes) {
+    return (size_t)bufs * b_slot_bytes + 1024 /*barriers*/ + (size_t)kGroups * raw_depth(K) * (16 * 8 * K) * 4 + 1024 /*alignment*/;
+}
+
 template <int K>
 static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
-    const size_t raw = (size_t)kGroups * raw_depth(K) * (16 * 8 * K) * 4;
-    const size_t smem = (size_t)P.bufs * P.b_slot_bytes + 1024 /*barriers*/ + raw + 1024 /*alignment*/;
+    const size_t smem = smem_bytes(K, P.bufs, P.b_slot_bytes);
     if (smem > 226 * 1024) return EXL3_E_SHAPE;
     if (cudaFuncSetAttribute(gemm_ts_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
         cudaGetLastError();

@@ -74,6 +74,11 @@ def lib():
                 L.exl3_gemm_tc_ex.argtypes = [vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ci, ci,
                                               ctypes.POINTER(Exl3GemvFusion), vp]
                 L.exl3_gemm_tc_ex.restype = ci
+                L.exl3_gemm_tc_grouped_scratch_bytes.restype = sz
+                L.exl3_gemm_tc_grouped_scratch_bytes.argtypes = [ctypes.POINTER(Exl3Shard), ci, ci, ci]
+                L.exl3_gemm_tc_grouped.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp, sz, ci,
+                                                   ctypes.POINTER(Exl3GemvFusion), vp]
+                L.exl3_gemm_tc_grouped.restype = ci
                 L.exl3_gemm_tc_status.restype = ctypes.c_uint
                 L.exl3_gemv_static_capacity.restype = sz
                 L.exl3_gemv_grouped_static.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp]
@@ -372,6 +377,39 @@ def gemm_tc(x: torch.Tensor, trellis: torch.Tensor, y: torch.Tensor, suh: torch.
             y.copy_(tmp)
         return
     _check(rc, "exl3_gemm_tc_ex")
+
+
+def gemm_tc_grouped(x: torch.Tensor, shards, y: torch.Tensor, in_mode: int = IN_PLAIN, norm_weight=None,
+                    eps: float = 1e-6, residual=None) -> bool:
+    """All shards of a fused layer at 17..128 rows in three launches (the grouped form of gemm_tc): shard s
+    writes y[:, out_col_s : out_col_s + oc_s].  Returns False, having done nothing, when the shapes are
+    outside what the grouped kernel takes (more than 128 rows, an oc that is not a multiple of 256);
+    the caller then goes shard by shard."""
+    _rows_view(x, "x", _DT)
+    _rows_view(y, "y", torch.float16)
+    rows = x.shape[0]
+    ic = x.shape[1] // 2 if in_mode == IN_SILU_MUL else x.shape[1]
+    arr = _shard_array(x, shards, ic)
+    L = lib()
+    nbytes = L.exl3_gemm_tc_grouped_scratch_bytes(arr, len(shards), rows, ic)
+    if nbytes == 0:
+        return False
+    if y.shape[0] != rows:
+        raise RuntimeError("gemm_tc_grouped: y has a different number of rows than x")
+    if norm_weight is not None:
+        _cuda(norm_weight, "norm_weight", torch.float16)
+    if residual is not None:
+        _rows_view(residual, "residual", torch.float16)
+        if residual.shape != y.shape:
+            raise RuntimeError("residual must have the shape of y")
+    scratch = torch.empty((nbytes,), dtype=torch.uint8, device=x.device)
+    fus = Exl3GemvFusion(in_mode, None if norm_weight is None else norm_weight.data_ptr(), float(eps), x.stride(0),
+                         None if residual is None else residual.data_ptr(),
+                         0 if residual is None else residual.stride(0))
+    _check(L.exl3_gemm_tc_grouped(arr, len(shards), x.data_ptr(), y.data_ptr(), rows, ic, y.stride(0),
+                                  scratch.data_ptr(), nbytes, int(x.dtype == torch.bfloat16), ctypes.byref(fus),
+                                  _stream(x)), "exl3_gemm_tc_grouped")
+    return True
 
 
 def gemm_tc_status() -> int:

@@ -89,11 +89,13 @@ def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Te
         return y
     n = len(trellis)
     if rows > _ext.GEMV_MAX_ROWS and USE_TC and rows <= TC_MAX_ROWS:
-        col = 0
-        for i in range(n):
-            # every shard writes its own column block of y (no torch.cat, reference config.py:242)
-            _ext.gemm_tc(x, trellis[i], y[:, col:col + ocs[i]], suh[i], svh[i], mcg[i], mul1[i])
-            col += ocs[i]
+        shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i]) for i in range(n)]
+        if not (n <= _ext.MAX_SHARDS and _ext.gemm_tc_grouped(x, shards, y)):    # one grouped launch where it applies
+            col = 0
+            for i in range(n):
+                # every shard writes its own column block of y (no torch.cat, reference config.py:242)
+                _ext.gemm_tc(x, trellis[i], y[:, col:col + ocs[i]], suh[i], svh[i], mcg[i], mul1[i])
+                col += ocs[i]
     elif rows <= GEMM_MAX_ROWS:
         shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i])
                   for i in range(n)]

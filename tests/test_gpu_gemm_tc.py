@@ -113,3 +113,54 @@ def test_gemm_tc_fused_silu_mul(ext, rows, ic, oc, K):
     ref = _dense_ref(ext, act, trg, sug, svg, K).float()
     assert ext.gemm_tc_status() == 0
     assert (y.float() - ref).abs().max() / ref.abs().max() < 5e-3
+
+
+@pytest.mark.parametrize("rows", [17, 64, 128])
+def test_gemm_tc_grouped_fused_layer(ext, coracle, rows):
+    """Three shards with different bitrates in one grouped launch (the mid-batch form of a fused
+    qkv_proj), plain and with RMSNorm + residual, against the oracle and the single-shard calls."""
+    ic, spec = 512, [(768, 4), (256, 5), (256, 6)]
+    shards, refs, col = [], [], 0
+    x = None
+    for i, (oc, K) in enumerate(spec):
+        tr, suh, svh, xi = R.make_layer(40 * rows + i, ic, oc, K, rows)
+        x = xi if x is None else x
+        shards.append(dict(trellis=tr.cuda(), suh=suh.cuda(), svh=svh.cuda(), mcg=False, mul1=False, out_col=col))
+        refs.append((tr, suh, svh))
+        col += oc
+    xg = x.half().cuda()
+    y = torch.full((rows, col), float("nan"), dtype=torch.half, device="cuda")
+    assert ext.gemm_tc_grouped(xg, shards, y)
+    torch.cuda.synchronize()
+    assert ext.gemm_tc_status() == 0
+    xf = x.half().numpy()
+    ref = np.concatenate([coracle.layer(xf, coracle.reconstruct(tr.numpy()), suh.numpy(), svh.numpy()) for tr, suh, svh in refs], 1)
+    got = y.float().cpu().numpy().astype(np.float64)
+    assert np.abs(got - ref).max() / np.abs(ref).max() <= MAX_REL_ERR
+    # identical to the single-shard kernel, shard by shard
+    y1 = torch.empty_like(y)
+    for s, (oc, K) in zip(shards, spec):
+        ext.gemm_tc(xg, s["trellis"], y1[:, s["out_col"]:s["out_col"] + oc], s["suh"], s["svh"])
+    assert torch.equal(y, y1)
+    # fused RMSNorm and in-place residual
+    g = torch.Generator().manual_seed(9)
+    gamma = (1.0 + 0.1 * torch.randn(ic, generator=g)).half().cuda()
+    acc = torch.randn((rows, col), generator=g).half().cuda()
+    acc1 = acc.clone()
+    assert ext.gemm_tc_grouped(xg, shards, acc, in_mode=ext.IN_RMSNORM, norm_weight=gamma, eps=1e-5, residual=acc)
+    for s, (oc, K) in zip(shards, spec):
+        blk = acc1[:, s["out_col"]:s["out_col"] + oc]
+        ext.gemm_tc(xg, s["trellis"], blk, s["suh"], s["svh"], in_mode=ext.IN_RMSNORM, norm_weight=gamma, eps=1e-5, residual=blk)
+    assert torch.equal(acc, acc1)
+
+
+def test_gemm_tc_grouped_declines_other_shapes(ext):
+    tr, suh, svh, x = R.make_layer(7, 256, 128, 4, 32)
+    sh = [dict(trellis=tr.cuda(), suh=suh.cuda(), svh=svh.cuda(), mcg=False, mul1=False)]
+    y = torch.zeros((32, 128), dtype=torch.half, device="cuda")
+    assert ext.gemm_tc_grouped(x.half().cuda(), sh, y) is False          # oc is not a multiple of 256
+    tr, suh, svh, x = R.make_layer(8, 256, 256, 4, 200)
+    sh = [dict(trellis=tr.cuda(), suh=suh.cuda(), svh=svh.cuda(), mcg=False, mul1=False)]
+    y = torch.zeros((200, 256), dtype=torch.half, device="cuda")
+    assert ext.gemm_tc_grouped(x.half().cuda(), sh, y) is False          # more than 128 rows
+    assert float(y.abs().max()) == 0.0
