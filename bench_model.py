@@ -31,6 +31,7 @@ import torch.distributed as dist  # noqa: E402
 import torch.nn.functional as F  # noqa: E402
 
 HIDDEN, FFN, LAYERS, QH, KVH, HD, VOCAB = 5120, 17408, 64, 24, 4, 256, 151936
+TC_FROM_ROWS = 9           # batch sizes from here on take the tcgen05 path (--tc-from; measured faster from 9 rows)
 
 
 def rand_shard(ic, oc, K, dev, gen):
@@ -57,7 +58,7 @@ class Linear:
     def __call__(self, x, in_mode=0, residual=None, out=None):
         """in_mode: 0 plain, 1 RMSNorm(x), 2 silu(x[:, :ic]) * x[:, ic:]; `residual` is added to the
         result (fused into the GEMV for <= 16 rows, into the pre- and post-pass of the tcgen05 path above)."""
-        if self.rows <= self.ext.GEMV_MAX_ROWS:
+        if self.rows < TC_FROM_ROWS:
             out = self.out if out is None else out
             self.ext.gemv_grouped(x, self.shards, out, in_mode=in_mode, residual=residual)
             return out
@@ -66,6 +67,9 @@ class Linear:
         out = self.out if out is None else out
         if self.ext.gemm_tc_grouped(x, self.shards, out, in_mode=in_mode, residual=residual):
             return out                                  # one grouped launch (up to 128 rows, oc % 256 == 0)
+        if self.rows <= self.ext.GEMV_MAX_ROWS:
+            self.ext.gemv_grouped(x, self.shards, out, in_mode=in_mode, residual=residual)
+            return out
         for s in self.shards:
             c0 = s["out_col"]
             self.ext.gemm_tc(x, s["trellis"], out[:, c0:c0 + s["oc"]], s["suh"], s["svh"], in_mode=in_mode,
@@ -109,7 +113,10 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for a quick functional run")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--tc-from", type=int, default=9, help="smallest batch that takes the tcgen05 path (9..17)")
     args = ap.parse_args()
+    global TC_FROM_ROWS
+    TC_FROM_ROWS = max(9, min(17, args.tc_from))
     world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)

@@ -6,7 +6,7 @@ used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, wr
 into the concatenated output.
 
 Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
-streaming of the packed trellis).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
+streaming of the packed trellis; from 9 rows the tensor-memory kernel below takes the shapes it serves).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
 packed weights with no dense copy in memory -- up to 128 rows (and a multiple of 256 output
 channels) the decoded weights go from registers into tensor memory and are the A operand of
 tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
@@ -88,17 +88,19 @@ def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Te
     if rows == 0:
         return y
     n = len(trellis)
-    if rows > _ext.GEMV_MAX_ROWS and USE_TC and rows <= TC_MAX_ROWS:
-        shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i]) for i in range(n)]
-        if not (n <= _ext.MAX_SHARDS and _ext.gemm_tc_grouped(x, shards, y)):    # one grouped launch where it applies
-            col = 0
-            for i in range(n):
-                # every shard writes its own column block of y (no torch.cat, reference config.py:242)
-                _ext.gemm_tc(x, trellis[i], y[:, col:col + ocs[i]], suh[i], svh[i], mcg[i], mul1[i])
-                col += ocs[i]
+    shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i]) for i in range(n)]
+    # 9 rows and up: one grouped launch of the tensor-memory kernel where its shapes apply (measured faster
+    # than the grouped GEMV from 9 rows on); it declines other shapes without doing anything
+    if (USE_TC and TC_MIN_ROWS_SINGLE <= rows <= TC_MAX_ROWS and n <= _ext.MAX_SHARDS
+            and _ext.gemm_tc_grouped(x, shards, y)):
+        pass
+    elif rows > _ext.GEMV_MAX_ROWS and USE_TC and rows <= TC_MAX_ROWS:
+        col = 0
+        for i in range(n):
+            # every shard writes its own column block of y (no torch.cat, reference config.py:242)
+            _ext.gemm_tc(x, trellis[i], y[:, col:col + ocs[i]], suh[i], svh[i], mcg[i], mul1[i])
+            col += ocs[i]
     elif rows <= GEMM_MAX_ROWS:
-        shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i])
-                  for i in range(n)]
         for g0 in range(0, n, _ext.MAX_SHARDS):
             grp = shards[g0:g0 + _ext.MAX_SHARDS]
             col0 = sum(ocs[:g0])
