@@ -66,7 +66,7 @@ class Linear:
         # activation rides in its activation pre-pass, the residual add in its post-pass
         out = self.out if out is None else out
         if self.ext.gemm_tc_grouped(x, self.shards, out, in_mode=in_mode, residual=residual):
-            return out                                  # one grouped launch (up to 128 rows, oc % 256 == 0)
+            return out                                  # one grouped launch (up to 128 rows)
         if self.rows <= self.ext.GEMV_MAX_ROWS:
             self.ext.gemv_grouped(x, self.shards, out, in_mode=in_mode, residual=residual)
             return out

@@ -145,7 +145,7 @@ int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, c
  * exl3_gemv_fusion) runs inside the activation pre-pass, the residual add inside the output
  * post-pass, and y may be a column block of a wider matrix: row pitch ldy >= oc elements, a multiple
  * of 4 (this is what removes the torch.cat of orcasaq2/config.py:236-242 for fused layers).
- * fusion == NULL and ldy == oc is exl3_gemm_tc.  Up to 128 rows with oc a multiple of 256 every
+ * fusion == NULL and ldy == oc is exl3_gemm_tc.  Up to 128 rows every
  * combination is served; beyond that a pitch or a residual is refused with EXL3_E_UNSUPPORTED when
  * the shape runs unsplit (the caller then applies them itself).
  */
@@ -155,8 +155,8 @@ int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, const void *suh
 /*
  * All shards of a fused layer (qkv_proj, gate_up_proj) at up to 128 rows in three launches: the
  * grouped form of exl3_gemm_tc_ex, as exl3_gemv_grouped is of exl3_gemv.  y is [rows][ldy]; shard s
- * writes columns out_col .. out_col + oc.  Every shard needs oc a multiple of 256; otherwise, and
- * above 128 rows, EXL3_E_UNSUPPORTED (scratch size 0) and the caller goes shard by shard.
+ * writes columns out_col .. out_col + oc.  Above 128 rows:
+ * EXL3_E_UNSUPPORTED (scratch size 0) and the caller goes shard by shard.
  * Replaces the per-shard loop + torch.cat of orcasaq2/config.py:236-242.
  */
 size_t exl3_gemm_tc_grouped_scratch_bytes(const exl3_shard *shards, int nshards, int rows, int ic);

@@ -866,11 +866,10 @@ static int plan_group(const exl3_shard *sh, int n, int rows, int ic, GroupPlan &
     int units = 0;
     for (int i = 0; i < n; ++i) {
         if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
-        if (sh[i].oc % kOcCta) return EXL3_E_UNSUPPORTED;
         if (sh[i].mcg || sh[i].mul1 || !integer_k(sh[i].k_times_2)) return EXL3_E_UNSUPPORTED;
         if (!sh[i].trellis || !sh[i].suh || !sh[i].svh) return EXL3_E_NULL;
         if (!aligned(sh[i].trellis, 16) || !aligned(sh[i].suh, 8) || !aligned(sh[i].svh, 8)) return EXL3_E_ALIGN;
-        units += sh[i].oc / kOcCta;
+        units += (sh[i].oc + kOcCta - 1) / kOcCta;
     }
     // every shard has the same input size, hence the same work per output block: one slice count for all
     int sk = 148 / units;
@@ -957,7 +956,7 @@ extern "C" int exl3_gemm_tc_grouped(const exl3_shard *shards, int nshards, const
         P.splitk = pl.splitk; P.b_slot_bytes = b_slot_bytes; P.bufs = bufs; P.one = 1u;
         G.K[i] = integer_k(shards[i].k_times_2);
         G.cta_begin[i] = ctas;
-        ctas += (shards[i].oc / ts::kOcCta) * pl.splitk;
+        ctas += ((shards[i].oc + ts::kOcCta - 1) / ts::kOcCta) * pl.splitk;
         const size_t sm = ts::smem_bytes(G.K[i], bufs, b_slot_bytes);
         smem = sm > smem ? sm : smem;
         const cuuint64_t gdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};

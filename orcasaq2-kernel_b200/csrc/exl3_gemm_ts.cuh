@@ -14,7 +14,8 @@
 // is organised to need few of them: a ROUND is four tile rows (64 input channels, one tile row per
 // decode group), and costs each of the two issuing threads one wait, one fence, four MMAs and one commit.
 //
-// CTA = 256 output channels x a slice of the input channels x up to 128 tokens, one CTA per SM:
+// CTA = 256 output channels (128 in the last block of an odd width) x a slice of the input channels x up
+// to 128 tokens, one CTA per SM:
 //   warp 0        lanes 0..3: packed trellis of the four decode groups (1-D bulk copies into
 //                 per-group rings)
 //   warp 19       activation tiles (2-D tiled TMA, 128-byte swizzle), one per round
@@ -145,6 +146,10 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
         const int g = lane & 3;
         const uint32_t *src = P.trellis + ((size_t)(r0 + g) * P.tiles_j + (size_t)bx * 16) * (size_t)(8 * K);
         const size_t src_step = (size_t)4 * P.tiles_j * (8 * K);
+        // the last block of a shard whose width is an odd multiple of 128 has eight tiles: the upper two
+        // lane quarters then decode whatever the ring holds, into accumulator rows that are never read
+        const int ntiles = min(16, P.tiles_j - bx * 16);
+        const uint32_t row_bytes = (uint32_t)ntiles * (8 * K) * 4;
         bool ok = true;
         Cursor rc(0, kRawDepth);
         for (int s = 0; s < nper; ++s, rc.advance(1)) {
@@ -153,8 +158,8 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
             if (!ok) break;
             if (lane < kGroups) {
                 const uint32_t bar = s32(&S.raw_full[g][rc.idx]);
-                mbar_expect_tx(bar, kRawBytes);
-                bulk_g2s(s32(raw + (size_t)(g * kRawDepth + rc.idx) * kRawWords), src + (size_t)s * src_step, kRawBytes, bar);
+                mbar_expect_tx(bar, row_bytes);
+                bulk_g2s(s32(raw + (size_t)(g * kRawDepth + rc.idx) * kRawWords), src + (size_t)s * src_step, row_bytes, bar);
             }
         }
     } else if (warp == kWarpActs) {
@@ -207,7 +212,7 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
             umma_commit(s32(&S.acc_full));
 #ifdef EXL3_TC_TRACE
             if (warp == 1) {
-                const int cta = bx + (P.oc / kOcCta) * by;
+                const int cta = bx + ((P.oc + kOcCta - 1) / kOcCta) * by;
                 if (cta < 4096) {
                     for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][1][i] = tc_acc[i];
                     tc::g_tc_trace[cta][1][4] = (unsigned long long)(clock64() - tc_begin);
@@ -308,7 +313,7 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
         announce();
 #ifdef EXL3_TC_TRACE
         if (lane == 0) {
-            const int cta = bx + (P.oc / kOcCta) * by;
+            const int cta = bx + ((P.oc + kOcCta - 1) / kOcCta) * by;
             if (cta < 4096) {
                 for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][warp][i] = tc_acc[i];
                 tc::g_tc_trace[cta][warp][4] = (unsigned long long)(clock64() - tc_begin);
@@ -332,7 +337,7 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
 #pragma unroll
                 for (int j = 0; j < 16; ++j) {
                     const int tok = c0 + j;
-                    if (tok < P.tokens) {
+                    if (tok < P.tokens && oc_idx < P.oc) {
                         P.partial[((size_t)by * P.tokens + tok) * P.oc + oc_idx] = __uint_as_float(v[j]);
                     }
                 }
@@ -374,7 +379,7 @@ gemm_ts_grouped_kernel(const __grid_constant__ MapPack maps, const __grid_consta
     while (s + 1 < G.nshards && (int)blockIdx.x >= G.cta_begin[s + 1]) ++s;
     const Params &P = G.p[s];
     const int local = blockIdx.x - G.cta_begin[s];
-    const int ux = P.oc / kOcCta;
+    const int ux = (P.oc + kOcCta - 1) / kOcCta;
     const int bx = local % ux, by = local / ux;
     switch (G.K[s]) {
         case 1: ts_body<1>(&maps.m[s], P, bx, by, smem_dyn); break;
@@ -400,7 +405,7 @@ static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
     }
-    dim3 grid(P.oc / kOcCta, P.splitk);
+    dim3 grid((P.oc + kOcCta - 1) / kOcCta, P.splitk);
     if (launch_pdl(gemm_ts_kernel<K>, grid, dim3(kThreads), smem, st, map, P) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
@@ -409,10 +414,10 @@ static int launch(const CUtensorMap &map, const Params &P, cudaStream_t st) {
 }
 
 // the shapes this path takes; everything else stays on the shared-memory kernel
-static bool eligible(int rows, int ic, int oc) { return rows <= kMaxTokens && (oc % kOcCta) == 0 && (ic % 128) == 0; }
+static bool eligible(int rows, int ic, int oc) { return rows <= kMaxTokens && (oc % 128) == 0 && (ic % 128) == 0; }
 
 static int choose_splitk(int ic, int oc) {
-    const int ctas = oc / kOcCta, units = ic / 64;
+    const int ctas = (oc + kOcCta - 1) / kOcCta, units = ic / 64;
     int sk = (148 + ctas / 2) / ctas;
     if (sk > units / 4) sk = units / 4;
     return sk < 1 ? 1 : sk;

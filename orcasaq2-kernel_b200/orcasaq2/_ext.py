@@ -383,7 +383,7 @@ def gemm_tc_grouped(x: torch.Tensor, shards, y: torch.Tensor, in_mode: int = IN_
                     eps: float = 1e-6, residual=None) -> bool:
     """All shards of a fused layer at 17..128 rows in three launches (the grouped form of gemm_tc): shard s
     writes y[:, out_col_s : out_col_s + oc_s].  Returns False, having done nothing, when the shapes are
-    outside what the grouped kernel takes (more than 128 rows, an oc that is not a multiple of 256);
+    outside what the grouped kernel takes (more than 128 rows, an unsupported codebook);
     the caller then goes shard by shard."""
     _rows_view(x, "x", _DT)
     _rows_view(y, "y", torch.float16)

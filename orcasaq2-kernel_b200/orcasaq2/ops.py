@@ -7,8 +7,7 @@ into the concatenated output.
 
 Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
 streaming of the packed trellis; from 9 rows the tensor-memory kernel below takes the shapes it serves).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
-packed weights with no dense copy in memory -- up to 128 rows (and a multiple of 256 output
-channels) the decoded weights go from registers into tensor memory and are the A operand of
+packed weights with no dense copy in memory -- up to 128 rows the decoded weights go from registers into tensor memory and are the A operand of
 tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
 weight once into a scratch buffer, dense library GEMM, rotate back.  GEMM_MAX_ROWS keeps the
 reference's name and default; it is the bound up to which the packed trellis is read directly
@@ -26,7 +25,7 @@ GEMM_MAX_ROWS = int(os.environ.get("ORCA_EXL3_GEMM_MAX_ROWS", "144"))
 USE_TC = os.environ.get("ORCA_EXL3_TC", "1") != "0"
 TC_MAX_ROWS = int(os.environ.get("ORCA_EXL3_TC_MAX_ROWS", "1023"))
 # A single shard with 9..16 rows is faster on the tensor-memory kernel than on the GEMV (measured
-# 43 us against 64 us for 5120 -> 17408 at 3 bpw); that kernel wants a multiple of 256 output channels.
+# 43 us against 64 us for 5120 -> 17408 at 3 bpw).
 TC_MIN_ROWS_SINGLE = int(os.environ.get("ORCA_EXL3_TC_MIN_ROWS", "9"))
 
 
@@ -62,7 +61,7 @@ def shard_gemm(x: Tensor, trellis: Tensor, suh: Tensor, svh: Tensor,
     y = torch.empty((rows, oc), dtype=torch.half, device=x.device)
     if rows == 0:
         return y
-    small_tc = USE_TC and TC_MIN_ROWS_SINGLE <= rows <= _ext.GEMV_MAX_ROWS and oc % 256 == 0
+    small_tc = USE_TC and TC_MIN_ROWS_SINGLE <= rows <= _ext.GEMV_MAX_ROWS
     if (rows <= _ext.GEMV_MAX_ROWS and not small_tc) or (not USE_TC and rows <= GEMM_MAX_ROWS):
         _ext.exl3_gemm(x, trellis, y, suh, x, svh, -1, mcg, mul1, 0)
     elif USE_TC and rows <= TC_MAX_ROWS:
