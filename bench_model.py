@@ -9,7 +9,7 @@ Model: 64 layers, hidden 5120, FFN 17408, 24 query / 4 KV heads of 256, vocabula
 projection (q, k, v, o, gate, up, down) gets a seeded bitrate from {2,..,6}; embed_tokens and the
 tied lm_head are one int8 table with per-row scales.  Weights are random (no checkpoint is
 involved); the KV cache is filled with random values for `ctx` tokens.  One step = one decoded
-token per sequence: RMSNorm, fused qkv GEMV, rotary, attention over the cache (library SDPA), o_proj,
+token per sequence: RMSNorm, fused qkv GEMV, rotary, attention over the cache (exl3_decode_attn; --attn sdpa for torch's), o_proj,
 RMSNorm, fused gate_up GEMV, SiLU*up, down_proj, final norm, int8 head, argmax.  The whole step is
 captured in a CUDA graph.  Under tensor parallelism qkv / gate_up are column-sliced, o_proj /
 down_proj row-sliced with an NCCL all-reduce after each, the head is vocabulary-sliced.
@@ -113,6 +113,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for a quick functional run")
     ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--attn", choices=["own", "sdpa"], default="own",
+                    help="decode attention: this library's kernel, or torch's scaled_dot_product_attention")
     ap.add_argument("--tc-from", type=int, default=9, help="smallest batch that takes the tcgen05 path (9..17)")
     args = ap.parse_args()
     global TC_FROM_ROWS
@@ -146,7 +148,10 @@ def main():
             v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
             kc[:, :, ctx] = k
             vc[:, :, ctx] = v
-            att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
+            if args.attn == "sdpa":
+                att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
+            else:
+                att = _ext.decode_attn(q, kc, vc, ctx + 1)                # [B, qh, HD], split-KV kernel of this library
             if world > 1:
                 a = o(att.reshape(B, qh * HD))
                 dist.all_reduce(a)
@@ -208,7 +213,7 @@ def main():
             "cuda_graph": graph is not None, "status_word": _ext.workspace_status(dev),
             "per_gpu_bytes_per_step": {"packed_weights": wbytes, "kv_cache": kvbytes},
             "per_gpu_hbm_gbs": round(per_gpu, 1), "frac_of_measured_hbm": round(per_gpu / peak, 4),
-            "data": "synthetic (random-init weights, random KV cache)", "attention": "torch SDPA (library)",
+            "data": "synthetic (random-init weights, random KV cache)", "attention": "exl3_decode_attn" if args.attn == "own" else "torch SDPA (library)",
         }), flush=True)
     if world > 1:
         # leave without tearing down NCCL under a live captured graph (that teardown can block)

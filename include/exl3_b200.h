@@ -220,6 +220,27 @@ int exl3_int8_embed(const void *qweight, const void *scales, const void *ids, vo
 int exl3_int8_head(const void *qweight, const void *scales, const void *x, void *logits, int rows,
                    int vocab, int hidden, long long ld_logits, int is_bf16, void *stream);
 
+/*
+ * Decode attention over a contiguous fp16 KV cache: one query token per sequence,
+ *     out[b][h][:] = softmax(q[b][h] . K[b][h / G]^T * scale) . V[b][h / G],   G = q_heads / kv_heads.
+ * The reference has no attention code of its own: it leaves this step to the serving engine
+ * (presets/16gb.env:17-18 pick the engine's attention backend), and it is the largest HBM stream
+ * of a decode step next to the quantised weights, so the model-level benchmark needs it.
+ *   q, out       [batch][q_heads][256] fp16, batches q_batch_stride / out_batch_stride elements apart
+ *   k_cache, v_cache   [batch][kv_heads][capacity][256] fp16: element strides kv_batch_stride and
+ *                kv_head_stride (multiples of 8), 16-byte aligned; tokens 0 .. seq_len-1 are read
+ *   head_dim     must be 256; G must be 1..8
+ *   workspace    exl3_decode_attn_workspace_bytes(...) bytes, 16-byte aligned (partial results of
+ *                the sequence splits); may be NULL when that size is 0
+ * Query head h uses KV head h / G (consecutive query heads share a KV head).  fp32 accumulation,
+ * probabilities rounded to fp16 before the product with V.
+ */
+size_t exl3_decode_attn_workspace_bytes(int batch, int q_heads, int kv_heads, int seq_len);
+int exl3_decode_attn(const void *q, const void *k_cache, const void *v_cache, void *out,
+                     void *workspace, size_t workspace_bytes, int batch, int q_heads, int kv_heads,
+                     int head_dim, int seq_len, long long q_batch_stride, long long out_batch_stride,
+                     long long kv_batch_stride, long long kv_head_stride, float scale, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,6 +6,7 @@
     python kernel_bench.py int8_head --rows 1 [--vocab 151936 --hidden 5120 --bf16]
     python kernel_bench.py int8_embed --rows 4096
     python kernel_bench.py had --rows 8192 --ic 5120
+    python kernel_bench.py attn --rows 32 --ctx 4096 [--qh 24 --kvh 4 --sdpa]   # decode attention, rows = batch
     python kernel_bench.py prefill        # BASELINE config 3: both shapes, M = 512 / 2048 / 8192
     python kernel_bench.py shards         # BASELINE configs 1 and 2: every shard, rows 1 / 4 / 16
 
@@ -146,10 +147,30 @@ def bench_had(rows, n, iters):
     return dict(kernel="had_r_128", rows=rows, n=n, us=round(t * 1e6, 1), GBs=round(rows * n * 4 / t / 1e9, 1))
 
 
+def bench_attn(batch, qh, kvh, ctx, iters, sdpa):
+    """Decode attention over `ctx` cached tokens; the caches are rotated so that every launch reads HBM."""
+    per = 2 * batch * kvh * ctx * 256 * 2
+    n = int(min(8, max(2, 400e6 // per + 1)))
+    kcs = [torch.randn(batch, kvh, ctx, 256, device=DEV).half() for _ in range(n)]
+    vcs = [torch.randn(batch, kvh, ctx, 256, device=DEV).half() for _ in range(n)]
+    q = torch.randn(batch, qh, 256, device=DEV).half()
+    o = torch.empty_like(q)
+    t = timeit(lambda i: _ext.decode_attn(q, kcs[i % n], vcs[i % n], ctx, out=o), max(iters, 2 * n), period=n)
+    b = per + 2 * q.numel() * 2
+    r = dict(kernel="decode_attn", batch=batch, q_heads=qh, kv_heads=kvh, ctx=ctx, us=round(t * 1e6, 1),
+             GBs=round(b / t / 1e9, 1))
+    if sdpa:
+        import torch.nn.functional as F
+        ts = timeit(lambda i: F.scaled_dot_product_attention(q.unsqueeze(2), kcs[i % n], vcs[i % n], enable_gqa=True),
+                    max(iters, 2 * n), period=n)
+        r.update(torch_sdpa_us=round(ts * 1e6, 1), torch_sdpa_GBs=round(b / ts / 1e9, 1))
+    return r
+
+
 def main():
     global DEV
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm_tc", "reconstruct", "int8_head", "int8_embed", "had", "prefill", "shards"])
+    ap.add_argument("what", choices=["gemv", "gemm_tc", "reconstruct", "int8_head", "int8_embed", "had", "prefill", "shards", "attn"])
     ap.add_argument("--ic", type=int, default=5120)
     ap.add_argument("--oc", type=int, default=17408)
     ap.add_argument("--k", type=int, default=4)
@@ -157,6 +178,10 @@ def main():
     ap.add_argument("--vocab", type=int, default=151936)
     ap.add_argument("--hidden", type=int, default=5120)
     ap.add_argument("--bf16", action="store_true")
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--qh", type=int, default=24)
+    ap.add_argument("--kvh", type=int, default=4)
+    ap.add_argument("--sdpa", action="store_true", help="attn: also time torch's scaled_dot_product_attention")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph")
     a = ap.parse_args()
@@ -179,6 +204,8 @@ def main():
         out.append(bench_int8_embed(a.vocab, a.hidden, a.rows, a.bf16, a.iters))
     elif a.what == "had":
         out.append(bench_had(a.rows, a.ic, a.iters))
+    elif a.what == "attn":
+        out.append(bench_attn(a.rows, a.qh, a.kvh, a.ctx, a.iters, a.sdpa))
     elif a.what == "prefill":
         for ic, oc, K in ((5120, 17408, 3), (17408, 5120, 4)):
             for m in (512, 2048, 8192):

@@ -83,6 +83,10 @@ def lib():
                 L.exl3_gemv_static_capacity.restype = sz
                 L.exl3_gemv_grouped_static.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp]
                 L.exl3_gemv_grouped_static.restype = ci
+                L.exl3_decode_attn_workspace_bytes.restype = sz
+                L.exl3_decode_attn_workspace_bytes.argtypes = [ci, ci, ci, ci]
+                L.exl3_decode_attn.argtypes = [vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ll, ll, ll, ll, cf, vp]
+                L.exl3_decode_attn.restype = ci
                 for name in ("exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
                              "exl3_int8_embed", "exl3_int8_head"):
                     getattr(L, name).restype = ci
@@ -414,3 +418,35 @@ def gemm_tc_grouped(x: torch.Tensor, shards, y: torch.Tensor, in_mode: int = IN_
 
 def gemm_tc_status() -> int:
     return int(lib().exl3_gemm_tc_status())
+
+
+# --------------------------------------------------------------------------- decode attention
+def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_len: int,
+                scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(q K^T * scale) V for one query token per sequence.
+
+    q [B, q_heads, 256] fp16 (last two dimensions contiguous); k_cache, v_cache [B, kv_heads, capacity, 256]
+    fp16 with contiguous rows, of which tokens 0 .. seq_len-1 are read; query head h uses KV head
+    h // (q_heads // kv_heads).  Returns [B, q_heads, 256] fp16."""
+    for t, name in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dtype != torch.float16:
+            raise RuntimeError(f"{name} must be a CUDA fp16 tensor (this build has no CPU path)")
+    if q.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape or v_cache.stride() != k_cache.stride():
+        raise RuntimeError("decode_attn: q must be [B, heads, 256], the caches [B, kv_heads, capacity, 256] with equal strides")
+    B, qh, hd = q.shape
+    kvh, cap = k_cache.shape[1], k_cache.shape[2]
+    if k_cache.shape[0] != B or k_cache.shape[3] != hd or q.stride(2) != 1 or q.stride(1) != hd \
+            or k_cache.stride(3) != 1 or k_cache.stride(2) != hd or not 0 < seq_len <= cap:
+        raise RuntimeError("decode_attn: inconsistent shapes or strides")
+    if out is None:
+        out = torch.empty((B, qh, hd), dtype=torch.float16, device=q.device)
+    elif out.shape != (B, qh, hd) or out.dtype != torch.float16 or out.stride(2) != 1 or out.stride(1) != hd:
+        raise RuntimeError("decode_attn: out must be [B, heads, 256] fp16 with contiguous heads")
+    L = lib()
+    need = L.exl3_decode_attn_workspace_bytes(B, qh, kvh, seq_len)
+    ws = torch.empty((need,), dtype=torch.uint8, device=q.device) if need else None
+    _check(L.exl3_decode_attn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                              ws.data_ptr() if ws is not None else None, need, B, qh, kvh, hd, int(seq_len),
+                              q.stride(0), out.stride(0), k_cache.stride(0), k_cache.stride(1),
+                              float(hd ** -0.5 if scale is None else scale), _stream(q)), "exl3_decode_attn")
+    return out

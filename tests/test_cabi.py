@@ -76,3 +76,24 @@ def test_gemv_plan_and_workspace(lib):
     assert lib.exl3_gemv_grouped(arr, 3, fake, fake, 1, 5120, 4096, fake, 1 << 30, None) == -1  # ldy too small
     arr[1].mul1 = 1
     assert lib.exl3_gemv_grouped(arr, 3, fake, fake, 1, 5120, 8192, fake, 1 << 30, None) == -3
+
+
+def test_decode_attn_argument_checks(lib):
+    vp, ci, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    lib.exl3_decode_attn_workspace_bytes.restype = ctypes.c_size_t
+    lib.exl3_decode_attn_workspace_bytes.argtypes = [ci] * 4
+    lib.exl3_decode_attn.argtypes = [vp] * 5 + [ctypes.c_size_t] + [ci] * 5 + [ll] * 4 + [ctypes.c_float, vp]
+    assert lib.exl3_decode_attn_workspace_bytes(1, 24, 4, 4096) > 0           # one sequence is split
+    assert lib.exl3_decode_attn_workspace_bytes(512, 24, 4, 4096) == 0        # enough sequences: no split
+    assert lib.exl3_decode_attn_workspace_bytes(1, 24, 5, 4096) == 0          # heads do not divide
+    fake = vp(4096)
+    args = lambda **kw: [kw.get("q", fake), fake, fake, fake, None, 0, kw.get("B", 512), kw.get("qh", 24),
+                         kw.get("kvh", 4), kw.get("hd", 256), kw.get("L", 64), 24 * 256, 24 * 256,
+                         4 * 64 * 256, kw.get("hs", 64 * 256), 0.0625, None]
+    assert lib.exl3_decode_attn(*args(q=None)) == -6
+    assert lib.exl3_decode_attn(*args(hd=128)) == -3
+    assert lib.exl3_decode_attn(*args(qh=40)) == -3                           # ten query heads per KV head
+    assert lib.exl3_decode_attn(*args(qh=25)) == -1
+    assert lib.exl3_decode_attn(*args(L=0)) == -1
+    assert lib.exl3_decode_attn(*args(hs=63 * 256)) == -1                     # head stride shorter than seq_len rows
+    assert lib.exl3_decode_attn(*args(B=1, L=4096, hs=4096 * 256)) == -5                     # split, but no workspace

@@ -1,0 +1,79 @@
+"""Decode attention kernel (exl3_decode_attn, through the C ABI) against an fp32 PyTorch restatement of
+softmax(q K^T / sqrt(d)) V on the same fp16 inputs.  Tolerance: fp16 output rounding plus fp16
+probabilities, max abs error <= 2e-3 * max|ref| + 1e-3 and cosine >= 0.9999."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _ref(q, kc, vc, seq_len):
+    B, qh, hd = q.shape
+    kvh = kc.shape[1]
+    G = qh // kvh
+    k = kc[:, :, :seq_len].float().repeat_interleave(G, dim=1)      # query head h -> KV head h // G
+    v = vc[:, :, :seq_len].float().repeat_interleave(G, dim=1)
+    s = torch.einsum("bhd,bhtd->bht", q.float(), k) * hd ** -0.5
+    return torch.einsum("bht,bhtd->bhd", torch.softmax(s, dim=-1), v)
+
+
+def _check(out, ref):
+    err = (out.float() - ref).abs().max().item()
+    assert err <= 2e-3 * ref.abs().max().item() + 1e-3, err
+    cos = torch.nn.functional.cosine_similarity(out.float().flatten(), ref.flatten(), dim=0).item()
+    assert cos >= 0.9999, cos
+
+
+@pytest.mark.parametrize("B,qh,kvh,seq_len,cap", [
+    (1, 24, 4, 4097, 4100),      # the 27B decoder at batch 1: many splits
+    (2, 24, 4, 1, 64),           # a single token
+    (3, 6, 1, 15, 16),           # less than one tile
+    (2, 12, 2, 17, 40),          # one tile and one token
+    (4, 3, 1, 1000, 1024),       # three query heads per KV head (tensor-parallel slice), ragged tail
+    (32, 24, 4, 513, 520),       # batch 32: few splits
+    (2, 8, 1, 333, 400),         # eight query heads on one KV head
+    (2, 4, 4, 200, 200),         # no grouping
+])
+def test_decode_attn_matches_fp32(ext, B, qh, kvh, seq_len, cap):
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + seq_len)
+    q = torch.randn(B, qh, 256, device="cuda", generator=g).half()
+    kc = torch.randn(B, kvh, cap, 256, device="cuda", generator=g).half()
+    vc = torch.randn(B, kvh, cap, 256, device="cuda", generator=g).half()
+    # rows beyond seq_len must not matter, whatever they hold
+    kc[:, :, seq_len:] = float("nan")
+    vc[:, :, seq_len:] = float("nan")
+    out = ext.decode_attn(q, kc, vc, seq_len)
+    _check(out, _ref(q, kc, vc, seq_len))
+    again = ext.decode_attn(q, kc, vc, seq_len)
+    assert torch.equal(out, again)                                   # fixed summation order
+
+
+def test_decode_attn_peaked_scores_and_views(ext):
+    """Large score spread (the running maximum moves often) and q / out given as views of wider rows."""
+    g = torch.Generator(device="cuda").manual_seed(7)
+    B, qh, kvh, L = 2, 24, 4, 700
+    wide = torch.randn(B, (qh + 2 * kvh) * 256, device="cuda", generator=g).half()
+    q = wide[:, :qh * 256].view(B, qh, 256) * 4.0
+    q = torch.as_strided(wide, (B, qh, 256), (wide.stride(0), 256, 1))
+    kc = (torch.randn(B, kvh, L, 256, device="cuda", generator=g) * 2.0).half()
+    vc = torch.randn(B, kvh, L, 256, device="cuda", generator=g).half()
+    buf = torch.zeros(B, qh * 256 + 64, device="cuda", dtype=torch.half)
+    out = torch.as_strided(buf, (B, qh, 256), (buf.stride(0), 256, 1))
+    ext.decode_attn(q, kc, vc, L, out=out)
+    _check(out, _ref(q, kc, vc, L))
+    assert torch.count_nonzero(buf[:, qh * 256:]) == 0
+
+
+def test_decode_attn_rejects_bad_arguments(ext):
+    q = torch.zeros(1, 24, 128, device="cuda", dtype=torch.half)
+    kc = torch.zeros(1, 4, 16, 128, device="cuda", dtype=torch.half)
+    with pytest.raises(RuntimeError):
+        ext.decode_attn(q, kc, kc, 16)                               # head size 128 is not built
+    q = torch.zeros(1, 36, 256, device="cuda", dtype=torch.half)
+    kc = torch.zeros(1, 4, 16, 256, device="cuda", dtype=torch.half)
+    with pytest.raises(RuntimeError):
+        ext.decode_attn(q, kc, kc, 16)                               # nine query heads per KV head
+    with pytest.raises(RuntimeError):
+        ext.decode_attn(q[:, :24], kc, kc, 17)                       # longer than the cache
+    with pytest.raises(RuntimeError):
+        ext.decode_attn(q[:, :24].cpu(), kc, kc, 16)                 # no CPU path
