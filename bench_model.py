@@ -143,11 +143,15 @@ def main():
             dist.all_reduce(h)                                            # vocabulary-parallel embedding
         for qkv, o, gu, down, kc, vc in model:
             y = qkv(h, in_mode=1)
-            qk = rope(y[:, :(qh + kvh) * HD].reshape(B, qh + kvh, HD))    # query and key heads in one pass
-            q, k = qk[:, :qh], qk[:, qh:]
-            v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
-            kc[:, :, ctx] = k
-            vc[:, :, ctx] = v
+            if args.attn == "sdpa":
+                qk = rope(y[:, :(qh + kvh) * HD].reshape(B, qh + kvh, HD))    # query and key heads in one pass
+                q, k = qk[:, :qh], qk[:, qh:]
+                v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
+                kc[:, :, ctx] = k
+                vc[:, :, ctx] = v
+            else:
+                _ext.rope_append(y, cos, sin, kc, vc, ctx, qh)            # rotary + cache append, one launch
+                q = torch.as_strided(y, (B, qh, HD), (y.stride(0), HD, 1))
             if args.attn == "sdpa":
                 att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
             else:

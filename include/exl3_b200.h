@@ -241,6 +241,21 @@ int exl3_decode_attn(const void *q, const void *k_cache, const void *v_cache, vo
                      int head_dim, int seq_len, long long q_batch_stride, long long out_batch_stride,
                      long long kv_batch_stride, long long kv_head_stride, float scale, void *stream);
 
+/*
+ * The step before exl3_decode_attn, in one launch: rotary embedding (rotate-half form, fp32 math,
+ * one rounding) of the query and key heads of one new token per sequence, and the append of the
+ * rotated key and of the value to the caches at token index pos.  Like the attention itself this
+ * has no counterpart in the reference (the serving engine does it there).
+ *   qkv      [batch][ld_qkv] fp16: q_heads, then kv_heads key heads, then kv_heads value heads, 256
+ *            elements each; the query heads are rotated in place
+ *   cos, sin [128] fp16 of this position, or one row per sequence cos_sin_batch_stride elements
+ *            apart (0 = the same row for every sequence)
+ *   k_cache, v_cache   as for exl3_decode_attn; capacity must exceed pos
+ */
+int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, int cos_sin_batch_stride,
+                     void *k_cache, void *v_cache, int batch, int q_heads, int kv_heads, int head_dim,
+                     int pos, long long kv_batch_stride, long long kv_head_stride, void *stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -313,6 +313,38 @@ __global__ void __launch_bounds__(128) decode_attn_merge_kernel(const __grid_con
         __floats2half2_rn(a0 * inv, a1 * inv);
 }
 
+// Rotary embedding of the query and key heads of one decoded token per sequence and the append of
+// the rotated key and the value to the cache, in one launch (the step before decode_attn_kernel).
+// Rotate-half form: out[i] = t[i] cos[i] - t[i+128] sin[i],  out[i+128] = t[i+128] cos[i] + t[i] sin[i],
+// computed in fp32 and rounded once.  grid = (q_heads + 2 kv_heads, batch), 128 threads.
+struct RopeParams {
+    __half *qkv;             // [B][ld]: q heads, then k heads, then v heads, 256 each
+    const __half *cos, *sin; // [B or 1][128]
+    __half *k, *v;           // caches [B][kvh][cap][256]
+    long long kv_bstride, kv_hstride;
+    int ld, qh, kvh, pos, cs_stride;
+};
+
+__global__ void __launch_bounds__(128) rope_append_kernel(const __grid_constant__ RopeParams P) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int h = blockIdx.x, b = blockIdx.y, i = threadIdx.x;
+    __half *t = P.qkv + (size_t)b * P.ld + (size_t)h * kHD;
+    if (h >= P.qh + P.kvh) {                                   // value head: copy
+        __half *dst = P.v + (size_t)b * P.kv_bstride + (size_t)(h - P.qh - P.kvh) * P.kv_hstride + (size_t)P.pos * kHD;
+        reinterpret_cast<uint32_t *>(dst)[i] = reinterpret_cast<const uint32_t *>(t)[i];
+        return;
+    }
+    const float c = __half2float(P.cos[(size_t)b * P.cs_stride + i]);
+    const float sn = __half2float(P.sin[(size_t)b * P.cs_stride + i]);
+    const float lo = __half2float(t[i]), hi = __half2float(t[i + 128]);
+    const __half olo = __float2half_rn(lo * c - hi * sn), ohi = __float2half_rn(hi * c + lo * sn);
+    __half *dst = h < P.qh ? t
+                           : P.k + (size_t)b * P.kv_bstride + (size_t)(h - P.qh) * P.kv_hstride + (size_t)P.pos * kHD;
+    dst[i] = olo;
+    dst[i + 128] = ohi;
+}
+
 static int pick_splits(int B, int kvh, int seq_len) {
     // A CTA takes a whole SM (192 KB of rings) and costs a few microseconds whatever its length, so a
     // second wave of short CTAs is dear (measured on B200, one sequence of 4096 tokens: 9.5-9.9 us with
@@ -385,6 +417,28 @@ extern "C" int exl3_decode_attn(const void *q, const void *k_cache, const void *
         return EXL3_E_LAUNCH;
     if (P.nsplit > 1 &&
         launch_pdl(decode_attn_merge_kernel, dim3(q_heads, batch), dim3(128), 0, st, P) != cudaSuccess)
+        return EXL3_E_LAUNCH;
+    return launch_status();
+}
+
+extern "C" int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, int cos_sin_batch_stride,
+                                void *k_cache, void *v_cache, int batch, int q_heads, int kv_heads, int head_dim,
+                                int pos, long long kv_batch_stride, long long kv_head_stride, void *stream) {
+    using namespace exl3;
+    if (!qkv || !cos || !sin || !k_cache || !v_cache) return EXL3_E_NULL;
+    if (head_dim != kHD) return EXL3_E_UNSUPPORTED;
+    if (batch <= 0 || batch > 65535 || q_heads <= 0 || kv_heads <= 0 || pos < 0 ||
+        ld_qkv < (q_heads + 2 * kv_heads) * kHD || (ld_qkv & 1) || cos_sin_batch_stride < 0 ||
+        kv_head_stride < (long long)(pos + 1) * kHD || (kv_head_stride & 1) || (kv_batch_stride & 1))
+        return EXL3_E_SHAPE;
+    if (!aligned(qkv, 4) || !aligned(k_cache, 4) || !aligned(v_cache, 4)) return EXL3_E_ALIGN;
+    RopeParams P = {};
+    P.qkv = (__half *)qkv; P.cos = (const __half *)cos; P.sin = (const __half *)sin;
+    P.k = (__half *)k_cache; P.v = (__half *)v_cache;
+    P.kv_bstride = kv_batch_stride; P.kv_hstride = kv_head_stride;
+    P.ld = ld_qkv; P.qh = q_heads; P.kvh = kv_heads; P.pos = pos; P.cs_stride = cos_sin_batch_stride;
+    if (launch_pdl(rope_append_kernel, dim3(q_heads + 2 * kv_heads, batch), dim3(128), 0, (cudaStream_t)stream, P) !=
+        cudaSuccess)
         return EXL3_E_LAUNCH;
     return launch_status();
 }

@@ -87,6 +87,8 @@ def lib():
                 L.exl3_decode_attn_workspace_bytes.argtypes = [ci, ci, ci, ci]
                 L.exl3_decode_attn.argtypes = [vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ll, ll, ll, ll, cf, vp]
                 L.exl3_decode_attn.restype = ci
+                L.exl3_rope_append.argtypes = [vp, ci, vp, vp, ci, vp, vp, ci, ci, ci, ci, ci, ll, ll, vp]
+                L.exl3_rope_append.restype = ci
                 for name in ("exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
                              "exl3_int8_embed", "exl3_int8_head"):
                     getattr(L, name).restype = ci
@@ -450,3 +452,26 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, s
                               q.stride(0), out.stride(0), k_cache.stride(0), k_cache.stride(1),
                               float(hd ** -0.5 if scale is None else scale), _stream(q)), "exl3_decode_attn")
     return out
+
+
+def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor,
+                v_cache: torch.Tensor, pos: int, q_heads: int) -> None:
+    """Rotate the query and key heads of qkv [B, (q_heads + 2 kv_heads) * 256] in place (rotate-half form) and
+    write the rotated keys and the values to k_cache / v_cache [B, kv_heads, capacity, 256] at token `pos`.
+    cos, sin: [128] fp16 (one position for all sequences) or [B, 128]."""
+    for t, name in ((qkv, "qkv"), (cos, "cos"), (sin, "sin"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+        if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dtype != torch.float16:
+            raise RuntimeError(f"{name} must be a CUDA fp16 tensor (this build has no CPU path)")
+    if qkv.dim() != 2 or qkv.stride(1) != 1 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape \
+            or v_cache.stride() != k_cache.stride() or k_cache.stride(3) != 1 or k_cache.stride(2) != k_cache.shape[3]:
+        raise RuntimeError("rope_append: qkv must be [B, n] with contiguous rows, the caches [B, kv_heads, capacity, 256]")
+    B, kvh, cap, hd = k_cache.shape
+    if qkv.shape[0] != B or qkv.shape[1] < (q_heads + 2 * kvh) * hd or not 0 <= pos < cap:
+        raise RuntimeError("rope_append: inconsistent shapes")
+    if cos.shape != sin.shape or cos.shape[-1] != hd // 2 or not cos.is_contiguous() or not sin.is_contiguous() \
+            or (cos.dim() == 2 and cos.shape[0] != B) or cos.dim() > 2:
+        raise RuntimeError("rope_append: cos / sin must be [128] or [B, 128], contiguous")
+    _check(lib().exl3_rope_append(qkv.data_ptr(), qkv.stride(0), cos.data_ptr(), sin.data_ptr(),
+                                  hd // 2 if cos.dim() == 2 else 0, k_cache.data_ptr(), v_cache.data_ptr(), B,
+                                  q_heads, kvh, hd, int(pos), k_cache.stride(0), k_cache.stride(1), _stream(qkv)),
+           "exl3_rope_append")

@@ -77,3 +77,34 @@ def test_decode_attn_rejects_bad_arguments(ext):
         ext.decode_attn(q[:, :24], kc, kc, 17)                       # longer than the cache
     with pytest.raises(RuntimeError):
         ext.decode_attn(q[:, :24].cpu(), kc, kc, 16)                 # no CPU path
+
+
+@pytest.mark.parametrize("B,qh,kvh,per_seq", [(1, 24, 4, False), (5, 3, 1, True), (32, 12, 2, False)])
+def test_rope_append_matches_fp32(ext, B, qh, kvh, per_seq):
+    """Rotary + cache append against the rotate-half formula in fp32 (within 2e-3 of the largest value:
+    one fp16 rounding), untouched cache rows stay as they were."""
+    g = torch.Generator(device="cuda").manual_seed(11 + B)
+    cap, pos = 40, 17
+    qkv = torch.randn(B, (qh + 2 * kvh) * 256 + 128, device="cuda", generator=g).half()   # wider rows than needed
+    ang = torch.rand((B, 128) if per_seq else (128,), device="cuda", generator=g) * 6.28
+    cos, sin = torch.cos(ang).half(), torch.sin(ang).half()
+    kc = torch.randn(B, kvh, cap, 256, device="cuda", generator=g).half()
+    vc = torch.randn(B, kvh, cap, 256, device="cuda", generator=g).half()
+    kc0, vc0, src = kc.clone(), vc.clone(), qkv.clone()
+    ext.rope_append(qkv, cos, sin, kc, vc, pos, qh)
+
+    t = src[:, :(qh + kvh) * 256].float().view(B, qh + kvh, 256)
+    c = cos.float().view(-1, 1, 128) if per_seq else cos.float()
+    s = sin.float().view(-1, 1, 128) if per_seq else sin.float()
+    lo, hi = t[..., :128], t[..., 128:]
+    want = torch.cat([lo * c - hi * s, hi * c + lo * s], dim=-1)
+    got_q = qkv[:, :qh * 256].view(B, qh, 256)
+    assert (got_q.float() - want[:, :qh]).abs().max().item() <= 2e-3 * want.abs().max().item()
+    assert (kc[:, :, pos].float() - want[:, qh:]).abs().max().item() <= 2e-3 * want.abs().max().item()
+    assert torch.equal(vc[:, :, pos], src[:, (qh + kvh) * 256:(qh + 2 * kvh) * 256].view(B, kvh, 256))
+    assert torch.equal(qkv[:, qh * 256:], src[:, qh * 256:])          # k, v and the padding of qkv are not modified
+    mask = torch.ones(cap, dtype=torch.bool, device="cuda")
+    mask[pos] = False
+    assert torch.equal(kc[:, :, mask], kc0[:, :, mask]) and torch.equal(vc[:, :, mask], vc0[:, :, mask])
+    with pytest.raises(RuntimeError):
+        ext.rope_append(qkv, cos, sin, kc, vc, cap, qh)               # position outside the cache
