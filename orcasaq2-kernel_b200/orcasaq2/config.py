@@ -144,7 +144,10 @@ class Exl3Config(QuantizationConfig):
         if self.quantized_prefixes:
             leaf = prefix.rsplit(".", 1)[-1]
             if not any(name in self.quantized_prefixes for name in _expand(prefix, leaf)):
-                from vllm.model_executor.layers.quantization.unquant import UnquantizedLinearMethod
+                try:       # where the reference imports it from (orcasaq2/config.py:144-147)
+                    from vllm.model_executor.layers.quantization.unquant import UnquantizedLinearMethod
+                except ImportError:   # vLLM 0.22 keeps the class beside the linear layers
+                    from vllm.model_executor.layers.linear import UnquantizedLinearMethod
                 return UnquantizedLinearMethod()
         return Exl3LinearMethod(self, prefix)
 

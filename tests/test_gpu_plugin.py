@@ -185,3 +185,50 @@ def test_vllm_qkv_merged_and_row_parallel_layers(vllm_layers, cfg, coracle, rows
                               for tr, suh, svh in refs], 1)
         assert y.shape == (rows, sum(oc for _, oc, _ in specs)) and y.dtype == torch.bfloat16
         _close(y, ref, tol=2e-2)
+
+
+def test_vllm_layers_loaded_from_a_checkpoint_on_disk(vllm_layers, cfg, coracle, tmp_path):
+    """A synthetic checkpoint (safetensors + quantization_config.json with its manifest) is read back from
+    disk and delivered through the parameters' own weight loaders under vLLM's stacked renaming; the
+    manifest decides which layers are EXL3 and which stay dense; every layer's output matches the oracle."""
+    from orcasaq2 import checkpoint as C
+    L = vllm_layers
+    dims = dict(layers=2, hidden=256, ffn=384, q_heads=3, kv_heads=1, head_dim=128, vocab=300)
+    dense = "model.layers.1.self_attn.o_proj"
+    C.write_synthetic_checkpoint(str(tmp_path), seed=21, dense=[dense], max_file_bytes=200_000, **dims)
+    qc = cfg.Exl3Config.from_config(C.read_quantization_config(str(tmp_path)))
+    H, F, QH, KVH, HD = (dims[k] for k in ("hidden", "ffn", "q_heads", "kv_heads", "head_dim"))
+    modules = {}
+    for li in range(dims["layers"]):
+        p = f"model.layers.{li}."
+        kw = dict(bias=False, quant_config=qc, params_dtype=torch.float16)
+        modules[p + "self_attn.qkv_proj"] = L.QKVParallelLinear(H, HD, QH, KVH, prefix=p + "self_attn.qkv_proj", **kw)
+        modules[p + "self_attn.o_proj"] = L.RowParallelLinear(QH * HD, H, prefix=p + "self_attn.o_proj", **kw)
+        modules[p + "mlp.gate_up_proj"] = L.MergedColumnParallelLinear(H, [F, F], prefix=p + "mlp.gate_up_proj", **kw)
+        modules[p + "mlp.down_proj"] = L.RowParallelLinear(F, H, prefix=p + "mlp.down_proj", **kw)
+    for name, m in modules.items():
+        want = cfg.Exl3LinearMethod if name != dense else L.UnquantizedLinearMethod
+        assert isinstance(m.quant_method, want), name
+    unused = C.load_into(modules, C.iter_checkpoint_tensors(str(tmp_path)))
+    assert all(n.endswith("norm.weight") or n.startswith("model.embed_tokens") for n in unused)
+    tensors, storage = C.synthetic_tensors(seed=21, dense=[dense], **dims)
+    hf = {"self_attn.qkv_proj": ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"],
+          "mlp.gate_up_proj": ["mlp.gate_proj", "mlp.up_proj"]}
+    for name, m in modules.items():
+        m.cuda()
+        m.quant_method.process_weights_after_loading(m)
+        ic = m.input_size
+        x = torch.randn((3, ic), generator=torch.Generator().manual_seed(len(name))).half()
+        out = m(x.cuda())
+        y = out[0] if isinstance(out, tuple) else out
+        li, suffix = name.split(".")[2], name.split(".", 3)[3]
+        parts = [f"model.layers.{li}.{s}" for s in hf.get(suffix, [suffix])]
+        if name == dense:
+            ref = x.double().numpy() @ tensors[dense + ".weight"].double().numpy().T
+        else:
+            assert [s["K"] for s in m.exl3_shards] == [storage[p]["bits_per_weight"] for p in parts]
+            ref = np.concatenate([coracle.layer(x.numpy(), coracle.reconstruct(tensors[p + ".trellis"].numpy()),
+                                                tensors[p + ".suh"].numpy(), tensors[p + ".svh"].numpy())
+                                  for p in parts], 1)
+        assert y.dtype == torch.float16 and y.shape == ref.shape
+        _close(y, ref, tol=1e-2)
