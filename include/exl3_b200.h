@@ -242,6 +242,25 @@ int exl3_decode_attn(const void *q, const void *k_cache, const void *v_cache, vo
                      long long kv_batch_stride, long long kv_head_stride, float scale, void *stream);
 
 /*
+ * exl3_decode_attn over a paged cache.  k_pages / v_pages are page pools of equal layout; a page
+ * holds page_size tokens (a multiple of 16) of every KV head: the element of (page p, head h, token
+ * t, dimension d) is at p*page_stride + h*head_stride + t*token_stride + d, all strides multiples
+ * of 8, which covers both [pages][heads][page_size][256] and [pages][page_size][heads][256].
+ *   block_table  int32 [batch][block_table_stride]: the page of tokens i*page_size ... of a sequence
+ *   seq_lens     int32 [batch] tokens to read per sequence, each <= max_seq_len, or NULL when every
+ *                sequence has max_seq_len tokens; a sequence of length 0 yields a zero row
+ *   workspace    exl3_decode_attn_workspace_bytes(batch, q_heads, kv_heads, max_seq_len) bytes
+ * block_table must cover ceil(max_seq_len / page_size) entries per sequence; entries beyond a
+ * sequence's own length are not read.  Everything else as for exl3_decode_attn.
+ */
+int exl3_decode_attn_paged(const void *q, const void *k_pages, const void *v_pages, const void *block_table,
+                           const void *seq_lens, void *out, void *workspace, size_t workspace_bytes,
+                           int batch, int q_heads, int kv_heads, int head_dim, int max_seq_len,
+                           int page_size, int block_table_stride, long long q_batch_stride,
+                           long long out_batch_stride, long long page_stride, long long head_stride,
+                           long long token_stride, float scale, void *stream);
+
+/*
  * The step before exl3_decode_attn, in one launch: rotary embedding (rotate-half form, fp32 math,
  * one rounding) of the query and key heads of one new token per sequence, and the append of the
  * rotated key and of the value to the caches at token index pos.  Like the attention itself this

@@ -41,6 +41,11 @@ struct AttnParams {
     long long kv_bstride, kv_hstride;        // elements between batches / heads of the cache
     int B, qh, kvh, G, seq_len, nsplit, split_tokens;
     float scale_log2;     // scale * log2(e)
+    // paged form: k / v are page pools, a page holds page_size tokens of every KV head
+    const int *block_table;   // [B][bt_stride]: page number of every page_size tokens of a sequence
+    const int *seq_lens;      // [B] tokens to read per sequence (seq_len is then their upper bound)
+    long long page_stride, tok_stride;       // elements between pages / between tokens of a head
+    int bt_stride, page_size;
 };
 
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, bool valid) {
@@ -72,20 +77,38 @@ __device__ __forceinline__ uint32_t pack_h2(float a, float b) {
 }
 
 // One warp copies a 16-token tile of K and of V (16 x 512 bytes each): one instruction moves one
-// token row, 32 lanes x 16 bytes, into its swizzled place.  Tokens at or beyond `end` are zero-filled.
-__device__ __forceinline__ void load_tile(uint32_t stage, const __half *kbase, const __half *vbase, int tok0,
-                                          int end, int lane) {
+// token row, 32 lanes x 16 bytes, into its swizzled place.  krow / vrow point at the tile's first
+// token; rows at or beyond `nvalid` are zero-filled.
+__device__ __forceinline__ void load_tile(uint32_t stage, const __half *krow, const __half *vrow, long long tok_stride,
+                                          int nvalid, int lane) {
 #pragma unroll
     for (int r = 0; r < kTile; ++r) {
-        const int tok = tok0 + r;
-        const bool ok = tok < end;
-        const size_t off = (size_t)(ok ? tok : tok0) * kHD + lane * 8;
+        const bool ok = r < nvalid;
+        const size_t off = (size_t)(ok ? r : 0) * tok_stride + lane * 8;
         const uint32_t dst = stage + r * kRowBytes + ((lane ^ (r & 7)) << 4);
-        cp_async16(dst, kbase + off, ok);
-        cp_async16(dst + kTileBytes, vbase + off, ok);
+        cp_async16(dst, krow + off, ok);
+        cp_async16(dst + kTileBytes, vrow + off, ok);
     }
 }
 
+// Where the tile that starts at token tok0 of (sequence b, KV head hk) lies.  Contiguous cache: rows 256
+// elements apart behind the head's base.  Paged cache: a tile never straddles a page (page sizes are
+// multiples of 16 and tiles start at multiples of 16), so one block-table entry locates it.
+template <bool PAGED>
+__device__ __forceinline__ void issue_tile(const AttnParams &P, uint32_t stage, int b, int hk, int tok0, int t_end,
+                                           int lane) {
+    if constexpr (PAGED) {
+        const int page = __ldg(P.block_table + (size_t)b * P.bt_stride + tok0 / P.page_size);
+        const size_t off = (size_t)page * P.page_stride + (size_t)hk * P.kv_hstride +
+                           (size_t)(tok0 % P.page_size) * P.tok_stride;
+        load_tile(stage, P.k + off, P.v + off, P.tok_stride, t_end - tok0, lane);
+    } else {
+        const size_t off = (size_t)b * P.kv_bstride + (size_t)hk * P.kv_hstride + (size_t)tok0 * kHD;
+        load_tile(stage, P.k + off, P.v + off, kHD, t_end - tok0, lane);
+    }
+}
+
+template <bool PAGED>
 __global__ void __launch_bounds__(kAttnWarps * 32, 1) decode_attn_kernel(const __grid_constant__ AttnParams P) {
     extern __shared__ __align__(128) unsigned char smem[];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -93,13 +116,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) decode_attn_kernel(const _
     const int split = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
     const int G = P.G;
 
+    const int seq_len = PAGED && P.seq_lens ? min(P.seq_len, __ldg(P.seq_lens + b)) : P.seq_len;
     const int t_begin = split * P.split_tokens;
-    const int t_end = min(P.seq_len, t_begin + P.split_tokens);
+    const int t_end = min(seq_len, t_begin + P.split_tokens);
     const int ntiles = t_end > t_begin ? (t_end - t_begin + kTile - 1) / kTile : 0;
     const int my_tiles = ntiles > warp ? (ntiles - warp + kAttnWarps - 1) / kAttnWarps : 0;
 
-    const __half *kbase = P.k + (size_t)b * P.kv_bstride + (size_t)hk * P.kv_hstride;
-    const __half *vbase = P.v + (size_t)b * P.kv_bstride + (size_t)hk * P.kv_hstride;
     const uint32_t ring = static_cast<uint32_t>(__cvta_generic_to_shared(smem)) + warp * (kAttnStages * kStageBytes);
 
     // Both the query and the newest cache row may come from kernels just before this one on the
@@ -109,7 +131,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) decode_attn_kernel(const _
 
 #pragma unroll
     for (int s = 0; s < kAttnStages - 1; ++s) {
-        if (s < my_tiles) load_tile(ring + s * kStageBytes, kbase, vbase, t_begin + (warp + s * kAttnWarps) * kTile, t_end, lane);
+        if (s < my_tiles) issue_tile<PAGED>(P, ring + s * kStageBytes, b, hk, t_begin + (warp + s * kAttnWarps) * kTile, t_end, lane);
         cp_async_commit();
     }
 
@@ -142,8 +164,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 1) decode_attn_kernel(const _
         {
             const int nxt = i + kAttnStages - 1;
             if (nxt < my_tiles)
-                load_tile(ring + (nxt % kAttnStages) * kStageBytes, kbase, vbase,
-                          t_begin + (warp + nxt * kAttnWarps) * kTile, t_end, lane);
+                issue_tile<PAGED>(P, ring + (nxt % kAttnStages) * kStageBytes, b, hk,
+                                  t_begin + (warp + nxt * kAttnWarps) * kTile, t_end, lane);
             cp_async_commit();
         }
         cp_async_wait<kAttnStages - 1>();
@@ -360,6 +382,37 @@ static int pick_splits(int B, int kvh, int seq_len) {
     return want;
 }
 
+// Split choice, workspace carving and the one or two launches, shared by the contiguous and the paged form.
+static int launch_attn(AttnParams &P, bool paged, void *workspace, size_t workspace_bytes, cudaStream_t st) {
+    P.nsplit = pick_splits(P.B, P.kvh, P.seq_len);
+    const int tiles = (P.seq_len + kTile - 1) / kTile;
+    const int per = (tiles + P.nsplit - 1) / P.nsplit;
+    P.split_tokens = per * kTile;
+    P.nsplit = (tiles + per - 1) / per;              // no split beyond the longest sequence
+    if (P.nsplit > 1) {
+        const size_t rows = (size_t)P.B * P.qh * P.nsplit;
+        if (!workspace || workspace_bytes < rows * kHD * 4 + rows * 8) return EXL3_E_WORKSPACE;
+        if (!aligned(workspace, 16)) return EXL3_E_ALIGN;
+        P.part_o = (float *)workspace;
+        P.part_ml = P.part_o + rows * kHD;
+    }
+    auto kernel = paged ? decode_attn_kernel<true> : decode_attn_kernel<false>;
+    static bool attr_done[2][64] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_done[paged][dev]) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess)
+            return EXL3_E_LAUNCH;
+        attr_done[paged][dev] = true;
+    }
+    if (launch_pdl(kernel, dim3(P.nsplit, P.kvh, P.B), dim3(kAttnWarps * 32), kAttnSmem, st, P) != cudaSuccess)
+        return EXL3_E_LAUNCH;
+    if (P.nsplit > 1 &&
+        launch_pdl(decode_attn_merge_kernel, dim3(P.qh, P.B), dim3(128), 0, st, P) != cudaSuccess)
+        return EXL3_E_LAUNCH;
+    return launch_status();
+}
+
 }  // namespace exl3
 
 extern "C" size_t exl3_decode_attn_workspace_bytes(int batch, int q_heads, int kv_heads, int seq_len) {
@@ -391,34 +444,40 @@ extern "C" int exl3_decode_attn(const void *q, const void *k_cache, const void *
     P.q_bstride = q_batch_stride; P.o_bstride = out_batch_stride;
     P.kv_bstride = kv_batch_stride; P.kv_hstride = kv_head_stride;
     P.B = batch; P.qh = q_heads; P.kvh = kv_heads; P.G = G; P.seq_len = seq_len;
-    P.nsplit = pick_splits(batch, kv_heads, seq_len);
-    const int tiles = (seq_len + kTile - 1) / kTile;
-    const int per = (tiles + P.nsplit - 1) / P.nsplit;
-    P.split_tokens = per * kTile;
-    P.nsplit = (tiles + per - 1) / per;              // no empty split
     P.scale_log2 = scale * 1.4426950408889634f;
-    if (P.nsplit > 1) {
-        const size_t rows = (size_t)batch * q_heads * P.nsplit;
-        if (!workspace || workspace_bytes < rows * kHD * 4 + rows * 8) return EXL3_E_WORKSPACE;
-        if (!aligned(workspace, 16)) return EXL3_E_ALIGN;
-        P.part_o = (float *)workspace;
-        P.part_ml = P.part_o + rows * kHD;
-    }
-    cudaStream_t st = (cudaStream_t)stream;
-    static bool attr_done[64] = {};
-    int dev = 0;
-    cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-        if (cudaFuncSetAttribute(decode_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem) != cudaSuccess)
-            return EXL3_E_LAUNCH;
-        attr_done[dev] = true;
-    }
-    if (launch_pdl(decode_attn_kernel, dim3(P.nsplit, kv_heads, batch), dim3(kAttnWarps * 32), kAttnSmem, st, P) != cudaSuccess)
-        return EXL3_E_LAUNCH;
-    if (P.nsplit > 1 &&
-        launch_pdl(decode_attn_merge_kernel, dim3(q_heads, batch), dim3(128), 0, st, P) != cudaSuccess)
-        return EXL3_E_LAUNCH;
-    return launch_status();
+    return launch_attn(P, false, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int exl3_decode_attn_paged(const void *q, const void *k_pages, const void *v_pages, const void *block_table,
+                                      const void *seq_lens, void *out, void *workspace, size_t workspace_bytes,
+                                      int batch, int q_heads, int kv_heads, int head_dim, int max_seq_len,
+                                      int page_size, int block_table_stride, long long q_batch_stride,
+                                      long long out_batch_stride, long long page_stride, long long head_stride,
+                                      long long token_stride, float scale, void *stream) {
+    using namespace exl3;
+    if (!q || !k_pages || !v_pages || !block_table || !out) return EXL3_E_NULL;
+    if (head_dim != kHD) return EXL3_E_UNSUPPORTED;
+    if (batch <= 0 || batch > 65535 || kv_heads <= 0 || kv_heads > 65535 || q_heads <= 0 || q_heads % kv_heads ||
+        max_seq_len <= 0 || page_size <= 0 || (page_size % kTile))
+        return EXL3_E_SHAPE;
+    const int G = q_heads / kv_heads;
+    if (G > 8) return EXL3_E_UNSUPPORTED;
+    if (block_table_stride < (max_seq_len + page_size - 1) / page_size || token_stride < kHD || (token_stride & 7) ||
+        (head_stride & 7) || (page_stride & 7) || head_stride <= 0 || page_stride <= 0 || (q_batch_stride & 1) ||
+        (out_batch_stride & 1))
+        return EXL3_E_SHAPE;
+    if (!aligned(k_pages, 16) || !aligned(v_pages, 16) || !aligned(q, 4) || !aligned(out, 4) || !aligned(block_table, 4) ||
+        !aligned(seq_lens, 4))
+        return EXL3_E_ALIGN;
+    AttnParams P = {};
+    P.q = (const __half *)q; P.k = (const __half *)k_pages; P.v = (const __half *)v_pages; P.out = (__half *)out;
+    P.q_bstride = q_batch_stride; P.o_bstride = out_batch_stride;
+    P.kv_hstride = head_stride; P.page_stride = page_stride; P.tok_stride = token_stride;
+    P.block_table = (const int *)block_table; P.seq_lens = (const int *)seq_lens;
+    P.bt_stride = block_table_stride; P.page_size = page_size;
+    P.B = batch; P.qh = q_heads; P.kvh = kv_heads; P.G = G; P.seq_len = max_seq_len;
+    P.scale_log2 = scale * 1.4426950408889634f;
+    return launch_attn(P, true, workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 extern "C" int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, int cos_sin_batch_stride,

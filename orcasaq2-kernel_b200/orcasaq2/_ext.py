@@ -87,6 +87,9 @@ def lib():
                 L.exl3_decode_attn_workspace_bytes.argtypes = [ci, ci, ci, ci]
                 L.exl3_decode_attn.argtypes = [vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ll, ll, ll, ll, cf, vp]
                 L.exl3_decode_attn.restype = ci
+                L.exl3_decode_attn_paged.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ci,
+                                                     ll, ll, ll, ll, ll, cf, vp]
+                L.exl3_decode_attn_paged.restype = ci
                 L.exl3_rope_append.argtypes = [vp, ci, vp, vp, ci, vp, vp, ci, ci, ci, ci, ci, ll, ll, vp]
                 L.exl3_rope_append.restype = ci
                 for name in ("exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
@@ -475,3 +478,43 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache
                                   hd // 2 if cos.dim() == 2 else 0, k_cache.data_ptr(), v_cache.data_ptr(), B,
                                   q_heads, kvh, hd, int(pos), k_cache.stride(0), k_cache.stride(1), _stream(qkv)),
            "exl3_rope_append")
+
+
+def decode_attn_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
+                      seq_lens: torch.Tensor | None, max_seq_len: int, layout: str = "HND",
+                      scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """decode_attn over a paged cache.  k_pages / v_pages: [pages, kv_heads, page_size, 256] (layout "HND") or
+    [pages, page_size, kv_heads, 256] ("NHD"), fp16, rows contiguous; block_table int32 [B, >= ceil(max_seq_len /
+    page_size)]; seq_lens int32 [B] or None (every sequence has max_seq_len tokens)."""
+    for t, name in ((q, "q"), (k_pages, "k_pages"), (v_pages, "v_pages")):
+        if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dtype != torch.float16:
+            raise RuntimeError(f"{name} must be a CUDA fp16 tensor (this build has no CPU path)")
+    if layout not in ("HND", "NHD") or k_pages.dim() != 4 or v_pages.shape != k_pages.shape \
+            or v_pages.stride() != k_pages.stride() or k_pages.stride(3) != 1:
+        raise RuntimeError("decode_attn_paged: page pools must be 4-D with equal shapes and strides, layout HND or NHD")
+    hdim, tdim = (1, 2) if layout == "HND" else (2, 1)
+    kvh, page_size, hd = k_pages.shape[hdim], k_pages.shape[tdim], k_pages.shape[3]
+    B, qh = q.shape[0], q.shape[1]
+    if q.dim() != 3 or q.shape[2] != hd or q.stride(2) != 1 or q.stride(1) != hd:
+        raise RuntimeError("decode_attn_paged: q must be [B, heads, 256] with contiguous heads")
+    if block_table.device != q.device or block_table.dtype != torch.int32 or block_table.dim() != 2 \
+            or block_table.shape[0] != B or block_table.stride(1) != 1:
+        raise RuntimeError("decode_attn_paged: block_table must be a CUDA int32 [B, n] tensor")
+    if seq_lens is not None and (seq_lens.device != q.device or seq_lens.dtype != torch.int32
+                                 or seq_lens.shape != (B,) or not seq_lens.is_contiguous()):
+        raise RuntimeError("decode_attn_paged: seq_lens must be a CUDA int32 [B] tensor")
+    if out is None:
+        out = torch.empty((B, qh, hd), dtype=torch.float16, device=q.device)
+    elif out.shape != (B, qh, hd) or out.dtype != torch.float16 or out.stride(2) != 1 or out.stride(1) != hd:
+        raise RuntimeError("decode_attn_paged: out must be [B, heads, 256] fp16 with contiguous heads")
+    L = lib()
+    need = L.exl3_decode_attn_workspace_bytes(B, qh, kvh, int(max_seq_len))
+    ws = torch.empty((need,), dtype=torch.uint8, device=q.device) if need else None
+    _check(L.exl3_decode_attn_paged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+                                    None if seq_lens is None else seq_lens.data_ptr(), out.data_ptr(),
+                                    ws.data_ptr() if ws is not None else None, need, B, qh, kvh, hd,
+                                    int(max_seq_len), page_size, block_table.stride(0) if B > 1 else block_table.shape[1],
+                                    q.stride(0), out.stride(0), k_pages.stride(0), k_pages.stride(hdim),
+                                    k_pages.stride(tdim), float(hd ** -0.5 if scale is None else scale), _stream(q)),
+           "exl3_decode_attn_paged")
+    return out

@@ -97,3 +97,21 @@ def test_decode_attn_argument_checks(lib):
     assert lib.exl3_decode_attn(*args(L=0)) == -1
     assert lib.exl3_decode_attn(*args(hs=63 * 256)) == -1                     # head stride shorter than seq_len rows
     assert lib.exl3_decode_attn(*args(B=1, L=4096, hs=4096 * 256)) == -5                     # split, but no workspace
+
+
+def test_decode_attn_paged_argument_checks(lib):
+    vp, ci, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+    lib.exl3_decode_attn_paged.argtypes = [vp] * 7 + [ctypes.c_size_t] + [ci] * 7 + [ll] * 5 + [ctypes.c_float, vp]
+    fake = vp(4096)
+
+    def call(**kw):
+        return lib.exl3_decode_attn_paged(kw.get("q", fake), fake, fake, kw.get("bt", fake), None, fake, None, 0,
+                                          512, kw.get("qh", 24), 4, kw.get("hd", 256), kw.get("L", 64),
+                                          kw.get("page", 32), kw.get("bts", 2), 24 * 256, 24 * 256, 4 * 32 * 256,
+                                          32 * 256, kw.get("ts", 256), 0.0625, None)
+    assert call(bt=None) == -6
+    assert call(hd=64) == -3
+    assert call(qh=36) == -3
+    assert call(page=24) == -1                 # not a multiple of 16
+    assert call(L=65) == -1                    # three pages needed, the table holds two per sequence
+    assert call(ts=100) == -1

@@ -108,3 +108,61 @@ def test_rope_append_matches_fp32(ext, B, qh, kvh, per_seq):
     assert torch.equal(kc[:, :, mask], kc0[:, :, mask]) and torch.equal(vc[:, :, mask], vc0[:, :, mask])
     with pytest.raises(RuntimeError):
         ext.rope_append(qkv, cos, sin, kc, vc, cap, qh)               # position outside the cache
+
+
+def _paginate(kc, vc, page, layout, gen):
+    """Scatter contiguous caches [B, kvh, cap, 256] into page pools in a shuffled page order."""
+    B, kvh, cap, hd = kc.shape
+    per_seq = cap // page
+    n = B * per_seq
+    perm = torch.randperm(n + 3, device="cuda", generator=gen)[:n].to(torch.int32)     # three pages stay unused
+    table = perm.view(B, per_seq).contiguous()
+    shape = (n + 3, kvh, page, hd) if layout == "HND" else (n + 3, page, kvh, hd)
+    kp = torch.full(shape, float("nan"), device="cuda", dtype=torch.half)
+    vp = torch.full(shape, float("nan"), device="cuda", dtype=torch.half)
+    for b in range(B):
+        for i in range(per_seq):
+            ks, vs = kc[b, :, i * page:(i + 1) * page], vc[b, :, i * page:(i + 1) * page]   # [kvh, page, hd]
+            pg = int(table[b, i])
+            kp[pg] = ks if layout == "HND" else ks.transpose(0, 1)
+            vp[pg] = vs if layout == "HND" else vs.transpose(0, 1)
+    return kp, vp, table
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+@pytest.mark.parametrize("B,qh,kvh,page,cap", [(1, 24, 4, 16, 2048), (3, 6, 1, 64, 512), (32, 12, 2, 32, 256)])
+def test_decode_attn_paged(ext, layout, B, qh, kvh, page, cap):
+    """Paged form: same bytes as the contiguous kernel when all sequences are full, fp32 parity with
+    ragged per-sequence lengths (including a sequence of one token), unused pages and table entries ignored."""
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + page)
+    q = torch.randn(B, qh, 256, device="cuda", generator=g).half()
+    kc = torch.randn(B, kvh, cap, 256, device="cuda", generator=g).half()
+    vc = torch.randn(B, kvh, cap, 256, device="cuda", generator=g).half()
+    kp, vp, table = _paginate(kc, vc, page, layout, g)
+    full = ext.decode_attn_paged(q, kp, vp, table, None, cap, layout=layout)
+    assert torch.equal(full, ext.decode_attn(q, kc, vc, cap))
+    lens = torch.randint(1, cap + 1, (B,), device="cuda", generator=g).to(torch.int32)
+    lens[0] = 1
+    lens[-1] = cap - 5 if B > 1 else 1
+    table2 = table.clone()
+    for b in range(B):                                   # entries past a sequence's length must not be read:
+        table2[b, (int(lens[b]) + page - 1) // page:] = kp.shape[0] - 1      # they point at a page of NaNs
+    out = ext.decode_attn_paged(q, kp, vp, table2, lens, cap, layout=layout)
+    for b in range(B):
+        n = int(lens[b])
+        _check(out[b:b + 1], _ref(q[b:b + 1], kc[b:b + 1], vc[b:b + 1], n))
+
+
+def test_decode_attn_paged_rejects_bad_arguments(ext):
+    q = torch.zeros(2, 8, 256, device="cuda", dtype=torch.half)
+    kp = torch.zeros(8, 2, 24, 256, device="cuda", dtype=torch.half)      # 24 tokens per page: not a multiple of 16
+    table = torch.zeros(2, 4, device="cuda", dtype=torch.int32)
+    with pytest.raises(RuntimeError):
+        ext.decode_attn_paged(q, kp, kp, table, None, 48)
+    kp = torch.zeros(8, 2, 32, 256, device="cuda", dtype=torch.half)
+    with pytest.raises(RuntimeError):
+        ext.decode_attn_paged(q, kp, kp, table, None, 32 * 5)             # the table is too short for 160 tokens
+    with pytest.raises(RuntimeError):
+        ext.decode_attn_paged(q, kp, kp, table.long(), None, 64)
+    with pytest.raises(RuntimeError):
+        ext.decode_attn_paged(q, kp, kp, table, torch.zeros(3, device="cuda", dtype=torch.int32), 64)
