@@ -6,7 +6,7 @@
     python kernel_bench.py int8_head --rows 1 [--vocab 151936 --hidden 5120 --bf16]
     python kernel_bench.py int8_embed --rows 4096
     python kernel_bench.py had --rows 8192 --ic 5120
-    python kernel_bench.py attn --rows 32 --ctx 4096 [--qh 24 --kvh 4 --sdpa]   # decode attention, rows = batch
+    python kernel_bench.py attn --rows 32 --ctx 4096 [--qh 24 --kvh 4 --sdpa --page 16]   # decode attention, rows = batch
     python kernel_bench.py prefill        # BASELINE config 3: both shapes, M = 512 / 2048 / 8192
     python kernel_bench.py shards         # BASELINE configs 1 and 2: every shard, rows 1 / 4 / 16
 
@@ -147,7 +147,7 @@ def bench_had(rows, n, iters):
     return dict(kernel="had_r_128", rows=rows, n=n, us=round(t * 1e6, 1), GBs=round(rows * n * 4 / t / 1e9, 1))
 
 
-def bench_attn(batch, qh, kvh, ctx, iters, sdpa):
+def bench_attn(batch, qh, kvh, ctx, iters, sdpa, page=0):
     """Decode attention over `ctx` cached tokens; the caches are rotated so that every launch reads HBM."""
     per = 2 * batch * kvh * ctx * 256 * 2
     n = int(min(8, max(2, 400e6 // per + 1)))
@@ -159,6 +159,25 @@ def bench_attn(batch, qh, kvh, ctx, iters, sdpa):
     b = per + 2 * q.numel() * 2
     r = dict(kernel="decode_attn", batch=batch, q_heads=qh, kv_heads=kvh, ctx=ctx, us=round(t * 1e6, 1),
              GBs=round(b / t / 1e9, 1))
+    if page:
+        # the same tokens in page pools [pages, kv_heads, page, 256], pages in shuffled order
+        npg = ctx // page
+        perm = torch.randperm(batch * npg, device=DEV)
+        table = torch.empty(batch * npg, dtype=torch.int32, device=DEV)
+        table[perm] = torch.arange(batch * npg, dtype=torch.int32, device=DEV)     # page of (b, i) = table[b * npg + i]
+        table = table.view(batch, npg)
+
+        def pool(c):
+            pg = c.view(batch, kvh, npg, page, 256).permute(0, 2, 1, 3, 4).reshape(batch * npg, kvh, page, 256)
+            out = torch.empty_like(pg)
+            out[table.view(-1).long()] = pg
+            return out
+        kps, vps = [pool(c) for c in kcs], [pool(c) for c in vcs]
+        tp = timeit(lambda i: _ext.decode_attn_paged(q, kps[i % n], vps[i % n], table, None, npg * page, out=o),
+                    max(iters, 2 * n), period=n)
+        same = bool(torch.equal(_ext.decode_attn_paged(q, kps[0], vps[0], table, None, npg * page),
+                                _ext.decode_attn(q, kcs[0], vcs[0], npg * page)))
+        r.update(page=page, paged_us=round(tp * 1e6, 1), paged_GBs=round(b / tp / 1e9, 1), paged_equals_contiguous=same)
     if sdpa:
         import torch.nn.functional as F
         ts = timeit(lambda i: F.scaled_dot_product_attention(q.unsqueeze(2), kcs[i % n], vcs[i % n], enable_gqa=True),
@@ -181,6 +200,7 @@ def main():
     ap.add_argument("--ctx", type=int, default=4096)
     ap.add_argument("--qh", type=int, default=24)
     ap.add_argument("--kvh", type=int, default=4)
+    ap.add_argument("--page", type=int, default=0, help="attn: also time the paged form with this page size (divides ctx)")
     ap.add_argument("--sdpa", action="store_true", help="attn: also time torch's scaled_dot_product_attention")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph")
@@ -205,7 +225,7 @@ def main():
     elif a.what == "had":
         out.append(bench_had(a.rows, a.ic, a.iters))
     elif a.what == "attn":
-        out.append(bench_attn(a.rows, a.qh, a.kvh, a.ctx, a.iters, a.sdpa))
+        out.append(bench_attn(a.rows, a.qh, a.kvh, a.ctx, a.iters, a.sdpa, a.page))
     elif a.what == "prefill":
         for ic, oc, K in ((5120, 17408, 3), (17408, 5120, 4)):
             for m in (512, 2048, 8192):
