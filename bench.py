@@ -17,6 +17,11 @@ e2e     = same metric through the plugin's custom op with HOST activations: pinn
 N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
           down_proj followed by an NCCL all-reduce), strong scaling: the job's total bytes are fixed.
 
+decoder_27b = (N = 1 only, after the timed region, `--no-decoder` skips it) tokens/s of the random-init 27B
+          decoder of bench_model.py at batch 1 and 32 with a 4096-token cache, each run in a child
+          process; the second half of the headline metric, reported beside the GEMV figure and
+          not part of `value`, `e2e` or `ms_per_step`.
+
 `--impl reference` times the CPU restatement of the reference path (PyTorch on the host cores:
 decode -> Hadamard -> matmul) on a bounded sample of the same workload.
 """
@@ -394,8 +399,34 @@ def run_gpu(args):
     }
     if cpu is not None:
         line["cpu_baseline"] = cpu
+    if world == 1 and not args.no_decoder:
+        line["decoder_27b"] = decoder_tok_s()
     print(json.dumps(line), flush=True)
     _leave(world)
+
+
+def decoder_tok_s():
+    """The second half of the headline metric, after the timed region and outside every figure above: the
+    random-init 27B decoder of bench_model.py at batch 1 and 32 (4096-token cache), each in a process of
+    its own.  Any failure or a run over its time limit is reported in place of the number; it never
+    fails the benchmark."""
+    import subprocess
+    out = {"unit": "tok/s", "ctx": 4096, "source": "bench_model.py (CUDA-graph replay, 64 layers)"}
+    script = os.path.join(ROOT, "bench_model.py")
+    for batch in (1, 32):
+        key = f"bs{batch}"
+        try:
+            p = subprocess.run([sys.executable, script, "--batch", str(batch), "--ctx", "4096", "--steps", "10"],
+                               capture_output=True, text=True, timeout=180)
+            last = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
+            if p.returncode != 0 or not last:
+                out[key] = {"unavailable": f"exit code {p.returncode}"}
+                continue
+            r = json.loads(last[-1])
+            out[key] = {"value": r["value"], "ms_per_step": r["ms_per_step"], "status_word": r.get("status_word")}
+        except Exception as e:                                          # noqa: BLE001
+            out[key] = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+    return out
 
 
 # per-launch DRAM traffic of the gate_up kernel from ncu (dram__bytes_read.sum + write), keyed by
@@ -495,6 +526,8 @@ def main():
     ap.add_argument("--only", default=None, choices=[l[0] for l in LAYERS],
                     help="run just this fused layer each step (small case for profiling)")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
+    ap.add_argument("--no-decoder", action="store_true",
+                    help="skip the 27B decoder runs reported beside the GEMV figure (N = 1 only)")
     ap.add_argument("--skip-extras", action="store_true",
                     help="skip the end-to-end, roofline and CPU-baseline legs (profiling runs)")
     args = ap.parse_args()
