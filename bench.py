@@ -6,24 +6,32 @@ Workload (`config.workload`): the mixed-bitwidth decode shards of one 27B-class 
 qkv_proj (q 5120->6144 @4 bpw, k 5120->1024 @5, v 5120->1024 @6; one grouped launch),
 gate_up_proj (2 x 5120->17408 @3; one grouped launch), down_proj (17408->5120 @4) -- at batch
 `--rows` (default 1), fp16 activations ~N(0,1), uniform-random trellis words, +-1 sign vectors.
-One step = one pass over the three fused layers (3 kernel launches).  Three independent weight
-sets (3 x 134 MB) are rotated so no step finds its trellis in the 126 MB L2.
+One step = one pass over the three fused layers: three kernel launches at one or two rows (the GEMV
+rotates the activations itself), six above (an activation pre-pass before each).  Three independent
+weight sets (3 x 134 MB) are rotated so no step finds its trellis in the 126 MB L2.
 
 metric  = algorithmic bytes (trellis + activations in + out) moved per second, whole job.
-value   = inputs resident in HBM, device-timed with CUDA events.
+value   = inputs resident in HBM: ONE CUDA graph of exactly `--steps` steps, replayed >= 100 times and
+          for >= 250 ms, every replay timed with CUDA events (max over ranks); the median replay is
+          reported, its spread is in `timing`.  `by_rows` repeats this at 1 / 4 / 16 rows.
 e2e     = same metric through the plugin's custom op with HOST activations: pinned host x ->
           device, three `orcasaq2::layer_gemm` calls, outputs back to pinned host, every step;
           replayed from a CUDA graph (the plugin's serving mode), the eager time is reported beside it.
 N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
           down_proj followed by an NCCL all-reduce), strong scaling: the job's total bytes are fixed.
+          The line then also carries `decoder_27b_tp`: the 27B decoder of bench_model.py at batch 64 with
+          an 8192-token cache on the same ranks (BASELINE config 5).
+roofline      = the dominant kernel (gate_up grouped GEMV) alone, graph-replayed; `roofline_by_k` (N = 1):
+                one 5120->17408 shard at 2..6 bits per weight, 1 and 16 rows.
 
 decoder_27b = (N = 1 only, after the timed region, `--no-decoder` skips it) tokens/s of the random-init 27B
           decoder of bench_model.py at batch 1 and 32 with a 4096-token cache, each run in a child
           process; the second half of the headline metric, reported beside the GEMV figure and
-          not part of `value`, `e2e` or `ms_per_step`.
+          not part of `value`, `e2e` or `ms_per_step`; with the same decoder's token rate on the host
+          cores extrapolated from per-layer CPU timings.
 
 `--impl reference` times the CPU restatement of the reference path (PyTorch on the host cores:
-decode -> Hadamard -> matmul) on a bounded sample of the same workload.
+decode -> Hadamard -> matmul) over the same whole step.
 """
 import argparse
 import json
@@ -168,6 +176,68 @@ def _leave(world):
         os._exit(0)
 
 
+def _graph_of(torch, body, steps, warm):
+    """Capture `steps` calls of body(i) into one CUDA graph on a side stream (after `warm` eager calls on that
+    stream, so every scratch buffer exists before capture)."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for i in range(warm):
+            body(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            for i in range(steps):
+                body(i)
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    return graph
+
+
+def time_replays(torch, dist, graph, world, dev, min_region_ms, min_replays, max_replays=5000):
+    """Replay `graph` often enough that the timed region lasts at least `min_region_ms`, with a CUDA event
+    between replays; every replay's time is the max over ranks.  Returns per-replay milliseconds (sorted) and
+    the length of the whole region."""
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+    for _ in range(3):
+        graph.replay()
+    barrier()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(5):
+        graph.replay()
+    b.record()
+    torch.cuda.synchronize()
+    est = torch.tensor([a.elapsed_time(b) / 5.0], device=dev)
+    if world > 1:
+        dist.all_reduce(est, op=dist.ReduceOp.MAX)          # every rank must issue the same number of replays
+    n = int(min(max_replays, max(min_replays, min_region_ms / max(float(est.item()), 1e-4) + 1)))
+    evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
+    barrier()
+    evs[0].record()
+    for i in range(n):
+        graph.replay()
+        evs[i + 1].record()
+    barrier()
+    t = torch.tensor([evs[i].elapsed_time(evs[i + 1]) for i in range(n)], device=dev)
+    region = torch.tensor([evs[0].elapsed_time(evs[n])], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(region, op=dist.ReduceOp.MAX)
+    return sorted(t.tolist()), float(region.item())
+
+
+def _spread(ts, per):
+    """median / min / p10 / p90 / max of per-replay times, divided by `per` (steps or launches per replay)."""
+    n = len(ts)
+    q = lambda f: ts[min(n - 1, int(f * n))] / per               # noqa: E731
+    return {"median": round(ts[n // 2] / per, 6), "min": round(ts[0] / per, 6), "p10": round(q(0.10), 6),
+            "p90": round(q(0.90), 6), "max": round(ts[-1] / per, 6), "replays": n}
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
@@ -187,94 +257,106 @@ def run_gpu(args):
     _ext.lib()
     if world > 1:
         dist.init_process_group("nccl", device_id=dev)
-    rows = args.rows
+    rows, K_steps = args.rows, max(1, args.steps)
+    warm = max(3, args.warmup)
     sets = build_sets(torch, dev, rank, world)
-    xs = {ic: torch.randn((rows, ic), generator=torch.Generator().manual_seed(5)).half().to(dev)
-          for ic in {l[1] for l in sets[0]}}
-    ys = [[torch.empty((rows, tot), dtype=torch.half, device=dev) for (_, _, _, tot) in layers] for layers in sets]
-    full_bytes = sum(algorithmic_bytes(ic, spec, rows) for _, ic, spec in LAYERS)
 
-    def step(i):
-        layers, out = sets[i % N_SETS], ys[i % N_SETS]
-        for (name, ic_r, shards, _), y in zip(layers, out):
-            _ext.gemv_grouped(xs[ic_r], shards, y)
-            if world > 1 and name == "down_proj":
-                dist.all_reduce(y)                          # row-parallel partial sums
+    def make_io(r):
+        xs_ = {ic: torch.randn((r, ic), generator=torch.Generator().manual_seed(5)).half().to(dev)
+               for ic in {l[1] for l in sets[0]}}
+        ys_ = [[torch.empty((r, tot), dtype=torch.half, device=dev) for (_, _, _, tot) in layers] for layers in sets]
+        return xs_, ys_
 
-    def barrier():
+    def stepper(xs_, ys_, only=None):
+        def step(i):
+            layers, out = sets[i % N_SETS], ys_[i % N_SETS]
+            for li, ((name, ic_r, shards, _), y) in enumerate(zip(layers, out)):
+                if only is not None and li != only:
+                    continue
+                _ext.gemv_grouped(xs_[ic_r], shards, y)
+                if world > 1 and name == "down_proj":
+                    dist.all_reduce(y)                      # row-parallel partial sums
+        return step
+
+    def bytes_per_step(r):
+        return sum(algorithmic_bytes(ic, spec, r) for _, ic, spec in LAYERS)
+
+    # ---- the timed region: ONE CUDA graph holding exactly `--steps` steps (weight sets rotated, so no step
+    # finds its trellis in L2), replayed at least 100 times and for at least 250 ms; every replay is timed by
+    # itself with CUDA events and the median replay is the figure reported.  Launches and, for N > 1, the NCCL
+    # all-reduces are issued by the GPU front end, so the host's launch cost is not what gets measured.
+    xs, ys = make_io(rows)
+    step = stepper(xs, ys)
+    for i in range(warm):
+        step(i)
+    torch.cuda.synchronize()
+    sampler = ClockSampler(local)
+    if args.no_graph:
+        graph = None
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
-
-    for i in range(max(3, args.warmup)):
-        step(i)
-    # The timed region replays ONE CUDA graph holding exactly `--steps` steps (weight sets rotated):
-    # the launches, and for N > 1 the NCCL all-reduces, are issued by the GPU front end, so the
-    # host's launch cost (tens of microseconds per call from Python) is not what gets measured.
-    graph, period = None, args.steps
-    if not args.no_graph:
-        side = torch.cuda.Stream()
-        side.wait_stream(torch.cuda.current_stream())
-        with torch.cuda.stream(side):
-            for i in range(N_SETS):
-                step(i)                                     # scratch for this stream exists before capture
-            torch.cuda.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                for i in range(period):
-                    step(i)
-        torch.cuda.current_stream().wait_stream(side)
+        sampler.start()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K_steps):
+            step(i)
+        e1.record()
         torch.cuda.synchronize()
-        graph.replay()
-    reps = max(1, args.steps // period) if graph is not None else 0
-    timed_steps = reps * period if graph is not None else args.steps
-
-    def timed():
-        if graph is not None:
-            for _ in range(reps):
-                graph.replay()
-        else:
-            for i in range(args.steps):
-                step(i)
-
-    sampler = ClockSampler(local)
-    barrier()
-    sampler.start()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    timed()
-    e1.record()
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if world > 1:
-        t = torch.tensor([ms], device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    if ms < 400:
-        # keep the GPU under the same load long enough for the 100 ms clock sampler to see it; the
-        # repeat count comes from the rank-agreed time so every rank issues the same collectives
-        for _ in range(int(400.0 / max(ms, 1e-3))):
-            timed()
+        tm = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(tm, op=dist.ReduceOp.MAX)
+        ts, region_ms = [float(tm.item())], float(tm.item())
+    else:
+        graph = _graph_of(torch, step, K_steps, N_SETS)
+        sampler.start()
+        ts, region_ms = time_replays(torch, dist, graph, world, dev, 250.0 if not args.skip_extras else 0.0,
+                                     100 if not args.skip_extras else 1)
+    if region_ms < 400 and graph is not None and not args.skip_extras:
+        # keep the GPU under the same load long enough for the 100 ms clock sampler to see it
+        for _ in range(int((400 - region_ms) / max(ts[len(ts) // 2], 1e-3)) + 1):
+            graph.replay()
         torch.cuda.synchronize()
     clocks = sampler.stop()
-    ms_step = ms / timed_steps
+    spread = _spread(ts, K_steps)
+    ms_step = spread["median"]
+    full_bytes = bytes_per_step(rows)
     value = full_bytes / (ms_step * 1e-3) / 1e9
+    launches_per_layer = 1 if rows <= 2 else 2       # one or two rows: the GEMV rotates the activations itself
 
     if args.skip_extras:
         if rank == 0:
             print(json.dumps({"metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)",
                               "value": round(value, 1), "unit": "GB/s", "ms_per_step": round(ms_step, 5),
-                              "steps": timed_steps,
-                              "config": {"workload": ",".join(l[0] for l in LAYERS), "rows": rows},
+                              "steps": K_steps, "config": {"workload": ",".join(l[0] for l in LAYERS), "rows": rows},
                               "note": "profiling run: extras skipped"}), flush=True)
         _leave(world)
         return
+
+    # ---- the other batch sizes BASELINE config 2 names, same method, shorter regions
+    by_rows = {str(rows): {"value": round(value, 1), "ms_per_step": round(ms_step, 5)}}
+    if not args.no_graph:
+        for r in (1, 4, 16):
+            if r == rows:
+                continue
+            xr, yr = make_io(r)
+            g = _graph_of(torch, stepper(xr, yr), K_steps, N_SETS)
+            tr_, _ = time_replays(torch, dist, g, world, dev, 60.0, 30)
+            m = tr_[len(tr_) // 2] / K_steps
+            by_rows[str(r)] = {"value": round(bytes_per_step(r) / (m * 1e-3) / 1e9, 1), "ms_per_step": round(m, 5)}
+            del g, xr, yr
+
     # ---- end to end: host activations in, host outputs back, through the plugin's custom op
     hx = {ic: x.cpu().pin_memory() for ic, x in xs.items()}
     hy = [torch.empty((rows, tot), dtype=torch.half).pin_memory() for (_, _, _, tot) in sets[0]]
     lay_args = [[([s["trellis"] for s in sh], [s["suh"] for s in sh], [s["svh"] for s in sh],
                   [s["oc"] for s in sh], [float(s["K"]) for s in sh], [False] * len(sh), [False] * len(sh))
                  for (_, _, sh, _) in layers] for layers in sets]
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
 
     def e2e_step(i):
         layers = sets[i % N_SETS]
@@ -286,14 +368,15 @@ def run_gpu(args):
             hy[li].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
+    n_e2e = max(K_steps, 200)
     for i in range(3):
         e2e_step(i)
     barrier()
     t0 = time.perf_counter()
-    for i in range(args.steps):
+    for i in range(n_e2e):
         e2e_step(i)
     barrier()
-    e2e_eager_s = (time.perf_counter() - t0) / args.steps
+    e2e_eager_s = (time.perf_counter() - t0) / n_e2e
     e2e_s, e2e_mode = e2e_eager_s, "eager: per layer H2D copy, plugin op, D2H copy; one sync per step"
     if not args.no_graph:
         # The serving mode of the plugin (the op is built to replay inside CUDA graphs): per weight set
@@ -334,12 +417,13 @@ def run_gpu(args):
             e2e_graph_step(i)
         barrier()
         t0 = time.perf_counter()
-        for i in range(args.steps):
+        for i in range(n_e2e):
             e2e_graph_step(i)
         barrier()
-        e2e_s = (time.perf_counter() - t0) / args.steps
+        e2e_s = (time.perf_counter() - t0) / n_e2e
         e2e_mode = ("CUDA-graph replay per step of [pinned host x -> device, three orcasaq2::layer_gemm ops, "
-                    "outputs -> pinned host], host inputs rewritten before and one sync after every replay")
+                    "outputs -> pinned host], host inputs rewritten before and one sync after every replay; "
+                    f"{n_e2e} steps timed on the host clock")
     if world > 1:
         t = torch.tensor([e2e_s, e2e_eager_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -347,62 +431,115 @@ def run_gpu(args):
     h2d = sum(rows * ic_r * 2 for (_, ic_r, _, _) in sets[0])
     d2h = sum(rows * tot * 2 for (_, _, _, tot) in sets[0])
 
-    # ---- roofline of the dominant kernel (the gate_up grouped GEMV), timed alone on rank 0
-    roof = None
-    cpu = None
-    if rank == 0:
-        gi = max(range(len(sets[0])), key=lambda j: sum(s_["ic"] * s_["oc"] * s_["K"] for s_ in sets[0][j][2]))
-        name, ic_r, _, _ = sets[0][gi]
-        spec_r = [(s["oc"], s["K"]) for s in sets[0][gi][2]]
-        kb = algorithmic_bytes(ic_r, spec_r, rows)
-        n = 60
-        for i in range(6):
-            _ext.gemv_grouped(xs[ic_r], sets[i % N_SETS][gi][2], ys[i % N_SETS][gi])
-        torch.cuda.synchronize()
-        evs = [torch.cuda.Event(enable_timing=True) for _ in range(n + 1)]
-        evs[0].record()
-        for i in range(n):
-            # rotate through all sets plus the other layers' traffic-free gap: 3 x 67 MB > L2
-            _ext.gemv_grouped(xs[ic_r], sets[i % N_SETS][gi][2], ys[i % N_SETS][gi])
-            evs[i + 1].record()
-        torch.cuda.synchronize()
-        avg_ms = evs[0].elapsed_time(evs[n]) / n
-        peak, kind = measured_peaks()
-        achieved = kb / (avg_ms * 1e-3) / 1e9
-        roof = {"bound": "hbm", "kernel": f"gemv_kernel ({name}, {len(spec_r)} shard(s), one launch)",
-                "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
-                "frac": round(achieved / peak, 4), "frac_of_8000_nominal": round(achieved / 8000.0, 4),
-                "algorithmic_bytes_per_launch": kb, "avg_launch_us": round(avg_ms * 1e3, 2),
-                "traffic": NCU_TRAFFIC_BYTES.get((rows, world))}
-        if world == 1:
-            cpu = cpu_baseline(rows)
+    # ---- roofline of the dominant kernel (the gate_up grouped GEMV), alone: a graph of N_SETS launches over
+    # the rotated weight sets (3 x 67 MB > L2), replayed; duration per launch from CUDA events around each replay
+    gi = max(range(len(sets[0])), key=lambda j: sum(s_["ic"] * s_["oc"] * s_["K"] for s_ in sets[0][j][2]))
+    name, ic_r, _, _ = sets[0][gi]
+    spec_r = [(s["oc"], s["K"]) for s in sets[0][gi][2]]
+    kb = algorithmic_bytes(ic_r, spec_r, rows)
+    xg, yg = make_io(rows)
+
+    def one_layer(i):
+        _ext.gemv_grouped(xg[ic_r], sets[i % N_SETS][gi][2], yg[i % N_SETS][gi])
+
+    peak, kind = measured_peaks()
+    if args.no_graph:
+        avg_ms = ms_step
+    else:
+        g = _graph_of(torch, one_layer, 2 * N_SETS, N_SETS)
+        tl, _ = time_replays(torch, dist, g, 1, dev, 40.0, 50)          # this rank's own kernel, no collective inside
+        avg_ms = tl[len(tl) // 2] / (2 * N_SETS)
+    achieved = kb / (avg_ms * 1e-3) / 1e9
+    roof = {"bound": "hbm", "kernel": f"gemv_kernel ({name}, {len(spec_r)} shard(s), one launch)",
+            "achieved": round(achieved, 1), "peak": peak, "peak_kind": f"of {kind}", "unit": "GB/s",
+            "frac": round(achieved / peak, 4), "frac_of_8000_nominal": round(achieved / 8000.0, 4),
+            "algorithmic_bytes_per_launch": kb, "avg_launch_us": round(avg_ms * 1e3, 2),
+            "timing": "median graph replay of 6 launches over 3 rotated weight sets, CUDA events on the replay stream",
+            "traffic": NCU_TRAFFIC_BYTES.get((rows, world))}
+    by_k = roofline_by_k(torch, dist, _ext, dev, peak) if world == 1 and rank == 0 and not args.no_graph else None
+    cpu = cpu_baseline(rows) if world == 1 and rank == 0 else None
+    tp_model = None
+    if world > 1 and not args.no_decoder:
+        # BASELINE config 5 on the same ranks and kernels: the 27B decoder under tensor parallelism
+        del sets, xs, ys, xg, yg, lay_args, graph
+        torch.cuda.empty_cache()
+        import bench_model
+        try:
+            tp_model = bench_model.run(bench_model.default_args(batch=64, ctx=8192, steps=10, warmup=2))
+        except Exception as e:                                          # noqa: BLE001
+            tp_model = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     if rank != 0:
         _leave(world)
         return
     line = {
         "metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)", "value": round(value, 1),
-        "unit": "GB/s", "n_gpus": world, "steps": timed_steps, "warmup": max(3, args.warmup),
+        "unit": "GB/s", "n_gpus": world, "steps": K_steps, "warmup": warm,
         "ms_per_step": round(ms_step, 5), "higher_is_better": True,
-        "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f16",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16",
         "data": "synthetic",
         "config": {"workload": f"mixed-bitwidth decode shards of one layer (qkv 4/5/6 bpw, gate_up 3 bpw, "
                                f"down 4 bpw), rows={rows}", "rows": rows,
                    "bytes_per_step": full_bytes, "l2": "inputs larger than L2: 3 weight sets of 134 MB rotated",
                    "parallelism": f"tp{world}" if world > 1 else "single GPU",
                    "pct_of_8TBs_nominal": round(value / 8000.0 * 100, 2)},
+        "timing": {"method": f"one CUDA graph of {K_steps} steps replayed {spread['replays']} times, each replay timed "
+                             "with CUDA events (max over ranks); value = median replay",
+                   "timed_region_ms": round(region_ms, 2), "ms_per_step": spread},
+        "by_rows": by_rows,
         "e2e": {"value": round(full_bytes / e2e_s / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 5), "mode": e2e_mode,
                 "eager_ms_per_step": round(e2e_eager_s * 1e3, 5)},
-        # every fused layer is two kernels of this library: the activation pre-pass and the GEMV
-        "gpu_launches": timed_steps * len(LAYERS) * 2, "cuda_graph": graph is not None,
+        # kernels of this library per fused layer: the GEMV, plus the activation pre-pass above two rows
+        "gpu_launches": K_steps * spread["replays"] * len(LAYERS) * launches_per_layer, "cuda_graph": graph is not None,
         "clocks": clocks, "roofline": roof,
     }
+    if by_k is not None:
+        line["roofline_by_k"] = by_k
     if cpu is not None:
         line["cpu_baseline"] = cpu
     if world == 1 and not args.no_decoder:
         line["decoder_27b"] = decoder_tok_s()
+        if cpu is not None and "decoder_27b_tok_s" in cpu:
+            line["decoder_27b"]["cpu_tok_s_bs1"] = cpu["decoder_27b_tok_s"]
+            b1 = line["decoder_27b"].get("bs1", {}).get("value")
+            if b1 and cpu["decoder_27b_tok_s"]:
+                line["decoder_27b"]["gpu_over_cpu_bs1"] = round(b1 / cpu["decoder_27b_tok_s"], 1)
+    if tp_model is not None:
+        line["decoder_27b_tp"] = tp_model
     print(json.dumps(line), flush=True)
     _leave(world)
+
+
+# Decode + mma.sync rate of the 3INST codebook with no memory access at all (registers only, every SM busy),
+# in 10^12 weights per second on B200 at 1.9 GHz, per bitrate: the ceiling of any kernel that decodes this
+# codebook with integer instructions and consumes the codewords with mma.sync (profiles/decode_rate_b200.md).
+DECODE_CEILING_TWS = {2: 6.35, 3: 5.48, 4: 5.96, 5: 5.37, 6: 5.28}
+
+
+def roofline_by_k(torch, dist, _ext, dev, peak):
+    """One 5120 -> 17408 shard at 2..6 bits per weight, 1 and 16 rows: achieved bytes/s against the HBM peak and
+    weights/s against the decode ceiling of that bitrate."""
+    out = {"shape": "5120->17408, one shard", "unit": "GB/s", "peak": peak, "decode_ceiling_tw_s": DECODE_CEILING_TWS,
+           "note": "frac = achieved / HBM peak; of_ceiling = weights per second / register-only decode+mma rate"}
+    ic, oc = 5120, 17408
+    for K in (2, 3, 4, 5, 6):
+        per = ic * oc * K // 8
+        n = int(max(3, 400e6 // per + 1))
+        shards = [[make_shard(torch, ic, oc, K, 9000 + 10 * K + i, dev)] for i in range(n)]
+        for r in (1, 16):
+            x = torch.randn((r, ic), generator=torch.Generator().manual_seed(6)).half().to(dev)
+            y = torch.empty((r, oc), dtype=torch.half, device=dev)
+            g = _graph_of(torch, lambda i: _ext.gemv_grouped(x, shards[i % n], y), n, min(n, 3))
+            ts, _ = time_replays(torch, dist, g, 1, dev, 30.0, 20)
+            sec = ts[len(ts) // 2] / n * 1e-3
+            b = algorithmic_bytes(ic, [(oc, K)], r)
+            out[f"k{K}_rows{r}"] = {"achieved": round(b / sec / 1e9, 1), "frac": round(b / sec / 1e9 / peak, 4),
+                                    "us": round(sec * 1e6, 2), "tw_s": round(ic * oc / sec / 1e12, 3),
+                                    "of_ceiling": round(ic * oc / sec / 1e12 / DECODE_CEILING_TWS[K], 3)}
+            del g
+        del shards
+        torch.cuda.empty_cache()
+    return out
 
 
 def decoder_tok_s():
@@ -435,56 +572,83 @@ NCU_TRAFFIC_BYTES = {(1, 1): 67_521_280}     # profiles/gemv_kernel_gate_up_rows
 
 
 # ------------------------------------------------------------------------------------ CPU arms
-CPU_SAMPLE = ("q shard 5120->6144 @4 bpw", 5120, 6144, 4)
+def _cpu_inputs(R, rows):
+    """Seeded inputs of one whole step on the host: every shard of every fused layer of LAYERS."""
+    out = []
+    for li, (_, ic, spec) in enumerate(LAYERS):
+        for i, (oc, K) in enumerate(spec):
+            tr, suh, svh, x = R.make_layer(4242 + 10 * li + i, ic, oc, K, rows)
+            out.append((x, tr, suh, svh))
+    return out
 
 
-def _cpu_layer_once(torch, R, rows, threads):
-    """One pass of the reference's CPU PyTorch path on the sample shard; seconds."""
-    _, ic, oc, K = CPU_SAMPLE
-    tr, suh, svh, x = R.make_layer(4242, ic, oc, K, rows)
+def _cpu_step_once(torch, R, inputs, threads):
+    """One pass of the reference's CPU PyTorch path (decode -> Hadamard -> matmul -> Hadamard) over all six shards
+    of the workload; seconds."""
     torch.set_num_threads(threads)
     t0 = time.perf_counter()
-    y = R.torch_layer(x, tr, suh, svh)
+    for x, tr, suh, svh in inputs:
+        y = R.torch_layer(x, tr, suh, svh)
     dt = time.perf_counter() - t0
     assert torch.isfinite(y.float()).all()
     return dt
 
 
 def cpu_baseline(rows):
-    """The oracle's PyTorch-CPU path (decode -> Hadamard -> matmul) on the host cores, on a
-    bounded sample, as the same metric (algorithmic bytes per second)."""
+    """The oracle's PyTorch-CPU path on the host cores over the whole workload step, as the same metric
+    (algorithmic bytes per second), on a bounded number of passes; plus the C/OpenMP oracle on the same step and
+    the 27B decoder's CPU token rate extrapolated from per-layer timings."""
     import torch
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import exl3_ref as R
     threads = os.cpu_count() or 1
-    _, ic, oc, K = CPU_SAMPLE
-    _cpu_layer_once(torch, R, rows, threads)
+    inputs = _cpu_inputs(R, rows)
+    full_bytes = sum(algorithmic_bytes(ic, spec, rows) for _, ic, spec in LAYERS)
+    _cpu_step_once(torch, R, inputs, threads)
     n, total = 0, 0.0
-    while total < 10.0 and n < 8:
-        total += _cpu_layer_once(torch, R, rows, threads)
+    while total < 10.0 and n < 6:
+        total += _cpu_step_once(torch, R, inputs, threads)
         n += 1
     sec = total / n
-    b = algorithmic_bytes(ic, [(oc, K)], rows)
-    out = {"value": round(b / sec / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
-           "sample": f"{CPU_SAMPLE[0]}, rows={rows}, {n} passes of {sec:.2f} s (PyTorch-CPU restatement "
-                     f"of the reference path, torch.set_num_threads({threads}))"}
-    try:                                                    # second CPU number: the C/OpenMP oracle
+    out = {"value": round(full_bytes / sec / 1e9, 4), "unit": "GB/s", "cores": threads, "kind": "port",
+           "sample": f"the whole step (all six shards, {full_bytes} bytes), rows={rows}, {n} passes of {sec:.2f} s "
+                     f"(PyTorch-CPU restatement of the reference path, torch.set_num_threads({threads}))"}
+    try:                                                    # second CPU number: the C/OpenMP oracle, same step
         co = R.COracle()
-        tr, suh, svh, x = R.make_layer(4242, ic, oc, K, rows)
         t0 = time.perf_counter()
-        w = co.reconstruct(tr.numpy())
-        co.layer(x.numpy(), w, suh.numpy(), svh.numpy())
-        out["c_openmp_value"] = round(b / (time.perf_counter() - t0) / 1e9, 4)
+        for x, tr, suh, svh in inputs:
+            co.layer(x.numpy(), co.reconstruct(tr.numpy()), suh.numpy(), svh.numpy())
+        out["c_openmp_value"] = round(full_bytes / (time.perf_counter() - t0) / 1e9, 4)
     except Exception as e:                                  # noqa: BLE001
         out["c_openmp_value"] = None
         out["c_openmp_error"] = str(e)[:80]
+    try:
+        # 27B decoder at batch 1 on the same cores: a layer is the step above plus o_proj (6144 -> 5120); the head is
+        # the reference's dequantise-then-linear on one eighth of the vocabulary, times eight; attention left out
+        # (it would only lower the figure)
+        tr, suh, svh, x = R.make_layer(4300, 6144, 5120, 4, 1)
+        torch.set_num_threads(threads)
+        t0 = time.perf_counter()
+        R.torch_layer(x, tr, suh, svh)
+        o_sec = time.perf_counter() - t0
+        q, sc = R.make_int8_table(4301, 151936 // 8, 5120)
+        xh = torch.randn((1, 5120), generator=torch.Generator().manual_seed(7)).half()
+        t0 = time.perf_counter()
+        R.int8_head_torch(q, sc, xh)
+        head_sec = 8 * (time.perf_counter() - t0)
+        tok = 1.0 / (64 * (sec + o_sec) + head_sec)
+        out["decoder_27b_tok_s"] = round(tok, 5)
+        out["decoder_27b_note"] = (f"extrapolated: 64 x ({sec:.2f} s step + {o_sec:.2f} s o_proj) + {head_sec:.2f} s head "
+                                   f"per token on {threads} cores, attention not counted")
+    except Exception as e:                                  # noqa: BLE001
+        out["decoder_27b_error"] = str(e)[:80]
     return out
 
 
 def run_reference(args):
-    """The reference's CPU implementation of the path (its PyTorch restatement: the trellis
-    kernels themselves live in a wheel that is not part of the reference tree), host cores only.
-    Same metric and config as the GPU arm; each step is one pass over the bounded sample."""
+    """The reference's CPU implementation of the path (its PyTorch restatement: the trellis kernels themselves live
+    in a wheel that is not part of the reference tree), host cores only.  Same metric and config as the GPU arm;
+    a step is one pass over all six shards of the workload."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
     import torch
@@ -492,24 +656,24 @@ def run_reference(args):
     import exl3_ref as R
     threads = os.cpu_count() or 1
     rows = args.rows
-    steps = max(1, min(args.steps, 6))
-    for _ in range(max(1, min(args.warmup, 2))):
-        _cpu_layer_once(torch, R, rows, threads)
-    t = [_cpu_layer_once(torch, R, rows, threads) for _ in range(steps)]
+    inputs = _cpu_inputs(R, rows)
+    warm = max(1, min(args.warmup, 5))
+    first = [_cpu_step_once(torch, R, inputs, threads) for _ in range(warm)]
+    # the whole run must end within a few minutes whatever --steps is
+    steps = max(1, min(args.steps, int(240.0 / max(first[-1], 1e-3))))
+    t = [_cpu_step_once(torch, R, inputs, threads) for _ in range(steps)]
     sec = sum(t) / len(t)
-    _, ic, oc, K = CPU_SAMPLE
-    b = algorithmic_bytes(ic, [(oc, K)], rows)
-    v = round(b / sec / 1e9, 4)
     full_bytes = sum(algorithmic_bytes(i, spec, rows) for _, i, spec in LAYERS)
-    sample = (f"{CPU_SAMPLE[0]}, rows={rows}: each step is one pass over this shard "
-              f"({b} of the workload's {full_bytes} bytes)")
+    v = round(full_bytes / sec / 1e9, 4)
+    sample = f"the whole step: all six shards ({full_bytes} bytes), rows={rows}, {steps} steps after {warm} warm-up"
     print(json.dumps({
         "impl": "reference", "metric": "EXL3 fused decode GEMV throughput (trellis + activation bytes)",
         "value": v, "unit": "GB/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": steps,
-        "warmup": max(1, min(args.warmup, 2)), "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "warmup": warm, "ms_per_step": round(sec * 1e3, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": {"workload": f"mixed-bitwidth decode shards of one layer (qkv 4/5/6 bpw, gate_up 3 bpw, "
-                               f"down 4 bpw), rows={rows}", "rows": rows, "sample": sample},
+                               f"down 4 bpw), rows={rows}", "rows": rows, "bytes_per_step": full_bytes,
+                   "parallelism": "host cores"},
         "cpu_baseline": {"value": v, "unit": "GB/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -519,7 +683,7 @@ def run_reference(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--rows", type=int, default=1, choices=range(1, 17))
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])

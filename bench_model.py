@@ -31,6 +31,7 @@ import torch.distributed as dist  # noqa: E402
 import torch.nn.functional as F  # noqa: E402
 
 HIDDEN, FFN, LAYERS, QH, KVH, HD, VOCAB = 5120, 17408, 64, 24, 4, 256, 151936
+DIMS_27B = dict(hidden=HIDDEN, ffn=FFN, qh=QH, kvh=KVH, hd=HD, vocab=VOCAB)
 TC_FROM_ROWS = 9           # batch sizes from here on take the tcgen05 path (--tc-from; measured faster from 9 rows)
 
 
@@ -82,7 +83,11 @@ def rms(x, eps=1e-6):
     return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).half()
 
 
-def build(rank, world, batch, ctx, dev, layers):
+def build(rank, world, batch, ctx, dev, layers, dims=None):
+    """Random-init decoder of `layers` layers on this rank: [(qkv, o, gate_up, down, k_cache, v_cache)], the int8
+    table and its scales, bytes of packed weights and of KV cache read per step, and the local head counts."""
+    d = dims or DIMS_27B
+    HIDDEN, FFN, QH, KVH, HD, VOCAB = d["hidden"], d["ffn"], d["qh"], d["kvh"], d["hd"], d["vocab"]
     kgen = torch.Generator().manual_seed(2026)                        # bitrates: same on every rank
     wgen = torch.Generator(device=dev).manual_seed(1234 + rank)
     qh, kvh = QH // world, max(1, KVH // world)
@@ -105,30 +110,20 @@ def build(rank, world, batch, ctx, dev, layers):
     return model, table, scales, wbytes + vslice * HIDDEN, kvbytes, qh, kvh
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--batch", type=int, default=1)
-    ap.add_argument("--ctx", type=int, default=4096)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for a quick functional run")
-    ap.add_argument("--no-graph", action="store_true")
-    ap.add_argument("--attn", choices=["own", "sdpa"], default="own",
-                    help="decode attention: this library's kernel, or torch's scaled_dot_product_attention")
-    ap.add_argument("--tc-from", type=int, default=9, help="smallest batch that takes the tcgen05 path (9..17)")
-    args = ap.parse_args()
-    global TC_FROM_ROWS
-    TC_FROM_ROWS = max(9, min(17, args.tc_from))
-    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+def default_args(**over):
+    """The command-line defaults as a namespace (for callers that run the benchmark in-process)."""
+    ns = argparse.Namespace(batch=1, ctx=4096, steps=20, warmup=3, layers=LAYERS, no_graph=False, attn="own", tc_from=9)
+    for k, v in over.items():
+        setattr(ns, k, v)
+    return ns
+
+
+def make_step(model, table, scales, ids, B, ctx, qh, kvh, world, attn="own", dims=None):
+    """One decode step over `model` as a closure: returns (argmax token per sequence, logits of this rank's
+    vocabulary slice).  The new token's key and value go to cache position `ctx`."""
     from orcasaq2 import _ext
-    _ext.lib()
-    B, ctx = args.batch, args.ctx
-    model, table, scales, wbytes, kvbytes, qh, kvh = build(rank, world, B, ctx, dev, args.layers)
-    ids = torch.randint(0, table.shape[0], (B,), device=dev)
+    HD = (dims or DIMS_27B)["hd"]
+    dev = table.device
     pos = torch.arange(HD // 2, device=dev).float()
     ang = ctx / (10000.0 ** (pos / (HD // 2)))
     cos, sin = torch.cos(ang).half(), torch.sin(ang).half()
@@ -143,18 +138,16 @@ def main():
             dist.all_reduce(h)                                            # vocabulary-parallel embedding
         for qkv, o, gu, down, kc, vc in model:
             y = qkv(h, in_mode=1)
-            if args.attn == "sdpa":
+            if attn == "sdpa":
                 qk = rope(y[:, :(qh + kvh) * HD].reshape(B, qh + kvh, HD))    # query and key heads in one pass
                 q, k = qk[:, :qh], qk[:, qh:]
                 v = y[:, (qh + kvh) * HD:].reshape(B, kvh, HD)
                 kc[:, :, ctx] = k
                 vc[:, :, ctx] = v
+                att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
             else:
                 _ext.rope_append(y, cos, sin, kc, vc, ctx, qh)            # rotary + cache append, one launch
                 q = torch.as_strided(y, (B, qh, HD), (y.stride(0), HD, 1))
-            if args.attn == "sdpa":
-                att = F.scaled_dot_product_attention(q.unsqueeze(2), kc, vc, enable_gqa=True)   # [B, qh, 1, HD]
-            else:
                 att = _ext.decode_attn(q, kc, vc, ctx + 1)                # [B, qh, HD], split-KV kernel of this library
             if world > 1:
                 a = o(att.reshape(B, qh * HD))
@@ -170,10 +163,31 @@ def main():
             else:
                 h = down(g, in_mode=2, residual=h)
         logits = _ext.int8_head(table, scales, rms(h))                    # vocabulary slice of this rank
-        return logits.argmax(-1)
+        return logits.argmax(-1), logits
+
+    return step
+
+
+def run(args):
+    """Build the decoder on this rank, time `args.steps` decode steps, and return the result line as a dict on
+    rank 0 (None elsewhere).  Joins the process group that is there, or creates one when launched multi-rank
+    without one."""
+    global TC_FROM_ROWS
+    TC_FROM_ROWS = max(9, min(17, args.tc_from))
+    world, rank, local = int(os.environ.get("WORLD_SIZE", "1")), int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=dev)
+    from orcasaq2 import _ext
+    _ext.lib()
+    B, ctx = args.batch, args.ctx
+    model, table, scales, wbytes, kvbytes, qh, kvh = build(rank, world, B, ctx, dev, args.layers)
+    ids = torch.randint(0, table.shape[0], (B,), device=dev)
+    step = make_step(model, table, scales, ids, B, ctx, qh, kvh, world, args.attn)
 
     for _ in range(max(2, args.warmup)):
-        out = step()
+        step()
     torch.cuda.synchronize()
     graph = None
     if not args.no_graph:
@@ -184,19 +198,19 @@ def main():
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=s):
-                out = step()
+                step()
         torch.cuda.current_stream().wait_stream(s)
         torch.cuda.synchronize()
-    run = graph.replay if graph is not None else step
+    run_once = graph.replay if graph is not None else step
     for _ in range(3):
-        run()
+        run_once()
     if world > 1:
         dist.barrier()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        run()
+        run_once()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
@@ -204,22 +218,40 @@ def main():
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    if rank == 0:
-        peak = 6549.8
-        try:
-            peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
-        except Exception:                                                 # noqa: BLE001
-            pass
-        per_gpu = (wbytes + kvbytes) / (ms * 1e-3) / 1e9
-        print(json.dumps({
-            "metric": "27B EXL3 decode tokens/s", "value": round(B / (ms * 1e-3), 2), "unit": "tok/s",
-            "ms_per_step": round(ms, 4), "n_gpus": world, "batch": B, "ctx": ctx, "layers": args.layers,
-            "cuda_graph": graph is not None, "status_word": _ext.workspace_status(dev),
-            "per_gpu_bytes_per_step": {"packed_weights": wbytes, "kv_cache": kvbytes},
-            "per_gpu_hbm_gbs": round(per_gpu, 1), "frac_of_measured_hbm": round(per_gpu / peak, 4),
-            "data": "synthetic (random-init weights, random KV cache)", "attention": "exl3_decode_attn" if args.attn == "own" else "torch SDPA (library)",
-        }), flush=True)
-    if world > 1:
+    if rank != 0:
+        return None
+    peak = 6549.8
+    try:
+        peak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["hbm_gbs"])
+    except Exception:                                                 # noqa: BLE001
+        pass
+    per_gpu = (wbytes + kvbytes) / (ms * 1e-3) / 1e9
+    return {
+        "metric": "27B EXL3 decode tokens/s", "value": round(B / (ms * 1e-3), 2), "unit": "tok/s",
+        "ms_per_step": round(ms, 4), "n_gpus": world, "batch": B, "ctx": ctx, "layers": args.layers,
+        "cuda_graph": graph is not None, "status_word": _ext.workspace_status(dev),
+        "per_gpu_bytes_per_step": {"packed_weights": wbytes, "kv_cache": kvbytes},
+        "per_gpu_hbm_gbs": round(per_gpu, 1), "frac_of_measured_hbm": round(per_gpu / peak, 4),
+        "data": "synthetic (random-init weights, random KV cache)", "attention": "exl3_decode_attn" if args.attn == "own" else "torch SDPA (library)",
+    }
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--ctx", type=int, default=4096)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--layers", type=int, default=LAYERS, help="fewer layers for a quick functional run")
+    ap.add_argument("--no-graph", action="store_true")
+    ap.add_argument("--attn", choices=["own", "sdpa"], default="own",
+                    help="decode attention: this library's kernel, or torch's scaled_dot_product_attention")
+    ap.add_argument("--tc-from", type=int, default=9, help="smallest batch that takes the tcgen05 path (9..17)")
+    args = ap.parse_args()
+    line = run(args)
+    if line is not None:
+        print(json.dumps(line), flush=True)
+    if int(os.environ.get("WORLD_SIZE", "1")) > 1:
         # leave without tearing down NCCL under a live captured graph (that teardown can block)
         torch.cuda.synchronize()
         dist.barrier()

@@ -40,7 +40,8 @@ enum {
     EXL3_E_UNSUPPORTED = -3, /* K, codebook flag or mode not implemented */
     EXL3_E_LAUNCH = -4,      /* CUDA reported an error on launch */
     EXL3_E_WORKSPACE = -5,   /* scratch buffer missing or too small */
-    EXL3_E_NULL = -6         /* required pointer is NULL */
+    EXL3_E_NULL = -6,        /* required pointer is NULL */
+    EXL3_E_DEVICE = -7       /* a tensor lives on another device than the current one */
 };
 
 int exl3_abi_version(void);
@@ -179,16 +180,24 @@ unsigned exl3_gemm_tc_status(void);
  *   - Inputs, outputs and all argument rules are those of exl3_gemv_grouped.
  *   - A launch whose scratch need (exl3_gemv_workspace_bytes) exceeds the capacity returns
  *     EXL3_E_WORKSPACE and launches nothing; use exl3_gemv_grouped with your own buffer then.
- *   - The FIRST call on each device resolves the array's device address and queues a clear of
- *     its header on the given stream.  Make that first call with the device current and before
- *     any stream capture begins.
+ *   - The scratch used is the copy of the array on the CURRENT device.  x and y must live on that
+ *     device; a call made with another device current returns EXL3_E_DEVICE and launches nothing.
+ *   - The FIRST call on each device looks up the array's device address (once, under a lock, so
+ *     host threads may race to it); make that first call with the device current and before any
+ *     stream capture begins.  Nothing is cleared at that point: the loader hands the array over
+ *     zero-filled, which is the state the kernels need and restore.
  *   - All calls on a device share the one array, which keeps what the last call left in it:
  *     the kernel restores the parts that must be zero before it exits, but two calls that
- *     overlap on the GPU (different streams without ordering) race on it.  Serialise them.
+ *     overlap on the GPU (different streams without ordering, or two host threads launching
+ *     without ordering between their streams) race on it.  Serialise them.
+ *   - exl3_gemv_static_status(&word) copies the sticky status word of the current device's array
+ *     to the host (it waits for the device; for diagnosis and tests): 0, or non-zero after a
+ *     bounded wait inside a kernel launched through this entry point ran out.
  */
 size_t exl3_gemv_static_capacity(void);
 int exl3_gemv_grouped_static(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
                              int ic, int ldy, void *stream);
+int exl3_gemv_static_status(unsigned *status_out);
 
 /*
  * The word at byte offset 0 of a GEMV workspace is a sticky device-side status: 0, or

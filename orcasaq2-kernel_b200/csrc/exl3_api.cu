@@ -12,6 +12,7 @@ extern "C" const char *exl3_strerror(int code) {
         case EXL3_E_LAUNCH: return "CUDA launch failed";
         case EXL3_E_WORKSPACE: return "workspace missing or too small";
         case EXL3_E_NULL: return "required pointer is NULL";
+        case EXL3_E_DEVICE: return "a tensor does not live on the current device";
     }
     return "unknown error";
 }

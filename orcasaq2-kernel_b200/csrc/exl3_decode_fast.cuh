@@ -109,6 +109,60 @@ struct PairDecoder<K, 16> {
     static __device__ __forceinline__ void run(const uint32_t (&)[K + 1], uint32_t (&)[32], const DecodeConsts &) {}
 };
 
+// Codewords [LO, HI) of one chunk (LO, HI multiples of 16), for callers that consume a chunk in two halves to
+// keep fewer codewords alive at a time.  v: the words shifted by 16 bits (shifted_words), unused when K divides 16.
+template <int K, int I, int HI>
+struct SplitRange {
+    static __device__ __forceinline__ void run(const uint32_t (&w)[K + 1], const uint32_t (&v)[K], uint32_t (&z)[32]) {
+        z[I] = mask_xor_v(mad_code<kAdd>(chunk_state_split<K, I>(w, v)));
+        SplitRange<K, I + 1, HI>::run(w, v, z);
+    }
+};
+template <int K, int HI>
+struct SplitRange<K, HI, HI> {
+    static __device__ __forceinline__ void run(const uint32_t (&)[K + 1], const uint32_t (&)[K], uint32_t (&)[32]) {}
+};
+template <int K, int J, int JHI>
+struct PairRange {
+    static constexpr int P = 16 / K;
+    static __device__ __forceinline__ void run(const uint32_t (&w)[K + 1], uint32_t (&z)[32], const DecodeConsts &dc) {
+        constexpr int a = (J / P) * 2 * P + (J % P);
+        constexpr int b = a + P;
+        constexpr int off = a * K;
+        constexpr int q = off >> 5;
+        constexpr int o = off & 31;
+        uint32_t Q;
+        if constexpr (o == 0) Q = w[q];
+        else Q = __funnelshift_r(w[q], w[q + 1], o);
+        const uint32_t sb = Q >> 16;
+        const uint32_t zb = mad_code<kAdd>(sb);
+        const uint32_t t = mad_code<kAdd + (kAdd << 16)>(Q);
+        const uint32_t za = mad_u32(zb, dc.neg65536, t);
+        z[a] = mask_xor_v(za);
+        z[b] = mask_xor_v(zb);
+        PairRange<K, J + 1, JHI>::run(w, z, dc);
+    }
+};
+template <int K, int JHI>
+struct PairRange<K, JHI, JHI> {
+    static __device__ __forceinline__ void run(const uint32_t (&)[K + 1], uint32_t (&)[32], const DecodeConsts &) {}
+};
+template <int K>
+__device__ __forceinline__ void shifted_words(const uint32_t (&w)[K + 1], uint32_t (&v)[K]) {
+    if constexpr (16 % K != 0) {
+#pragma unroll
+        for (int q = 0; q < K; ++q) v[q] = __funnelshift_r(w[q], w[q + 1], 16);
+    }
+}
+// pairs of a chunk lie inside blocks of 2 * (16 / K) consecutive weights, so a half chunk holds whole pairs for K >= 2
+template <int K, int LO, int HI>
+__device__ __forceinline__ void decode_range_fast(const uint32_t (&w)[K + 1], const uint32_t (&v)[K], uint32_t (&z)[32],
+                                                  const DecodeConsts &dc) {
+    static_assert(LO % 16 == 0 && HI % 16 == 0 && K >= 2, "half chunks only, and not at one bit per weight");
+    if constexpr (16 % K == 0) PairRange<K, LO / 2, HI / 2>::run(w, z, dc);
+    else SplitRange<K, LO, HI>::run(w, v, z);
+}
+
 // 32 codewords of one chunk, identical to decode_chunk<K>
 template <int K>
 __device__ __forceinline__ void decode_chunk_fast(const uint32_t (&w)[K + 1], uint32_t (&z)[32],

@@ -19,7 +19,8 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
-#include <stdlib.h>
+
+#include <mutex>
 
 #include "exl3_codec.cuh"
 #include "exl3_common.cuh"
@@ -104,12 +105,14 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
-// Bounded wait: gives up after kSpinLimit polls and reports through the status word.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status) {
-    for (int it = 0; it < kSpinLimit; ++it)
-        if (mbar_try_wait(bar, parity)) return true;
-    atomicOr(status, kStatusTimeout);
-    return false;
+// Bounded wait, the same answer in every lane of the warp: gives up after `limit` polls and reports through
+// the status word.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status, int limit = kSpinLimit) {
+    bool done = false;
+    for (int it = 0; it < limit && !done; ++it) done = mbar_try_wait(bar, parity);
+    done = __all_sync(0xffffffffu, done);
+    if (!done && (threadIdx.x & 31) == 0) atomicOr(status, kStatusTimeout);
+    return done;
 }
 __device__ __forceinline__ void bulk_g2s(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
     asm volatile(
@@ -125,26 +128,41 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t *a, uint3
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-// Phase timestamps of every CTA (start, after the dependency wait, activations landed, main loop
-// done, partial sums stored, ticket taken, end), compiled in only for timing studies.
-#ifdef EXL3_GEMV_TRACE
-__device__ unsigned long long g_gemv_trace[8192][8];
-#define EXL3_TRACE(slot)                                                                       \
-    do {                                                                                       \
-        if (threadIdx.x == 0) {                                                                \
-            unsigned long long t_;                                                             \
-            asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                             \
-            g_gemv_trace[blockIdx.x][slot] = t_;                                               \
-            if (slot == 0) {                                                                   \
-                unsigned sm_;                                                                  \
-                asm volatile("mov.u32 %0, %%smid;" : "=r"(sm_));                               \
-                g_gemv_trace[blockIdx.x][7] = sm_;                                             \
-            }                                                                                  \
-        }                                                                                      \
-    } while (0)
-#else
-#define EXL3_TRACE(slot) do { } while (0)
-#endif
+// The 32 codewords of one chunk (four tiles' worth of one lane) times the activations: acc[t][h][a] += ...
+template <int K, int NT>
+__device__ __forceinline__ void consume_chunk(const uint32_t (&w)[K + 1], float (&acc)[NT][2][4][4], const int h,
+                                              const uint4 (&xa)[NT], const DecodeConsts &dc) {
+    uint32_t z[32];
+    if constexpr (K == 1) {
+        decode_chunk_fast<K>(w, z, dc);
+#pragma unroll
+        for (int bsel = 0; bsel < 2; ++bsel)
+#pragma unroll
+            for (int a = 0; a < 4; ++a)
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    mma16816(acc[t][h][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
+    } else {
+        uint32_t v[K];
+        shifted_words<K>(w, v);
+        decode_range_fast<K, 0, 16>(w, v, z, dc);
+#pragma unroll
+        for (int bsel = 0; bsel < 2; ++bsel)
+#pragma unroll
+            for (int a = 0; a < 2; ++a)
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    mma16816(acc[t][h][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
+        decode_range_fast<K, 16, 32>(w, v, z, dc);
+#pragma unroll
+        for (int bsel = 0; bsel < 2; ++bsel)
+#pragma unroll
+            for (int a = 2; a < 4; ++a)
+#pragma unroll
+                for (int t = 0; t < NT; ++t)
+                    mma16816(acc[t][h][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
+    }
+}
 
 // ---------------------------------------------------------------------------------------------
 template <int K, int NT>
@@ -160,7 +178,6 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     const int g = lane >> 2, q = lane & 3;
     const int NB = P.nb;
     const DecodeConsts dc(P.one);
-    EXL3_TRACE(0);
 
     const int ob = local / S.splitk, ks = local - ob * S.splitk;
     const int kb0 = (int)((long long)ks * P.kblocks / S.splitk);
@@ -221,7 +238,6 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     // finish, and let the grid after this one begin its own weight prefetch.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
-    EXL3_TRACE(1);
 
     for (int b0 = 0; b0 < nblk; b0 += sub_max) {
         const int nb_sub = min(sub_max, nblk - b0);
@@ -234,7 +250,6 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         }
         ok = mbar_wait(xbar, xphase, P.status) && ok;
         xphase ^= 1u;
-        if (b0 == 0) EXL3_TRACE(2);
 
         // ---- stream, decode, multiply
         const uint32_t *xfp = xf_lane;
@@ -251,16 +266,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             wa[K] = __shfl_sync(0xffffffffu, wa[0], nxt_lane);
             wb[K] = __shfl_sync(0xffffffffu, wb[0], nxt_lane);
 
-            uint32_t z[32];
-            decode_chunk_fast<K>(wa, z, dc);
-#pragma unroll
-            for (int bsel = 0; bsel < 2; ++bsel)
-#pragma unroll
-                for (int a = 0; a < 4; ++a)
-#pragma unroll
-                    for (int t = 0; t < NT; ++t)
-                        mma16816(acc[t][0][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
-            decode_chunk_fast<K>(wb, z, dc);
+            consume_chunk<K, NT>(wa, acc, 0, xa, dc);
             // every lane has consumed the slot (its words are in registers): refill it
             __syncwarp();
             if (lane == 0 && s + kDepth < nblk) {
@@ -268,18 +274,17 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
                 bulk_g2s(ring0 + slot * kStageBytes, src0 + (size_t)(s + kDepth) * src_step, kStageBytes,
                          bar0 + 8 * slot);
             }
-#pragma unroll
-            for (int bsel = 0; bsel < 2; ++bsel)
-#pragma unroll
-                for (int a = 0; a < 4; ++a)
-#pragma unroll
-                    for (int t = 0; t < NT; ++t)
-                        mma16816(acc[t][1][a], &z[8 * a + 4 * bsel], bsel ? xa[t].z : xa[t].x, bsel ? xa[t].w : xa[t].y);
+            consume_chunk<K, NT>(wb, acc, 1, xa, dc);
             if (++slot == kDepth) { slot = 0; phase ^= 1u; }
         }
     }
+    // a wait that ran out leaves copies that may still be in flight into this warp's ring: give them one more
+    // bounded chance to land before the region is reused and the CTA goes away
+    if (!ok) {
+#pragma unroll
+        for (int s = 0; s < kDepth; ++s) mbar_wait(bar0 + 8 * s, s < slot ? phase ^ 1u : phase, P.status, 1 << 16);
+    }
     __syncthreads();   // every warp is done with its ring: the region is reused below
-    EXL3_TRACE(3);
 
     // ---- reduce the eight warps, eight rows (one accumulator tile) per pass: the staging buffer stays
     // small enough for two CTAs per SM also with sixteen rows
@@ -314,8 +319,6 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
         }
     }
-
-    EXL3_TRACE(4);
     if (S.splitk > 1) {
         __shared__ unsigned s_last;
         __threadfence();
@@ -326,7 +329,6 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             if (s_last) P.tickets[unit] = 0u;   // ready for the next launch
         }
         __syncthreads();
-        EXL3_TRACE(5);
         if (!s_last) return;
         __threadfence();
         for (int n = tid >> 7; n < P.rows; n += 2) {
@@ -370,7 +372,6 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         o.y = *reinterpret_cast<const uint32_t *>(&o23);
         *reinterpret_cast<uint2 *>(P.y + (size_t)n * P.ldy + ocol) = o;
     }
-    EXL3_TRACE(6);
 }
 
 // Pre-pass: H128(x * suh) of every shard, rounded to fp16 once, written in the order the GEMV's
@@ -471,17 +472,6 @@ struct GemvPlan {
     long long partial_off[EXL3_MAX_SHARDS];
 };
 
-// CTAs per launch the plan aims for; EXL3_GEMV_TARGET_CTAS overrides it (tuning knob).
-static int target_ctas() {
-    static int v = 0;
-    if (!v) {
-        const char *e = getenv("EXL3_GEMV_TARGET_CTAS");
-        v = e ? atoi(e) : kTargetCtas;
-        if (v < 1) v = kTargetCtas;
-    }
-    return v;
-}
-
 static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl) {
     if (!sh) return EXL3_E_NULL;
     if (n < 1 || n > EXL3_MAX_SHARDS || rows < 1 || rows > EXL3_GEMV_MAX_ROWS || ic <= 0 || (ic & 127))
@@ -507,7 +497,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     for (int i = 0; i < n; ++i) {
         const int ocb = sh[i].oc / 128;
         const double share = (double)ic * sh[i].oc * pl.K[i] / 8.0 / total_bytes;
-        int sk = (int)(target_ctas() * share / ocb + 0.5);
+        int sk = (int)(kTargetCtas * share / ocb + 0.5);
         if (sk < 1) sk = 1;
         if (sk > pl.kblocks) sk = pl.kblocks;
         if (sk > kMaxSplitK) sk = kMaxSplitK;
@@ -671,30 +661,43 @@ extern "C" int exl3_gemv(const void *x, const void *trellis, void *y, const void
 // memory instead of a caller buffer.
 //
 // The array below is reserved on every GPU that loads the library and stays reserved until the
-// process exits.  In HOST code its name is only a handle, not a device address, so the address is
-// looked up once per device with cudaGetSymbolAddress (with that device current) and cached.
+// process exits; the loader zero-fills it, which is the state the kernel needs (status word and
+// tickets at zero) and the state every launch restores.  In HOST code its name is only a handle,
+// not a device address, so the address is looked up once per device with cudaGetSymbolAddress
+// (with that device current) and cached.
 #define EXL3_STATIC_WS_BYTES_IMPL (2u << 20)
 static __device__ __align__(256) unsigned char g_exl3_static_ws[EXL3_STATIC_WS_BYTES_IMPL];
 
 namespace exl3 {
 constexpr int kMaxDevices = 64;
 static void *g_static_ws_ptr[kMaxDevices];       // device address of g_exl3_static_ws, per device
-static int g_static_ws_ready[kMaxDevices];
+static std::mutex g_static_ws_mutex;
 
-// First use on the current device: resolve the device address and zero the status word and the
-// tickets (asynchronously, on the caller's stream, ahead of the first launch).
-static int static_ws_for_current_device(cudaStream_t st, void **out) {
+// Device address of the built-in scratch on the CURRENT device; resolved under a lock on first use, so
+// two host threads making the first call on one device get the same answer and nothing is queued.
+static int static_ws_for_current_device(void **out, int *dev_out) {
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-    if (!__atomic_load_n(&g_static_ws_ready[dev], __ATOMIC_ACQUIRE)) {
-        void *p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_exl3_static_ws) != cudaSuccess || !p) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-        if (cudaMemsetAsync(p, 0, kWsHeadBytes, st) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-        g_static_ws_ptr[dev] = p;
-        __atomic_store_n(&g_static_ws_ready[dev], 1, __ATOMIC_RELEASE);
+    void *p = __atomic_load_n(&g_static_ws_ptr[dev], __ATOMIC_ACQUIRE);
+    if (!p) {
+        std::lock_guard<std::mutex> lock(g_static_ws_mutex);
+        p = g_static_ws_ptr[dev];
+        if (!p) {
+            if (cudaGetSymbolAddress(&p, g_exl3_static_ws) != cudaSuccess || !p) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+            __atomic_store_n(&g_static_ws_ptr[dev], p, __ATOMIC_RELEASE);
+        }
     }
-    *out = g_static_ws_ptr[dev];
+    *out = p;
+    if (dev_out) *dev_out = dev;
     return EXL3_OK;
+}
+
+// The device a pointer belongs to, or -1 when the runtime does not know it as device memory.
+static int device_of(const void *p) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return -1; }
+    if (a.type != cudaMemoryTypeDevice && a.type != cudaMemoryTypeManaged) return -1;
+    return a.device;
 }
 }  // namespace exl3
 
@@ -707,8 +710,27 @@ extern "C" int exl3_gemv_grouped_static(const exl3_shard *shards, int nshards, c
     const int rc = make_plan(shards, nshards, rows, ic, pl);
     if (rc != EXL3_OK) return rc;
     if (plan_workspace_bytes(pl) > (size_t)EXL3_STATIC_WS_BYTES_IMPL) return EXL3_E_WORKSPACE;   // beyond the built-in scratch
+    if (!x || !y) return EXL3_E_NULL;
     void *ws = nullptr;
-    const int rs = static_ws_for_current_device(static_cast<cudaStream_t>(stream), &ws);
+    int dev = -1;
+    const int rs = static_ws_for_current_device(&ws, &dev);
     if (rs != EXL3_OK) return rs;
+    // the scratch is the CURRENT device's copy of the array: refuse tensors that live elsewhere
+    if (device_of(x) != dev || device_of(y) != dev) return EXL3_E_DEVICE;
     return exl3_gemv_grouped(shards, nshards, x, y, rows, ic, ldy, ws, EXL3_STATIC_WS_BYTES_IMPL, stream);
+}
+
+extern "C" int exl3_gemv_static_status(unsigned *status_out) {
+    using namespace exl3;
+    if (!status_out) return EXL3_E_NULL;
+    void *ws = nullptr;
+    const int rs = static_ws_for_current_device(&ws, nullptr);
+    if (rs != EXL3_OK) return rs;
+    unsigned v = 0;
+    if (cudaMemcpy(&v, static_cast<unsigned char *>(ws) + EXL3_WS_STATUS_OFFSET, sizeof(v), cudaMemcpyDeviceToHost) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    *status_out = v;
+    return EXL3_OK;
 }

@@ -10,6 +10,7 @@ from __future__ import annotations
 import ctypes
 import os
 import threading
+import warnings
 
 import torch
 
@@ -83,6 +84,8 @@ def lib():
                 L.exl3_gemv_static_capacity.restype = sz
                 L.exl3_gemv_grouped_static.argtypes = [ctypes.POINTER(Exl3Shard), ci, vp, vp, ci, ci, ci, vp]
                 L.exl3_gemv_grouped_static.restype = ci
+                L.exl3_gemv_static_status.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+                L.exl3_gemv_static_status.restype = ci
                 L.exl3_decode_attn_workspace_bytes.restype = sz
                 L.exl3_decode_attn_workspace_bytes.argtypes = [ci, ci, ci, ci]
                 L.exl3_decode_attn.argtypes = [vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ll, ll, ll, ll, cf, vp]
@@ -132,21 +135,40 @@ def _trellis_dims(trellis: torch.Tensor):
 
 
 # --------------------------------------------------------------------------- workspaces
-# Scratch for the fused GEMV: split-K partial sums, arrival tickets, a status word.  One buffer
-# per (device, stream), grown on demand and zero-filled when (re)allocated; the kernels leave
-# the tickets at zero.  Allocation happens outside of CUDA-graph capture only if the first call
-# of a given size is made before capture (warm-up), as vLLM does.
+# Scratch for the fused GEMV: rotated activations, partial sums of shared output blocks, arrival
+# tickets, a status word.  One buffer per (device, stream), zero-filled when allocated; the kernels
+# leave the tickets at zero.  The default size covers every launch of the 27B-class shapes at up to
+# 16 rows, so the buffer made by `ensure_gemv_workspace` (called when a layer's weights are loaded)
+# is the one every later launch uses and nothing is allocated under CUDA-graph capture.  A launch
+# that does need more gets a new, larger buffer; the old one is kept alive, because graphs captured
+# earlier still write to it.
+GEMV_WORKSPACE_BYTES = 16 << 20
 _workspaces: dict = {}
+_retired: list = []
 
 
 def gemv_workspace(device: torch.device, nbytes: int) -> torch.Tensor:
     key = (device.index, torch.cuda.current_stream(device).cuda_stream)
     ws = _workspaces.get(key)
     if ws is None or ws.numel() < nbytes:
-        size = max(nbytes, 8 << 20)
-        ws = torch.zeros(size, dtype=torch.uint8, device=device)
+        if torch.cuda.is_current_stream_capturing():
+            # it still works (the buffer then lives in the graph's memory pool and its zero-fill is
+            # replayed with the graph), but it ties the scratch to that graph: say so once
+            warnings.warn(
+                "orcasaq2: the fused GEMV is allocating its scratch buffer inside a CUDA-graph capture; "
+                "call orcasaq2._ext.ensure_gemv_workspace(device) on the capturing stream before the "
+                "capture (any warm-up call on that stream does it too)", RuntimeWarning, stacklevel=3)
+        if ws is not None:
+            _retired.append(ws)
+        ws = torch.zeros(max(nbytes, GEMV_WORKSPACE_BYTES), dtype=torch.uint8, device=device)
         _workspaces[key] = ws
     return ws
+
+
+def ensure_gemv_workspace(device: torch.device, nbytes: int = 0) -> None:
+    """Allocate (and zero) the GEMV scratch of the current stream of `device` now, outside of any
+    capture, so that the first launch on that stream allocates nothing."""
+    gemv_workspace(torch.device(device), nbytes)
 
 
 def workspace_status(device: torch.device) -> int:
@@ -156,6 +178,14 @@ def workspace_status(device: torch.device) -> int:
         if idx == device.index:
             st |= int(ws[:4].view(torch.int32).item())
     return st
+
+
+def gemv_static_status(device: torch.device) -> int:
+    """Sticky status word of the built-in scratch that gemv_grouped_static uses on `device`."""
+    word = ctypes.c_uint(0)
+    with torch.cuda.device(device):
+        _check(lib().exl3_gemv_static_status(ctypes.byref(word)), "exl3_gemv_static_status")
+    return int(word.value)
 
 
 # --------------------------------------------------------------------------- entry points
@@ -248,6 +278,11 @@ def gemv_grouped_static(x: torch.Tensor, shards, y: torch.Tensor) -> None:
     _cuda(x, "x", torch.float16)
     _cuda(y, "y", torch.float16)
     arr = _shard_array(x, shards)
+    with torch.cuda.device(x.device):                 # the library uses the current device's scratch
+        _check_static(x, shards, y, arr)
+
+
+def _check_static(x, shards, y, arr):
     _check(lib().exl3_gemv_grouped_static(arr, len(shards), x.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1],
                                           y.stride(0), _stream(x)), "exl3_gemv_grouped_static")
 

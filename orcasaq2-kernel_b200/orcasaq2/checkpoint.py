@@ -29,6 +29,8 @@ from typing import Iterable, Iterator
 
 import torch
 
+from .ops import PACK_LAYOUT
+
 # HF projection name -> (fused vLLM parameter name, shard id)
 STACKED = {
     "q_proj": ("qkv_proj", "q"), "k_proj": ("qkv_proj", "k"), "v_proj": ("qkv_proj", "v"),
@@ -129,7 +131,7 @@ def write_synthetic_checkpoint(path: str, *, layers: int, hidden: int, ffn: int,
     with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
         json.dump({"metadata": {"total_size": total}, "weight_map": weight_map}, f, indent=1)
     kbits = [v["bits_per_weight"] for v in storage.values() if "bits_per_weight" in v]
-    qcfg = {"quant_method": "exl3", "bits": round(sum(kbits) / max(1, len(kbits)), 3), "codebook": "3inst",
+    qcfg = {"quant_method": "exl3", "bits": round(sum(kbits) / max(1, len(kbits)), 3), "codebook": "3inst", "exl3_layout": PACK_LAYOUT,
             "head_bits": 8, "tensor_storage": storage}
     with open(os.path.join(path, "quantization_config.json"), "w") as f:
         json.dump(qcfg, f, indent=1)

@@ -23,7 +23,7 @@ from vllm.model_executor.layers.quantization.base_config import (
 )
 from vllm.model_executor.parameter import BasevLLMParameter
 
-from .ops import GEMM_MAX_ROWS as _GEMM_MAX_ROWS, exl3_K  # noqa: F401  (registers the custom ops)
+from .ops import GEMM_MAX_ROWS as _GEMM_MAX_ROWS, PACK_LAYOUT, exl3_K  # noqa: F401  (registers the custom ops)
 
 logger = init_logger(__name__)
 
@@ -95,6 +95,16 @@ class Exl3Config(QuantizationConfig):
         self.codebook = codebook
         self.head_bits = head_bits
         self.full_config = full_config
+        # The reference tree does not pin the packed format (bit order, order of the weights inside a
+        # tile, codebook); this build fixes one and marks the packs it writes.  A pack without the
+        # mark loads, but nothing guarantees that it decodes to the weights its producer meant.
+        self.layout = full_config.get("exl3_layout")
+        if self.layout != PACK_LAYOUT:
+            logger.warning(
+                "orcasaq2: quantization_config.json carries no \"exl3_layout\": \"%s\" mark (found %r). "
+                "This build decodes the trellis layout it defines itself; packs written by other "
+                "producers (exllamav3 included) are NOT known to be compatible and may decode to "
+                "wrong weights without any error.", PACK_LAYOUT, self.layout)
         storage = full_config.get("tensor_storage") or {}
         self.quantized_prefixes = {
             prefix for prefix, entry in storage.items()
@@ -238,6 +248,15 @@ class Exl3LinearMethod(LinearMethodBase):
         mcg, mul1 = layer.mcg.shards, layer.mul1.shards
         dense = layer.weight.shards
         slots = sorted(tr) or sorted(dense)               # shard order == vLLM's concat order
+        # the kernels define the default codebook at integer bitrates only; say so at load, not at the first
+        # forward (which may already be inside a CUDA-graph capture)
+        for i in sorted(tr):
+            k_i = exl3_K(tr[i])
+            if mcg.get(i) is not None or mul1.get(i) is not None or not isinstance(k_i, int) or not 1 <= k_i <= 8:
+                raise RuntimeError(
+                    f"{self.prefix}: shard {i} needs the "
+                    f"{'mcg' if mcg.get(i) is not None else 'mul1' if mul1.get(i) is not None else 'K=' + str(k_i)} "
+                    "decoder, which this build does not define (default 3INST codebook, integer K in 1..8 only)")
         known = [t.device for t in list(tr.values()) + list(dense.values()) if t.device.type == "cuda"]
         dev = known[0] if known else torch.device("cuda", torch.cuda.current_device())
 
@@ -269,6 +288,10 @@ class Exl3LinearMethod(LinearMethodBase):
                 mcg=mcg.get(i) is not None, mul1=mul1.get(i) is not None,
                 K=exl3_K(t_i), ic=su_i.numel(), oc=sv_i.numel()))
         layer.exl3_shards = shards
+        if dev.type == "cuda":
+            from . import _ext
+            with torch.cuda.device(dev):
+                _ext.ensure_gemv_workspace(dev)        # scratch exists before any capture on this stream
         got = sum(s["oc"] for s in shards)
         if got != layer.exl3_out_total:
             raise RuntimeError(f"{self.prefix}: shards give {got} outputs, layer wants "

@@ -21,6 +21,10 @@ from torch import Tensor
 
 from . import _ext
 
+# Name of the packed layout this build reads and writes (bit order, order of the weights inside a tile,
+# "3INST" codebook); synthetic checkpoints carry it in quantization_config.json as "exl3_layout".
+PACK_LAYOUT = "orcasaq2-b200-3inst-v1"
+
 GEMM_MAX_ROWS = int(os.environ.get("ORCA_EXL3_GEMM_MAX_ROWS", "144"))
 USE_TC = os.environ.get("ORCA_EXL3_TC", "1") != "0"
 TC_MAX_ROWS = int(os.environ.get("ORCA_EXL3_TC_MAX_ROWS", "1023"))

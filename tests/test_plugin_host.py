@@ -173,3 +173,47 @@ def test_int8_embedding_table_api():
     assert torch.equal(tab.weight, q.half() * s.reshape(-1, 1))
     with pytest.raises(RuntimeError, match="exllamav3"):
         apply()
+
+
+def _loaded_layer(cfgmod, K=4, flag=None, width=None):
+    """A one-shard layer with its tensors captured, ready for process_weights_after_loading."""
+    m = cfgmod.Exl3LinearMethod(cfgmod.Exl3Config.from_config({}), "l.o_proj")
+    layer = torch.nn.Module()
+    m.create_weights(layer, 128, [128], 128, 128, torch.half)
+    tr, suh, svh, _ = R.make_layer(5, 128, 128, K, 1)
+    if width is not None:
+        tr = tr[..., :width].contiguous()
+    layer.trellis.weight_loader(layer.trellis, tr, None)
+    layer.suh.weight_loader(layer.suh, suh, None)
+    layer.svh.weight_loader(layer.svh, svh, None)
+    if flag:
+        getattr(layer, flag).weight_loader(getattr(layer, flag), torch.zeros(1), None)
+    return m, layer
+
+
+@pytest.mark.parametrize("flag,width,what", [("mcg", None, "mcg"), ("mul1", None, "mul1"), (None, 56, "K=3.5")])
+def test_undefined_decoders_are_refused_at_load(cfgmod, flag, width, what):
+    """The alternative codebooks and the half bitrates are flagged per tensor in the reference
+    (orcasaq2/config.py:218, ops.py:28-34) but defined nowhere in its tree: such a shard is refused when the
+    layer is loaded, with the reason, not at the first forward."""
+    m, layer = _loaded_layer(cfgmod, 4, flag, width)
+    with pytest.raises(RuntimeError, match=what.replace(".", r"\.")):
+        m.process_weights_after_loading(layer)
+
+
+def test_pack_layout_mark(cfgmod, caplog):
+    """A pack without this build's layout mark loads, with a loud warning; the synthetic checkpoints carry it."""
+    import logging
+    from orcasaq2 import checkpoint, ops
+    records = []
+    h = logging.Handler()
+    h.emit = lambda r: records.append(r.getMessage())
+    cfgmod.logger.addHandler(h)
+    try:
+        cfgmod.Exl3Config.from_config({"bits": 4.0})
+        assert any("exl3_layout" in r and "NOT known to be compatible" in r for r in records)
+        records.clear()
+        c = cfgmod.Exl3Config.from_config({"bits": 4.0, "exl3_layout": ops.PACK_LAYOUT})
+        assert not records and c.layout == ops.PACK_LAYOUT == checkpoint.PACK_LAYOUT
+    finally:
+        cfgmod.logger.removeHandler(h)

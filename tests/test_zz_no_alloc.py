@@ -50,6 +50,16 @@ def test_static_scratch_matches_regular_entry_point(ext, ic, spec, rows):
     ext.gemv_grouped_static(x2, shards, got)
     torch.cuda.synchronize()
     assert torch.equal(got, want)
+    # a first call made on a stream of its own works the same way (nothing is queued at set-up)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        got2 = torch.empty_like(want)
+        ext.gemv_grouped_static(x2, shards, got2)
+    side.synchronize()
+    assert torch.equal(got2, want)
+    # no bounded wait inside those launches ran out: the built-in array's sticky status word is clear
+    assert ext.gemv_static_status(x.device) == 0
 
 
 def test_static_scratch_rejects_oversized_request(ext):
