@@ -6,9 +6,9 @@ Workload (`config.workload`): the mixed-bitwidth decode shards of one 27B-class 
 qkv_proj (q 5120->6144 @4 bpw, k 5120->1024 @5, v 5120->1024 @6; one grouped launch),
 gate_up_proj (2 x 5120->17408 @3; one grouped launch), down_proj (17408->5120 @4) -- at batch
 `--rows` (default 1), fp16 activations ~N(0,1), uniform-random trellis words, +-1 sign vectors.
-One step = one pass over the three fused layers: three kernel launches at one or two rows (the GEMV
-rotates the activations itself), six above (an activation pre-pass before each).  Three independent
-weight sets (3 x 134 MB) are rotated so no step finds its trellis in the 126 MB L2.
+One step = one pass over the three fused layers: six kernel launches (an activation pre-pass and the
+GEMV per layer).  Three independent weight sets (3 x 134 MB) are rotated so no step finds its trellis
+in the 126 MB L2.
 
 metric  = algorithmic bytes (trellis + activations in + out) moved per second, whole job.
 value   = inputs resident in HBM: ONE CUDA graph of exactly `--steps` steps, replayed >= 100 times and
@@ -18,7 +18,8 @@ e2e     = same metric through the plugin's custom op with HOST activations: pinn
           device, three `orcasaq2::layer_gemm` calls, outputs back to pinned host, every step;
           replayed from a CUDA graph (the plugin's serving mode), the eager time is reported beside it.
 N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
-          down_proj followed by an NCCL all-reduce), strong scaling: the job's total bytes are fixed.
+          down_proj followed by this library's one-shot all-reduce over peer memory; `--allreduce nccl`
+          uses the library collective instead), strong scaling: the job's total bytes are fixed.
           The line then also carries `decoder_27b_tp`: the 27B decoder of bench_model.py at batch 64 with
           an 8192-token cache on the same ranks (BASELINE config 5).
 roofline      = the dominant kernel (gate_up grouped GEMV) alone, graph-replayed; `roofline_by_k` (N = 1):
@@ -260,6 +261,17 @@ def run_gpu(args):
     rows, K_steps = args.rows, max(1, args.steps)
     warm = max(3, args.warmup)
     sets = build_sets(torch, dev, rank, world)
+    # row-parallel partial sums: this library's one-shot all-reduce over peer memory (--allreduce nccl: the library collective)
+    ar = None
+    if world > 1 and args.allreduce == "oneshot":
+        from orcasaq2 import comm
+        ar = comm.OneShotAllReduce(max_values=64 * 5120, device=dev)
+
+    def all_reduce(t):
+        if ar is not None:
+            ar.all_reduce(t)
+        else:
+            dist.all_reduce(t)
 
     def make_io(r):
         xs_ = {ic: torch.randn((r, ic), generator=torch.Generator().manual_seed(5)).half().to(dev)
@@ -275,7 +287,7 @@ def run_gpu(args):
                     continue
                 _ext.gemv_grouped(xs_[ic_r], shards, y)
                 if world > 1 and name == "down_proj":
-                    dist.all_reduce(y)                      # row-parallel partial sums
+                    all_reduce(y)                           # row-parallel partial sums
         return step
 
     def bytes_per_step(r):
@@ -322,7 +334,7 @@ def run_gpu(args):
     ms_step = spread["median"]
     full_bytes = bytes_per_step(rows)
     value = full_bytes / (ms_step * 1e-3) / 1e9
-    launches_per_layer = 1 if rows <= 2 else 2       # one or two rows: the GEMV rotates the activations itself
+    launches_per_layer = 2                            # the activation pre-pass and the GEMV
 
     if args.skip_extras:
         if rank == 0:
@@ -364,7 +376,7 @@ def run_gpu(args):
             xd = hx[ic_r].to(dev, non_blocking=True)
             y = torch.ops.orcasaq2.layer_gemm(xd, *lay_args[i % N_SETS][li])
             if world > 1 and name == "down_proj":
-                dist.all_reduce(y)
+                all_reduce(y)
             hy[li].copy_(y, non_blocking=True)
         torch.cuda.synchronize()
 
@@ -389,7 +401,7 @@ def run_gpu(args):
                 dx[ic_r].copy_(hx[ic_r], non_blocking=True)
                 y = torch.ops.orcasaq2.layer_gemm(dx[ic_r], *lay_args[si][li])
                 if world > 1 and name == "down_proj":
-                    dist.all_reduce(y)
+                    all_reduce(y)
                 hy[li].copy_(y, non_blocking=True)
 
         side = torch.cuda.Stream()
@@ -458,6 +470,21 @@ def run_gpu(args):
             "traffic": NCU_TRAFFIC_BYTES.get((rows, world))}
     by_k = roofline_by_k(torch, dist, _ext, dev, peak) if world == 1 and rank == 0 and not args.no_graph else None
     cpu = cpu_baseline(rows) if world == 1 and rank == 0 else None
+    ar_block = None
+    if world > 1 and not args.no_graph:
+        # the exchange by itself: [rows, 5120] fp16, 20 calls per graph replay, this library's kernel and NCCL's
+        ar_block = {"values": rows * 5120, "unit": "us per call", "used_in_step": args.allreduce}
+        t_ar = torch.randn((rows, 5120), device=dev).half()
+        for nm, fn in (("oneshot", (lambda: ar.all_reduce(t_ar)) if ar is not None else None), ("nccl", lambda: dist.all_reduce(t_ar))):
+            if fn is None:
+                continue
+            g = _graph_of(torch, lambda i: fn(), 20, 3)
+            tl, _ = time_replays(torch, dist, g, world, dev, 20.0, 20)
+            ar_block[nm] = round(tl[len(tl) // 2] / 20 * 1e3, 2)
+            del g
+        if ar is not None:
+            ar_block["status_word"] = ar.status()
+    used_graph = graph is not None
     tp_model = None
     if world > 1 and not args.no_decoder:
         # BASELINE config 5 on the same ranks and kernels: the 27B decoder under tensor parallelism
@@ -465,7 +492,7 @@ def run_gpu(args):
         torch.cuda.empty_cache()
         import bench_model
         try:
-            tp_model = bench_model.run(bench_model.default_args(batch=64, ctx=8192, steps=10, warmup=2))
+            tp_model = bench_model.run(bench_model.default_args(batch=64, ctx=8192, steps=10, warmup=2, allreduce=args.allreduce))
         except Exception as e:                                          # noqa: BLE001
             tp_model = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
     if rank != 0:
@@ -489,8 +516,9 @@ def run_gpu(args):
         "e2e": {"value": round(full_bytes / e2e_s / 1e9, 1), "unit": "GB/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": round(e2e_s * 1e3, 5), "mode": e2e_mode,
                 "eager_ms_per_step": round(e2e_eager_s * 1e3, 5)},
-        # kernels of this library per fused layer: the GEMV, plus the activation pre-pass above two rows
-        "gpu_launches": K_steps * spread["replays"] * len(LAYERS) * launches_per_layer, "cuda_graph": graph is not None,
+        # kernels of this library per step: per fused layer the activation pre-pass and the GEMV, plus the all-reduce at N > 1
+        "gpu_launches": K_steps * spread["replays"] * (len(LAYERS) * launches_per_layer + (1 if ar is not None else 0)),
+        "cuda_graph": used_graph,
         "clocks": clocks, "roofline": roof,
     }
     if by_k is not None:
@@ -504,6 +532,8 @@ def run_gpu(args):
             b1 = line["decoder_27b"].get("bs1", {}).get("value")
             if b1 and cpu["decoder_27b_tok_s"]:
                 line["decoder_27b"]["gpu_over_cpu_bs1"] = round(b1 / cpu["decoder_27b_tok_s"], 1)
+    if ar_block is not None:
+        line["allreduce"] = ar_block
     if tp_model is not None:
         line["decoder_27b_tp"] = tp_model
     print(json.dumps(line), flush=True)
@@ -690,6 +720,9 @@ def main():
     ap.add_argument("--only", default=None, choices=[l[0] for l in LAYERS],
                     help="run just this fused layer each step (small case for profiling)")
     ap.add_argument("--no-graph", action="store_true", help="launch from Python instead of replaying a CUDA graph")
+    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
+                    help="N > 1: how the row-parallel partial sums are added (this library's one-shot kernel over peer "
+                         "memory, or the NCCL collective)")
     ap.add_argument("--no-decoder", action="store_true",
                     help="skip the 27B decoder runs reported beside the GEMV figure (N = 1 only)")
     ap.add_argument("--skip-extras", action="store_true",

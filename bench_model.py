@@ -12,7 +12,8 @@ involved); the KV cache is filled with random values for `ctx` tokens.  One step
 token per sequence: RMSNorm, fused qkv GEMV, rotary, attention over the cache (exl3_decode_attn; --attn sdpa for torch's), o_proj,
 RMSNorm, fused gate_up GEMV, SiLU*up, down_proj, final norm, int8 head, argmax.  The whole step is
 captured in a CUDA graph.  Under tensor parallelism qkv / gate_up are column-sliced, o_proj /
-down_proj row-sliced with an NCCL all-reduce after each, the head is vocabulary-sliced.
+down_proj row-sliced with an all-reduce after each (this library's one-shot kernel over peer memory;
+--allreduce nccl for the library collective), the head is vocabulary-sliced.
 
 Prints one JSON line: tokens/s, ms per step, bytes moved per step (packed weights + KV cache) and
 their share of the measured HBM bandwidth.
@@ -112,18 +113,21 @@ def build(rank, world, batch, ctx, dev, layers, dims=None):
 
 def default_args(**over):
     """The command-line defaults as a namespace (for callers that run the benchmark in-process)."""
-    ns = argparse.Namespace(batch=1, ctx=4096, steps=20, warmup=3, layers=LAYERS, no_graph=False, attn="own", tc_from=9)
+    ns = argparse.Namespace(batch=1, ctx=4096, steps=20, warmup=3, layers=LAYERS, no_graph=False, attn="own", tc_from=9,
+                            allreduce="oneshot")
     for k, v in over.items():
         setattr(ns, k, v)
     return ns
 
 
-def make_step(model, table, scales, ids, B, ctx, qh, kvh, world, attn="own", dims=None):
+def make_step(model, table, scales, ids, B, ctx, qh, kvh, world, attn="own", dims=None, all_reduce=None):
     """One decode step over `model` as a closure: returns (argmax token per sequence, logits of this rank's
     vocabulary slice).  The new token's key and value go to cache position `ctx`."""
     from orcasaq2 import _ext
     HD = (dims or DIMS_27B)["hd"]
     dev = table.device
+    if all_reduce is None:
+        all_reduce = dist.all_reduce
     pos = torch.arange(HD // 2, device=dev).float()
     ang = ctx / (10000.0 ** (pos / (HD // 2)))
     cos, sin = torch.cos(ang).half(), torch.sin(ang).half()
@@ -135,7 +139,7 @@ def make_step(model, table, scales, ids, B, ctx, qh, kvh, world, attn="own", dim
     def step():
         h = _ext.int8_embed(table, scales, ids)                           # [B, HIDDEN] (rank-local rows)
         if world > 1:
-            dist.all_reduce(h)                                            # vocabulary-parallel embedding
+            all_reduce(h)                                                 # vocabulary-parallel embedding
         for qkv, o, gu, down, kc, vc in model:
             y = qkv(h, in_mode=1)
             if attn == "sdpa":
@@ -151,14 +155,14 @@ def make_step(model, table, scales, ids, B, ctx, qh, kvh, world, attn="own", dim
                 att = _ext.decode_attn(q, kc, vc, ctx + 1)                # [B, qh, HD], split-KV kernel of this library
             if world > 1:
                 a = o(att.reshape(B, qh * HD))
-                dist.all_reduce(a)
+                all_reduce(a)
                 h = h + a
             else:
                 h = o(att.reshape(B, qh * HD), residual=h)           # residual add in the epilogue
             g = gu(h, in_mode=1)
             if world > 1:
                 d = down(g, in_mode=2)
-                dist.all_reduce(d)
+                all_reduce(d)
                 h = h + d
             else:
                 h = down(g, in_mode=2, residual=h)
@@ -184,7 +188,12 @@ def run(args):
     B, ctx = args.batch, args.ctx
     model, table, scales, wbytes, kvbytes, qh, kvh = build(rank, world, B, ctx, dev, args.layers)
     ids = torch.randint(0, table.shape[0], (B,), device=dev)
-    step = make_step(model, table, scales, ids, B, ctx, qh, kvh, world, args.attn)
+    ar = None
+    if world > 1 and getattr(args, "allreduce", "oneshot") == "oneshot":
+        from orcasaq2 import comm
+        ar = comm.OneShotAllReduce(max_values=max(64, B) * HIDDEN, device=dev)
+    step = make_step(model, table, scales, ids, B, ctx, qh, kvh, world, args.attn,
+                     all_reduce=None if ar is None else ar.all_reduce)
 
     for _ in range(max(2, args.warmup)):
         step()
@@ -229,7 +238,8 @@ def run(args):
     return {
         "metric": "27B EXL3 decode tokens/s", "value": round(B / (ms * 1e-3), 2), "unit": "tok/s",
         "ms_per_step": round(ms, 4), "n_gpus": world, "batch": B, "ctx": ctx, "layers": args.layers,
-        "cuda_graph": graph is not None, "status_word": _ext.workspace_status(dev),
+        "cuda_graph": graph is not None, "status_word": _ext.workspace_status(dev) | (ar.status() if ar is not None else 0),
+        "allreduce": "one-shot kernel over peer memory" if ar is not None else ("nccl" if world > 1 else None),
         "per_gpu_bytes_per_step": {"packed_weights": wbytes, "kv_cache": kvbytes},
         "per_gpu_hbm_gbs": round(per_gpu, 1), "frac_of_measured_hbm": round(per_gpu / peak, 4),
         "data": "synthetic (random-init weights, random KV cache)", "attention": "exl3_decode_attn" if args.attn == "own" else "torch SDPA (library)",
@@ -247,6 +257,8 @@ def main():
     ap.add_argument("--attn", choices=["own", "sdpa"], default="own",
                     help="decode attention: this library's kernel, or torch's scaled_dot_product_attention")
     ap.add_argument("--tc-from", type=int, default=9, help="smallest batch that takes the tcgen05 path (9..17)")
+    ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
+                    help="tensor parallel: this library's one-shot all-reduce over peer memory, or the NCCL collective")
     args = ap.parse_args()
     line = run(args)
     if line is not None:

@@ -284,6 +284,36 @@ int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, in
                      void *k_cache, void *v_cache, int batch, int q_heads, int kv_heads, int head_dim,
                      int pos, long long kv_batch_stride, long long kv_head_stride, void *stream);
 
+/*
+ * One-shot all-reduce (sum) of fp16 partial results over peer memory, for the outputs of row-parallel layers
+ * under tensor parallelism: one launch, no library collective.  The reference refuses tensor parallelism
+ * (orcasaq2/config.py:173-177); the engine around it would call a library all-reduce after every row-parallel
+ * projection (vllm/model_executor/layers/linear.py:1556-1559), which at decode sizes is pure latency.
+ *
+ * Every rank owns one communication buffer of exl3_allreduce_buffer_bytes(max_values) bytes that every other
+ * rank has mapped; peer_buffers[r] is rank r's buffer as THIS process addresses it (peer_buffers[rank] is the
+ * own one).  exl3_comm_alloc makes such a buffer (the one place this library allocates device memory: a
+ * zero-filled cudaMalloc block, plus its 64-byte CUDA IPC handle for the other processes of the node),
+ * exl3_comm_open maps a peer's buffer from its handle, exl3_comm_close / exl3_comm_free undo them.  All ranks
+ * must have finished allocating and mapping (a host barrier) before the first call.
+ *
+ * exl3_allreduce_oneshot: out[i] = sum over ranks of in[i], i < n_values (a multiple of 8; in, out 16-byte
+ * aligned; out == in allowed), added in fp32 in rank order, so all ranks get bitwise the same result.  Every
+ * rank must make the same sequence of calls with the same n_values on buffers of the same size.  Peers are
+ * reached with plain loads and stores only.  A wait inside the kernel gives up after spin_limit polls (0 = a
+ * default of seconds): the kernel then sets the buffer's sticky status word (exl3_comm_status, which waits for
+ * the device), leaves that part of out untouched and returns.
+ */
+#define EXL3_AR_MAX_RANKS 8
+size_t exl3_allreduce_buffer_bytes(size_t max_values);
+int exl3_allreduce_oneshot(void *const *peer_buffers, int rank, int world, size_t buffer_bytes, const void *in,
+                           void *out, long long n_values, int spin_limit, void *stream);
+int exl3_comm_alloc(size_t bytes, void **ptr_out, void *ipc_handle_out64);
+int exl3_comm_open(const void *ipc_handle64, void **ptr_out);
+int exl3_comm_close(void *ptr);
+int exl3_comm_free(void *ptr);
+int exl3_comm_status(const void *own_buffer, unsigned *status_out);
+
 #ifdef __cplusplus
 }
 #endif

@@ -36,7 +36,7 @@ constexpr int kThreads = kWarps * 32;
 __host__ __device__ constexpr int ring_depth(int K) { return K <= 4 ? 4 : 3; }
 constexpr int kTargetCtas = 296;       // two resident CTAs on each of 148 SMs
 constexpr int kMaxSplitK = 16;         // more slices cost more in the final reduction than they gain
-constexpr int kXfMaxBytes = 48 * 1024; // activation fragments
+constexpr int kCtaSmemBytes = 112 * 1024;   // dynamic shared memory of one CTA (two CTAs per SM)
 constexpr int kBarBytes = 1024;
 constexpr int kSpinLimit = 1 << 22;
 constexpr unsigned kStatusTimeout = 1u;
@@ -126,6 +126,27 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t *a, uint3
         "{%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
+    unsigned v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Sum of one output's partial sums over the slices of its unit in slice order (bitwise reproducible whichever
+// CTA does it), the loads issued four at a time; slice `self` is taken from `mine` instead of memory.
+__device__ __forceinline__ float sum_slices(const float *part, int splitk, int rows, int n, int ocl, int self, float mine) {
+    float v = 0.f;
+    for (int k2 = 0; k2 < splitk; k2 += 4) {
+        float p[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            p[j] = (k2 + j < splitk && k2 + j != self) ? __ldcg(part + ((size_t)(k2 + j) * rows + n) * 128 + ocl) : 0.f;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+            if (k2 + j < splitk) v += k2 + j == self ? mine : p[j];
+    }
+    return v;
 }
 
 // The 32 codewords of one chunk (four tiles' worth of one lane) times the activations: acc[t][h][a] += ...
@@ -293,6 +314,11 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     const int unit = S.unit_begin + ob;
     const int ocl = tid & 127;
     float *part = P.partial + S.partial_off + (size_t)ob * S.splitk * P.rows * 128;
+    // Split units: if every other slice of the unit has already arrived, this CTA is the last one.  It then
+    // need not publish its own sums and take a ticket: it adds the others' sums to its own, in slice order.
+    const bool split = S.splitk > 1;
+    __shared__ unsigned s_last, s_fast;
+    if (split && tid == 0) s_fast = ld_acquire_u32(P.tickets + unit) == (unsigned)(S.splitk - 1);
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         if (t) __syncthreads();                                      // the previous pass has been summed
@@ -315,12 +341,14 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             float v = 0.f;
 #pragma unroll
             for (int r = 0; r < kWarps; ++r) v += red[((size_t)(r * 8 + nl)) * 128 + ocl];
-            if (S.splitk == 1) fin[n * 128 + ocl] = v;
+            if (!split) fin[n * 128 + ocl] = v;
+            else if (s_fast) fin[n * 128 + ocl] = sum_slices(part, S.splitk, P.rows, n, ocl, ks, v);
             else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
         }
     }
-    if (S.splitk > 1) {
-        __shared__ unsigned s_last;
+    if (split && s_fast) {
+        if (tid == 0) P.tickets[unit] = 0u;     // ready for the next launch
+    } else if (split) {
         __threadfence();
         __syncthreads();
         if (tid == 0) {
@@ -331,20 +359,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
         __syncthreads();
         if (!s_last) return;
         __threadfence();
-        for (int n = tid >> 7; n < P.rows; n += 2) {
-            // fixed summation order (slice 0, 1, 2, ...) with the loads issued four at a time
-            float v = 0.f;
-            int k2 = 0;
-            for (; k2 + 4 <= S.splitk; k2 += 4) {
-                const float p0 = __ldcg(part + ((size_t)(k2 + 0) * P.rows + n) * 128 + ocl);
-                const float p1 = __ldcg(part + ((size_t)(k2 + 1) * P.rows + n) * 128 + ocl);
-                const float p2 = __ldcg(part + ((size_t)(k2 + 2) * P.rows + n) * 128 + ocl);
-                const float p3 = __ldcg(part + ((size_t)(k2 + 3) * P.rows + n) * 128 + ocl);
-                v = (((v + p0) + p1) + p2) + p3;
-            }
-            for (; k2 < S.splitk; ++k2) v += __ldcg(part + ((size_t)k2 * P.rows + n) * 128 + ocl);
-            fin[n * 128 + ocl] = v;
-        }
+        for (int n = tid >> 7; n < P.rows; n += 2) fin[n * 128 + ocl] = sum_slices(part, S.splitk, P.rows, n, ocl, -1, 0.f);
     }
     __syncthreads();
 
@@ -480,7 +495,6 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     pl.nt = rows > 8 ? 2 : 1;
     pl.nb = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
     const int frag_bytes_per_block = 8 * pl.nt * pl.nb * 64;
-    const int max_slice = kXfMaxBytes / frag_bytes_per_block;
     double total_bytes = 0;
     for (int i = 0; i < n; ++i) {
         if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
@@ -522,10 +536,13 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         pl.xf_off[i] = pl.xf_words;
         pl.xf_words += (long long)pl.kblocks * frag_bytes_per_block / 4;
     }
-    pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
-    pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
     const int red = (kWarps * 8 + pl.nt * 8) * 128 * 4;           // staging of one pass + the summed rows
     pl.region_bytes = ring > red ? ring : red;
+    // the activation fragments of as many 128-blocks at once as the rest of the CTA's shared memory holds
+    const int max_slice = (kCtaSmemBytes - kBarBytes - pl.region_bytes) / frag_bytes_per_block;
+    if (max_slice < 1) return EXL3_E_SHAPE;
+    pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
+    pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
     return EXL3_OK;
 }
 

@@ -99,3 +99,43 @@ def test_missing_rank_is_a_host_side_timeout():
     msg = q.get(timeout=120)
     p.join(timeout=30)
     assert msg.startswith("timeout:")
+
+
+def _oneshot_worker(rank, world, port, q):
+    """The exchange of the one-shot all-reduce, played with gloo: every rank publishes its partial (all_gather
+    stands in for the peers' mapped buffers), then adds ALL partials itself in rank order in fp32."""
+    sys.path.insert(0, os.path.join(ROOT, "orcasaq2-kernel_b200"))
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    from orcasaq2 import comm
+    ok = True
+    for it, n in enumerate([5120, 64 * 5120, 8]):
+        part = (torch.randn((n,), generator=torch.Generator().manual_seed(7 * it + rank)) * 80).half()
+        slots = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(slots, part)
+        mine = comm.allreduce_reference(slots)
+        # every rank ends with bitwise the same tensor ...
+        everyone = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(everyone, mine)
+        ok = ok and all(torch.equal(e, mine) for e in everyone)
+        # ... which is the library all-reduce's sum up to one fp16 rounding of a differently ordered sum
+        lib = part.clone().float()
+        dist.all_reduce(lib)
+        ok = ok and bool(((mine.float() - lib).abs() <= lib.abs() * 2 ** -10 + 1e-3).all())
+    if rank == 0:
+        q.put(ok)
+    dist.destroy_process_group()
+
+
+def test_one_shot_all_reduce_algebra_two_ranks():
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29300 + os.getpid() % 200
+    procs = [ctx.Process(target=_oneshot_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    ok = q.get(timeout=240)
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert ok
