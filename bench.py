@@ -302,6 +302,8 @@ def run_gpu(args):
     for i in range(warm):
         step(i)
     torch.cuda.synchronize()
+    if ar is not None and ar.status():
+        raise SystemExit("bench.py: the one-shot all-reduce timed out waiting for a peer during warm-up")
     sampler = ClockSampler(local)
     if args.no_graph:
         graph = None

@@ -60,7 +60,8 @@ class Linear:
     def __call__(self, x, in_mode=0, residual=None, out=None):
         """in_mode: 0 plain, 1 RMSNorm(x), 2 silu(x[:, :ic]) * x[:, ic:]; `residual` is added to the
         result (fused into the GEMV for <= 16 rows, into the pre- and post-pass of the tcgen05 path above)."""
-        if self.rows < TC_FROM_ROWS:
+        # fused layers stay on the grouped GEMV up to 16 rows (measured faster there), single shards switch earlier
+        if self.rows < TC_FROM_ROWS or (len(self.shards) > 1 and self.rows <= self.ext.GEMV_MAX_ROWS):
             out = self.out if out is None else out
             self.ext.gemv_grouped(x, self.shards, out, in_mode=in_mode, residual=residual)
             return out

@@ -165,6 +165,22 @@ int exl3_gemm_tc_grouped(const exl3_shard *shards, int nshards, const void *x, v
                          int ldy, void *scratch, size_t scratch_bytes, int x_is_bf16,
                          const exl3_gemv_fusion *fusion, void *stream);
 unsigned exl3_gemm_tc_status(void);
+int exl3_gemm_tc_status_reset(void);
+
+/*
+ * Self-tests of the bounded waits (no counterpart in the reference): every wait on an mbarrier inside these
+ * kernels gives up after a limit, sets a sticky status word and lets the kernel return.  These entry points
+ * launch ONE warp that waits, through the kernels' own wait helpers, on a barrier nothing will ever complete,
+ * with a short limit, so that the give-up path can be exercised without any fault: afterwards the status word
+ * is non-zero and the device is as usable as before.
+ *   exl3_gemv_selftest_wait     the GEMV's poll-counted wait; the word set is the first word of `workspace`
+ *                               (any 4-byte-aligned device word, e.g. a scratch of its own); 1 <= polls <= 2^20
+ *   exl3_gemm_tc_selftest_wait  the timer-bounded waits of exl3_gemm_tc (which 0: shared-memory-operand kernel,
+ *                               1: tensor-memory kernel); limit in microseconds; sets the word exl3_gemm_tc_status
+ *                               reports (clear it with exl3_gemm_tc_status_reset)
+ */
+int exl3_gemv_selftest_wait(void *workspace, int polls, void *stream);
+int exl3_gemm_tc_selftest_wait(int which, unsigned limit_us, void *stream);
 
 /*
  * exl3_gemv_grouped without a caller-supplied workspace.  This entry point has no counterpart
@@ -301,7 +317,7 @@ int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, in
  * aligned; out == in allowed), added in fp32 in rank order, so all ranks get bitwise the same result.  Every
  * rank must make the same sequence of calls with the same n_values on buffers of the same size.  Peers are
  * reached with plain loads and stores only.  A wait inside the kernel gives up after spin_limit polls (0 = a
- * default of seconds): the kernel then sets the buffer's sticky status word (exl3_comm_status, which waits for
+ * default worth a fraction of a second): the kernel then sets the buffer's sticky status word (exl3_comm_status, which waits for
  * the device), leaves that part of out untouched and returns.
  */
 #define EXL3_AR_MAX_RANKS 8

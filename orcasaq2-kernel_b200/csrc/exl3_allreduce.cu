@@ -244,7 +244,7 @@ extern "C" int exl3_allreduce_oneshot(void *const *peer_buffers, int rank, int w
     P.capacity = cap;
     P.rank = rank;
     P.world = world;
-    P.spin_limit = spin_limit > 0 ? spin_limit : (1 << 24);
+    P.spin_limit = spin_limit > 0 ? spin_limit : (1 << 19);       // a fraction of a second of polling
     const cudaError_t e = launch_pdl(n_values <= kArLLMaxValues ? allreduce_ll_kernel : allreduce_oneshot_kernel,
                                      dim3((unsigned)chunks), dim3(kArThreads), 0, static_cast<cudaStream_t>(stream), P);
     if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }

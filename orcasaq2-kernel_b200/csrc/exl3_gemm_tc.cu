@@ -74,7 +74,8 @@ __device__ __forceinline__ unsigned long long now_ns() {
 // status word and returns false (the caller stops its loop, the kernel still exits cleanly).
 // `sleep_ns` > 0 backs off between polls: a spinning warp competes with the decode warps for issue
 // slots (measured: more than half of the kernel's instructions were polls before this).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned sleep_ns = 0) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned sleep_ns = 0,
+                                          unsigned long long limit_ns = kWaitNs) {
     unsigned long long t0 = 0;
     for (int it = 0; it < kSpin; ++it) {
         uint32_t ok;
@@ -86,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
         if ((it & 255) == 255) {
             const unsigned long long t = now_ns();
             if (t0 == 0) t0 = t;
-            else if (t - t0 > kWaitNs) break;
+            else if (t - t0 > limit_ns) break;
         }
     }
     atomicOr(&g_tc_status, 1u);
@@ -172,14 +173,8 @@ struct SmemView {
 };
 
 // Per-warp cycle counts of the decode loop's phases, compiled in only for the timing study.
-#ifdef EXL3_TC_TRACE
-__device__ unsigned long long g_tc_trace[4096][32][6];
-#define TC_CLK(v) const long long v = clock64()
-#define TC_ACC(i, a, b) tc_acc[i] += (unsigned long long)((b) - (a))
-#else
 #define TC_CLK(v) do { } while (0)
 #define TC_ACC(i, a, b) do { } while (0)
-#endif
 
 template <int K, int G>
 __global__ void __launch_bounds__(threads_for(G), G == 1 ? 2 : 1)
@@ -299,10 +294,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
         const DecodeConsts dc(P.one);
         const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
         bool ok = true;
-#ifdef EXL3_TC_TRACE
-        unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
-        const long long tc_begin = clock64();
-#endif
         Cursor rc(grp, kStagesRaw), ac(grp, nStagesA);
         for (int s = grp; s < nsteps && ok; s += G, rc.advance(G), ac.advance(G)) {
             const int rs = rc.idx, as = ac.idx;
@@ -356,22 +347,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
             TC_CLK(c4);
             TC_ACC(3, c3, c4);
         }
-#ifdef EXL3_TC_TRACE
-        const long long tc_loop_end = clock64();
-#endif
 
         // ---------------- epilogue: TMEM -> fp16 -> y[token][oc]
         ok = mbar_wait(s32(&S.acc_full), 0, 200) && ok;
-#ifdef EXL3_TC_TRACE
-        if (lane == 0 && blockIdx.y == 0) {
-            const int cta = blockIdx.x + gridDim.x * blockIdx.z;
-            if (cta < 4096) {
-                for (int i = 0; i < 4; ++i) g_tc_trace[cta][warp][i] = tc_acc[i];
-                g_tc_trace[cta][warp][4] = (unsigned long long)(tc_loop_end - tc_begin);
-                g_tc_trace[cta][warp][5] = (unsigned long long)(clock64() - tc_loop_end);
-            }
-        }
-#endif
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
         const int oc_row = ob * kBM + 32 * quad + lane;
@@ -678,6 +656,32 @@ extern "C" unsigned exl3_gemm_tc_status(void) {
     unsigned v = 0;
     if (cudaMemcpyFromSymbol(&v, exl3::tc::g_tc_status, sizeof(v)) != cudaSuccess) { cudaGetLastError(); return ~0u; }
     return v;
+}
+extern "C" int exl3_gemm_tc_status_reset(void) {
+    const unsigned v = 0;
+    if (cudaMemcpyToSymbol(exl3::tc::g_tc_status, &v, sizeof(v)) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    return EXL3_OK;
+}
+
+// Self-test of the bounded waits: one warp waits, with a limit of `limit_us` microseconds, on a barrier that
+// nothing will ever complete, through the very helper the kernels use (which 0: the shared-memory-operand
+// kernel's, 1: the tensor-memory kernel's).  The wait runs out, the sticky status word is set, the kernel returns.
+namespace exl3 { namespace tc {
+__global__ void wait_selftest_kernel(int which, unsigned long long limit_ns) {
+    __shared__ __align__(8) unsigned long long bar;
+    if (threadIdx.x == 0) {
+        mbar_init(s32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (which == 0) mbar_wait(s32(&bar), 0, 32, limit_ns);
+    else t5::mbar_wait(s32(&bar), 0, &g_tc_status, 32, limit_ns);
+}
+}}  // namespace exl3::tc
+extern "C" int exl3_gemm_tc_selftest_wait(int which, unsigned limit_us, void *stream) {
+    if (which < 0 || which > 1 || limit_us == 0 || limit_us > 1000000u) return EXL3_E_SHAPE;
+    exl3::tc::wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(which, (unsigned long long)limit_us * 1000ull);
+    return exl3::launch_status();
 }
 
 namespace exl3 { namespace tc {

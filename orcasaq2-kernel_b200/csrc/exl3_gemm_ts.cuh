@@ -187,10 +187,6 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
             const uint32_t a_off = warp == 1 ? 0u : 8u;
             bool ok = true;
             Cursor bc(0, P.bufs);
-#ifdef EXL3_TC_TRACE
-            unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
-            const long long tc_begin = clock64();
-#endif
             for (int s = 0; s < nper && ok; ++s, bc.advance(1)) {
                 TC_CLK(m0);
                 ok = mbar_wait(s32(&S.full[bc.idx]), bc.phase, status, 0);
@@ -210,15 +206,6 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
                 TC_ACC(2, m1, m3);
             }
             umma_commit(s32(&S.acc_full));
-#ifdef EXL3_TC_TRACE
-            if (warp == 1) {
-                const int cta = bx + ((P.oc + kOcCta - 1) / kOcCta) * by;
-                if (cta < 4096) {
-                    for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][1][i] = tc_acc[i];
-                    tc::g_tc_trace[cta][1][4] = (unsigned long long)(clock64() - tc_begin);
-                }
-            }
-#endif
         }
     } else {
         // ---------------- decode warps
@@ -230,10 +217,6 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
         const uint32_t lane_base = (uint32_t)(32 * quad) << 16;
         bool ok = true;
         Cursor rc(0, kRawDepth), ac(0, P.bufs);
-#ifdef EXL3_TC_TRACE
-        unsigned long long tc_acc[6] = {0, 0, 0, 0, 0, 0};
-        const long long tc_begin = clock64();
-#endif
         // Two rounds per iteration: the sixteen decode warps move in lock step (a round's MMAs need all of
         // them), so within one warp the barrier polls, shared-memory loads, shuffles and tensor-memory
         // stores of a single chunk are a chain of exposed latencies.  Two independent chunks halve them.
@@ -311,15 +294,6 @@ __device__ __forceinline__ void ts_body(const CUtensorMap *xmap, const Params &P
             TC_ACC(3, c3, c4);
         }
         announce();
-#ifdef EXL3_TC_TRACE
-        if (lane == 0) {
-            const int cta = bx + ((P.oc + kOcCta - 1) / kOcCta) * by;
-            if (cta < 4096) {
-                for (int i = 0; i < 4; ++i) tc::g_tc_trace[cta][warp][i] = tc_acc[i];
-                tc::g_tc_trace[cta][warp][4] = (unsigned long long)(clock64() - tc_begin);
-            }
-        }
-#endif
 
         // ---------------- epilogue: accumulators -> fp32 partial sums
         ok = mbar_wait(s32(&S.acc_full), 0, status, 200) && ok;

@@ -673,6 +673,26 @@ extern "C" int exl3_gemv(const void *x, const void *trellis, void *y, const void
     return exl3_gemv_grouped(&s, 1, x, y, rows, ic, oc, workspace, workspace_bytes, stream);
 }
 
+// Self-test of the bounded wait: one warp waits `polls` polls, through the helper the GEMV uses, on a barrier that
+// nothing will ever complete.  The wait runs out, the status word of `workspace` is set, the kernel returns.
+namespace exl3 {
+__global__ void gemv_wait_selftest_kernel(unsigned *status, int polls) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    mbar_wait(smem_u32(&bar), 0, status, polls);
+}
+}  // namespace exl3
+extern "C" int exl3_gemv_selftest_wait(void *workspace, int polls, void *stream) {
+    if (!workspace) return EXL3_E_NULL;
+    if (polls < 1 || polls > (1 << 20)) return EXL3_E_SHAPE;
+    exl3::gemv_wait_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<unsigned *>(workspace), polls);
+    return exl3::launch_status();
+}
+
 // ---------------------------------------------------------------------------------------------
 // Allocation-free variant: the scratch of exl3_gemv_grouped lives in this library's own device
 // memory instead of a caller buffer.

@@ -29,7 +29,8 @@ __device__ __forceinline__ unsigned long long now_ns() {
 // Bounded wait: polls the barrier; after kWaitNs without success it sets bit 0 of *status and
 // returns false (the caller leaves its loop, the kernel still exits cleanly).  `sleep_ns` > 0 backs
 // off between polls so that a waiting warp does not take issue slots from the working ones.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status, unsigned sleep_ns = 0) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigned *status, unsigned sleep_ns = 0,
+                                          unsigned long long limit_ns = kWaitNs) {
     unsigned long long t0 = 0;
     for (int it = 0; it < kSpin; ++it) {
         uint32_t ok;
@@ -41,7 +42,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, unsigne
         if ((it & 255) == 255) {
             const unsigned long long t = now_ns();
             if (t0 == 0) t0 = t;
-            else if (t - t0 > kWaitNs) break;
+            else if (t - t0 > limit_ns) break;
         }
     }
     atomicOr(status, 1u);

@@ -145,8 +145,10 @@ class Exl3Config(QuantizationConfig):
                 VocabParallelEmbedding,
             )
             if isinstance(layer, ParallelLMHead):
-                # an lm_head below 16 bits is an ordinary EXL3 tensor; a dense one falls back
-                return Exl3LinearMethod(self, prefix)
+                # an lm_head below 16 bits is an ordinary EXL3 tensor, a dense one falls back, and an int8 table
+                # with per-row scales (which the reference can only serve tied to the embedding) is taken too
+                from .heads import Exl3LMHeadMethod
+                return Exl3LMHeadMethod(self, prefix)
             if isinstance(layer, VocabParallelEmbedding):
                 from .heads import Exl3EmbeddingMethod
                 return Exl3EmbeddingMethod()

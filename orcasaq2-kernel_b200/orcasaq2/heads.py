@@ -10,7 +10,7 @@ import torch
 from vllm.model_executor.layers.quantization.base_config import QuantizeMethodBase
 
 from . import _ext
-from .config import Exl3ShardParam
+from .config import Exl3LinearMethod, Exl3ShardParam
 
 _SLOTS = ("qweight", "scales", "weight")
 
@@ -74,4 +74,58 @@ class Exl3EmbeddingMethod(QuantizeMethodBase):
                 x2 = x2.to(layer.exl3_embed_s.dtype)
             out = _ext.int8_head(layer.exl3_embed_q, layer.exl3_embed_s, x2.contiguous()).to(x.dtype)
             out = out.reshape(*x.shape[:-1], out.shape[-1])
+        return out + bias if bias is not None else out
+
+
+class Exl3LMHeadMethod(Exl3LinearMethod):
+    """An untied output head (`ParallelLMHead`) in any of the three storage forms a pack may use for it: an EXL3
+    trellis, a dense `weight`, or -- what the reference cannot load -- an int8 table with per-row scales.
+
+    The reference hands every `ParallelLMHead` to `Exl3LinearMethod` (orcasaq2/config.py:128-132), which registers
+    no `qweight` / `scales` (config.py:183), so `lm_head.qweight` has nowhere to go and an int8 head only works
+    tied to the embedding (heads.py:69-75).  This method registers the int8 placeholders beside the linear ones and
+    serves the int8 form with the same kernel as the tied head; the other two forms are `Exl3LinearMethod`'s."""
+
+    def create_weights(self, layer, input_size_per_partition, output_partition_sizes,
+                       input_size, output_size, params_dtype, **extra_weight_attrs):
+        super().create_weights(layer, input_size_per_partition, output_partition_sizes, input_size, output_size,
+                               params_dtype, **extra_weight_attrs)
+        for name in ("qweight", "scales"):
+            layer.register_parameter(name, Exl3ShardParam(suffix=name))
+        layer.exl3_params_dtype = params_dtype
+
+    def process_weights_after_loading(self, layer):
+        q = layer.qweight.shards.get(0)
+        s = layer.scales.shards.get(0)
+        for name in ("qweight", "scales"):
+            if hasattr(layer, name):
+                delattr(layer, name)
+        layer.exl3_embed_q = None
+        if q is None:
+            if s is not None:
+                raise RuntimeError(f"{self.prefix}: scales without qweight")
+            return super().process_weights_after_loading(layer)
+        if s is None:
+            raise RuntimeError(f"{self.prefix}: qweight without scales")
+        if layer.trellis.shards or layer.weight.shards:
+            raise RuntimeError(f"{self.prefix}: an int8 table and another form of the same head were loaded")
+        for name in ("trellis", "suh", "svh", "mcg", "mul1", "weight"):
+            if hasattr(layer, name):
+                delattr(layer, name)
+        layer.exl3_shards, layer.exl3_dense = None, None
+        dev = q.device if q.device.type == "cuda" else torch.device("cuda", torch.cuda.current_device())
+        lo, hi = Exl3EmbeddingMethod._vocab_range(layer, q)
+        layer.exl3_embed_q = torch.nn.Parameter(q[lo:hi].contiguous().to(dev), requires_grad=False)
+        layer.exl3_embed_s = torch.nn.Parameter(
+            s.reshape(-1)[lo:hi].to(dev, layer.exl3_params_dtype).reshape(-1, 1).contiguous(), requires_grad=False)
+
+    def apply(self, layer, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+        if getattr(layer, "exl3_embed_q", None) is None:
+            return super().apply(layer, x, bias)
+        rows = x.numel() // x.shape[-1]
+        x2 = x.reshape(rows, x.shape[-1])
+        if x2.dtype not in (torch.float16, torch.bfloat16):
+            x2 = x2.to(layer.exl3_embed_s.dtype)
+        out = _ext.int8_head(layer.exl3_embed_q, layer.exl3_embed_s, x2.contiguous()).to(x.dtype)
+        out = out.reshape(*x.shape[:-1], out.shape[-1])
         return out + bias if bias is not None else out

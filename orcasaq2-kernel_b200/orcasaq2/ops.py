@@ -6,7 +6,7 @@ used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, wr
 into the concatenated output.
 
 Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
-streaming of the packed trellis; from 9 rows the tensor-memory kernel below takes the shapes it serves).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
+streaming of the packed trellis; a single shard moves to the tensor-memory kernel below from 9 rows).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
 packed weights with no dense copy in memory -- up to 128 rows the decoded weights go from registers into tensor memory and are the A operand of
 tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
 weight once into a scratch buffer, dense library GEMM, rotate back.  GEMM_MAX_ROWS keeps the
@@ -28,9 +28,12 @@ PACK_LAYOUT = "orcasaq2-b200-3inst-v1"
 GEMM_MAX_ROWS = int(os.environ.get("ORCA_EXL3_GEMM_MAX_ROWS", "144"))
 USE_TC = os.environ.get("ORCA_EXL3_TC", "1") != "0"
 TC_MAX_ROWS = int(os.environ.get("ORCA_EXL3_TC_MAX_ROWS", "1023"))
-# A single shard with 9..16 rows is faster on the tensor-memory kernel than on the GEMV (measured
-# 43 us against 64 us for 5120 -> 17408 at 3 bpw).
+# 9..16 rows, measured on B200 (us per call, GEMV against the tensor-memory kernel): a single shard with many
+# input channels is faster on the tensor-memory kernel (17408 -> 5120 at 4 bpw: 40.5 / 45.0 against 40.3 / 40.6 at
+# 9 / 16 rows), a fused layer on the grouped GEMV (2 x 5120 -> 17408 at 3 bpw: 64.8 / 67.7 against 74.3 / 74.7;
+# qkv: 27.1 / 30.6 against 29.4 / 29.3).  So single shards switch at 9 rows, fused layers at 17.
 TC_MIN_ROWS_SINGLE = int(os.environ.get("ORCA_EXL3_TC_MIN_ROWS", "9"))
+TC_MIN_ROWS_GROUPED = int(os.environ.get("ORCA_EXL3_TC_MIN_ROWS_GROUPED", "17"))
 
 
 def exl3_K(trellis: Tensor):
@@ -92,9 +95,10 @@ def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Te
         return y
     n = len(trellis)
     shards = [dict(trellis=trellis[i], suh=suh[i], svh=svh[i], mcg=mcg[i], mul1=mul1[i]) for i in range(n)]
-    # 9 rows and up: one grouped launch of the tensor-memory kernel where its shapes apply (measured faster
-    # than the grouped GEMV from 9 rows on); it declines other shapes without doing anything
-    if (USE_TC and TC_MIN_ROWS_SINGLE <= rows <= TC_MAX_ROWS and n <= _ext.MAX_SHARDS
+    # from the row count measured above: one grouped launch of the tensor-memory kernel where its shapes apply; it
+    # declines other shapes without doing anything
+    tc_from = TC_MIN_ROWS_SINGLE if n == 1 else TC_MIN_ROWS_GROUPED
+    if (USE_TC and tc_from <= rows <= TC_MAX_ROWS and n <= _ext.MAX_SHARDS
             and _ext.gemm_tc_grouped(x, shards, y)):
         pass
     elif rows > _ext.GEMV_MAX_ROWS and USE_TC and rows <= TC_MAX_ROWS:

@@ -232,3 +232,53 @@ def test_vllm_layers_loaded_from_a_checkpoint_on_disk(vllm_layers, cfg, coracle,
                                   for p in parts], 1)
         assert y.dtype == torch.float16 and y.shape == ref.shape
         _close(y, ref, tol=1e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_untied_int8_lm_head_on_vllm_layer(vllm_layers, cfg, ext, coracle, dtype):
+    """An untied `ParallelLMHead` whose checkpoint carries `lm_head.qweight` / `lm_head.scales`: the reference has
+    no slot for them (orcasaq2/config.py:128-132,183); here the head loads and runs on the int8 kernel."""
+    from vllm.model_executor.layers.vocab_parallel_embedding import ParallelLMHead
+    from orcasaq2.heads import Exl3LMHeadMethod
+    qc = cfg.Exl3Config.from_config({"head_bits": 8})
+    head = ParallelLMHead(300, 128, params_dtype=dtype, quant_config=qc, prefix="lm_head")
+    assert isinstance(head.quant_method, Exl3LMHeadMethod)
+    q, s = R.make_int8_table(31, 300, 128, dtype)
+    head.qweight.weight_loader(head.qweight, q)
+    head.scales.weight_loader(head.scales, s)
+    head.quant_method.process_weights_after_loading(head)
+    assert head.exl3_embed_q.dtype == torch.int8 and head.exl3_embed_q.is_cuda and head.exl3_shards is None
+    x = torch.randn((5, 128), generator=torch.Generator().manual_seed(4)).to(dtype)
+    logits = head.quant_method.apply(head, x.cuda())
+    bits = lambda t: t.contiguous().view(torch.int16).cpu().numpy().view(np.uint16)   # noqa: E731
+    lref = coracle.int8_head(q.numpy(), bits(s), bits(x), dtype == torch.bfloat16)
+    assert logits.shape[0] == 5 and logits.dtype == dtype
+    _close(logits[:, :300], lref, tol=1e-2)
+
+
+def test_lm_head_method_other_forms_and_errors(cfg, ext, coracle):
+    """The same method still serves a trellis head (the reference's only untied form) and refuses half a table."""
+    from orcasaq2.heads import Exl3LMHeadMethod
+    m = Exl3LMHeadMethod(cfg.Exl3Config.from_config({}), "lm_head")
+    layer = torch.nn.Module()
+    m.create_weights(layer, 128, [256], 128, 256, torch.half)
+    tr, suh, svh, x = R.make_layer(77, 128, 256, 4, 3)
+    for name, t in (("trellis", tr), ("suh", suh), ("svh", svh)):
+        getattr(layer, name).weight_loader(getattr(layer, name), t)
+    m.process_weights_after_loading(layer)
+    assert layer.exl3_embed_q is None and layer.exl3_shards[0]["K"] == 4
+    y = m.apply(layer, x.cuda())
+    _close(y, coracle.layer(x.numpy(), coracle.reconstruct(tr.numpy()), suh.numpy(), svh.numpy()))
+    half = torch.nn.Module()
+    m.create_weights(half, 128, [300], 128, 300, torch.half)
+    q, s = R.make_int8_table(3, 300, 128)
+    half.scales.weight_loader(half.scales, s)
+    with pytest.raises(RuntimeError, match="scales without qweight"):
+        m.process_weights_after_loading(half)
+    both = torch.nn.Module()
+    m.create_weights(both, 128, [300], 128, 300, torch.half)
+    both.qweight.weight_loader(both.qweight, q)
+    both.scales.weight_loader(both.scales, s)
+    both.weight.weight_loader(both.weight, torch.zeros(300, 128).half())
+    with pytest.raises(RuntimeError, match="another form"):
+        m.process_weights_after_loading(both)
