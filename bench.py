@@ -22,6 +22,8 @@ N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up
           uses the library collective instead), strong scaling: the job's total bytes are fixed.
           The line then also carries `decoder_27b_tp`: the 27B decoder of bench_model.py at batch 64 with
           an 8192-token cache on the same ranks (BASELINE config 5).
+prefill       = (N = 1) BASELINE config 3 on the same GPU: TFLOPS of the tcgen05 decode-GEMM and of the reference's
+                many-row route at M = 512 / 2048 / 8192, both shapes.
 roofline      = the dominant kernel (gate_up grouped GEMV) alone, graph-replayed; `roofline_by_k` (N = 1):
                 one 5120->17408 shard at 2..6 bits per weight, 1 and 16 rows.
 
@@ -471,6 +473,7 @@ def run_gpu(args):
             "timing": "median graph replay of 6 launches over 3 rotated weight sets, CUDA events on the replay stream",
             "traffic": NCU_TRAFFIC_BYTES.get((rows, world))}
     by_k = roofline_by_k(torch, dist, _ext, dev, peak) if world == 1 and rank == 0 and not args.no_graph else None
+    prefill = prefill_block(torch, _ext, dev) if world == 1 and rank == 0 and not args.no_graph else None
     cpu = cpu_baseline(rows) if world == 1 and rank == 0 else None
     ar_block = None
     if world > 1 and not args.no_graph:
@@ -525,6 +528,8 @@ def run_gpu(args):
     }
     if by_k is not None:
         line["roofline_by_k"] = by_k
+    if prefill is not None:
+        line["prefill"] = prefill
     if cpu is not None:
         line["cpu_baseline"] = cpu
     if world == 1 and not args.no_decoder:
@@ -540,6 +545,59 @@ def run_gpu(args):
         line["decoder_27b_tp"] = tp_model
     print(json.dumps(line), flush=True)
     _leave(world)
+
+
+def prefill_block(torch, _ext, dev):
+    """BASELINE config 3: M tokens x (5120 -> 17408 at 3 bpw, 17408 -> 5120 at 4 bpw), bf16 activations: TFLOPS of the
+    in-kernel-decode tcgen05 path (exl3_gemm_tc) and of the reference's own route for many rows (rotate, rebuild
+    the weight, library GEMM, rotate back: orcasaq2/ops.py:50-59), CUDA events over 8 calls after 2 warm-ups."""
+    peaks = {"burst": 1679.6, "sustained": 1385.7}
+    try:
+        mp = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
+        peaks = {"burst": float(mp["bf16_tflops"]), "sustained": float(mp["bf16_tflops_sustained"])}
+    except Exception:                                        # noqa: BLE001
+        pass
+    out = {"unit": "TFLOP/s", "flops": "2*M*ic*oc (decode and Hadamard not counted)", "peak_bf16_tflops": peaks, "cases": []}
+
+    def timed(fn, n=8):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(n):
+            fn()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / n * 1e-3
+
+    for ic, oc, K in ((5120, 17408, 3), (17408, 5120, 4)):
+        sh = make_shard(torch, ic, oc, K, 7000 + K, dev)
+        for m in (512, 2048, 8192):
+            x = torch.randn((m, ic), generator=torch.Generator().manual_seed(m)).to(torch.bfloat16).to(dev)
+            y = torch.empty((m, oc), dtype=torch.half, device=dev)
+            t_tc = timed(lambda: _ext.gemm_tc(x, sh["trellis"], y, sh["suh"], sh["svh"]))
+
+            def route():
+                xf = x.half()
+                xh = torch.empty_like(xf)
+                _ext.had_r_128(xf, xh, sh["suh"], None, 1.0)
+                w = torch.empty((ic, oc), dtype=torch.half, device=dev)
+                _ext.reconstruct(w, sh["trellis"], K, False, False)
+                _ext.hgemm_recon(xh, w, y)
+                _ext.had_r_128(y, y, None, sh["svh"], 1.0)
+            t_rt = timed(route)
+            fl = 2.0 * m * ic * oc
+            out["cases"].append({"shape": f"{ic}->{oc} @{K}bpw", "M": m,
+                                 "tcgen05_decode_gemm_tflops": round(fl / t_tc / 1e12, 1),
+                                 "tcgen05_frac_of_burst_peak": round(fl / t_tc / 1e12 / peaks["burst"], 3),
+                                 "rotate_reconstruct_library_gemm_tflops": round(fl / t_rt / 1e12, 1),
+                                 "plugin_dispatch": "tcgen05" if m <= 1023 else "rotate + reconstruct + library GEMM"})
+            del x, y
+        del sh
+        torch.cuda.empty_cache()
+    out["status_word"] = _ext.gemm_tc_status()
+    return out
 
 
 # Decode + mma.sync rate of the 3INST codebook with no memory access at all (registers only, every SM busy),

@@ -86,11 +86,14 @@ typedef struct exl3_shard {
  * torch.cat of orcasaq2/config.py:236-243.
  *
  * workspace: device scratch of at least exl3_gemv_workspace_bytes(...) bytes, 256-byte
- * aligned, ZERO-FILLED ONCE by the caller before its first use; the kernel leaves the part
- * that must stay zero at zero on exit, so it can be reused by later calls on the same
- * stream.  Calls that share a workspace must not overlap on the device.
+ * aligned, ZERO-FILLED ONCE by the caller before its first use (its first word is a sticky
+ * status word, the rest holds the rotated activations between the two launches of a call).
+ * Calls that share a workspace must not overlap on the device.
  */
 size_t exl3_gemv_workspace_bytes(const exl3_shard *shards, int nshards, int rows, int ic);
+/* How exl3_gemv_grouped would cut this launch on the current device: CTAs of the grid, and input slices per
+ * 128-column block (= CTAs per thread-block cluster; 1 = no cluster).  For diagnosis and tests. */
+int exl3_gemv_plan(const exl3_shard *shards, int nshards, int rows, int ic, int *ctas_out, int *slices_out);
 int exl3_gemv_grouped(const exl3_shard *shards, int nshards, const void *x, void *y, int rows,
                       int ic, int ldy, void *workspace, size_t workspace_bytes, void *stream);
 
@@ -188,7 +191,7 @@ int exl3_gemm_tc_selftest_wait(int which, unsigned limit_us, void *stream);
  * runs: a serving process that has already handed every free byte to its KV-cache pool, an
  * engine whose hot path is forbidden to call the allocator (no cudaMalloc, no torch caching
  * allocator) for latency or fragmentation reasons, or a plugin loaded into a runtime that owns
- * all memory.  The split-K partial sums, arrival tickets and status word live in a fixed array
+ * all memory.  The rotated activations that pass from the first launch of a call to the second, and the status word, live in a fixed array
  * inside the library (exl3_gemv_static_capacity() bytes, currently 2 MiB, held on every GPU
  * that loads the library until the process exits); the call itself allocates nothing and calls
  * no allocating routine.
@@ -201,9 +204,9 @@ int exl3_gemm_tc_selftest_wait(int which, unsigned limit_us, void *stream);
  *   - The FIRST call on each device looks up the array's device address (once, under a lock, so
  *     host threads may race to it); make that first call with the device current and before any
  *     stream capture begins.  Nothing is cleared at that point: the loader hands the array over
- *     zero-filled, which is the state the kernels need and restore.
- *   - All calls on a device share the one array, which keeps what the last call left in it:
- *     the kernel restores the parts that must be zero before it exits, but two calls that
+ *     zero-filled, which is the state the status word needs.
+ *   - All calls on a device share the one array, which keeps what the last call left in it
+ *     (every call overwrites what it reads; only the status word is sticky): two calls that
  *     overlap on the GPU (different streams without ordering, or two host threads launching
  *     without ordering between their streams) race on it.  Serialise them.
  *   - exl3_gemv_static_status(&word) copies the sticky status word of the current device's array

@@ -1,6 +1,7 @@
 // Fused trellis-decode GEMV for 1..16 rows, grouped over the shards of a fused layer:
 //     y[:, out_col : out_col+oc] = H128( H128(x * suh) . W(trellis) ) * svh
-// in one launch, with no intermediate tensor in global memory except split-K partial sums.
+// in two launches (activation pre-pass, GEMV), with no intermediate tensor in global memory except the rotated
+// activations.
 //
 // Work unit: one 128-wide block of output channels (the width of the output Hadamard) times one
 // slice of the input channels.  A CTA of eight warps owns one unit:
@@ -13,9 +14,9 @@
 //             the raw codewords to mma.m16n8k16: a codeword's two fp16 halves occupy two
 //             consecutive K slots that see the same activation, so their sum -- the weight --
 //             is formed inside the fp32 accumulator and never rounded to fp16.
-//   epilogue  warps are reduced through shared memory, slices through a global scratch with an
-//             arrival ticket; the last CTA of a unit sums the partials in slice order (bitwise
-//             reproducible), applies H128 and svh and writes fp16.
+//   epilogue  warps are reduced through shared memory; the slices of a unit are the CTAs of one thread-block
+//             cluster and are reduced through distributed shared memory into the cluster's first CTA, which adds
+//             them in slice order (bitwise reproducible), applies H128 and svh and writes fp16.
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -35,24 +36,21 @@ constexpr int kThreads = kWarps * 32;
 // B200, deeper rings LOSE bandwidth again (1 KB pieces: 7.2 TB/s at depth 4, 3.0 TB/s at depth 8).
 __host__ __device__ constexpr int ring_depth(int K) { return K <= 4 ? 4 : 3; }
 constexpr int kTargetCtas = 296;       // two resident CTAs on each of 148 SMs
-constexpr int kMaxSplitK = 16;         // more slices cost more in the final reduction than they gain
+constexpr int kMaxSplitK = 8;          // slices of a unit = CTAs of one cluster (portable cluster size)
 constexpr int kCtaSmemBytes = 112 * 1024;   // dynamic shared memory of one CTA (two CTAs per SM)
 constexpr int kBarBytes = 1024;
 constexpr int kSpinLimit = 1 << 22;
 constexpr unsigned kStatusTimeout = 1u;
 
-// Workspace layout: [status word, 256 B][arrival tickets, fixed capacity][split-K partial sums].
-// The ticket area has a FIXED size so that the partial sums of one launch can never land on the
-// tickets of a later launch with a different shape (tickets must stay zero between launches).
+// Workspace layout: [status word, 256 B][rotated activations of every shard].
 constexpr int kWsStatusBytes = 256;
 constexpr int kWsMaxUnits = 8192;                 // 128-column blocks per launch (oc total <= 1M)
-constexpr size_t kWsHeadBytes = kWsStatusBytes + (size_t)kWsMaxUnits * 4;
+constexpr size_t kWsHeadBytes = kWsStatusBytes;
 
 struct GemvShardDev {
     const uint32_t *trellis;
     const __half *suh;
     const __half *svh;
-    long long partial_off;  // in floats
     long long xf_off;       // in 32-bit words, into the fragment scratch
     int tiles_j;            // oc / 16
     int K;
@@ -70,9 +68,7 @@ struct GemvParams {
     float eps;
     int in_mode;              // 0 plain, 1 RMSNorm of x, 2 silu(x[:, :ic]) * x[:, ic:]
     int ldx, ld_res;
-    float *partial;
     uint32_t *xfg;          // rotated activations in B-fragment order, per shard
-    unsigned *tickets;
     unsigned *status;
     int rows, ic, ldy, kblocks;
     int nb;         // rows held per group of eight (1, 2, 4 or 8)
@@ -128,27 +124,13 @@ __device__ __forceinline__ void mma16816(float (&d)[4], const uint32_t *a, uint3
         : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ unsigned ld_acquire_u32(const unsigned *p) {
-    unsigned v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
+// all threads of all CTAs of the cluster
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Sum of one output's partial sums over the slices of its unit in slice order (bitwise reproducible whichever
-// CTA does it), the loads issued four at a time; slice `self` is taken from `mine` instead of memory.
-__device__ __forceinline__ float sum_slices(const float *part, int splitk, int rows, int n, int ocl, int self, float mine) {
-    float v = 0.f;
-    for (int k2 = 0; k2 < splitk; k2 += 4) {
-        float p[4];
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            p[j] = (k2 + j < splitk && k2 + j != self) ? __ldcg(part + ((size_t)(k2 + j) * rows + n) * 128 + ocl) : 0.f;
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            if (k2 + j < splitk) v += k2 + j == self ? mine : p[j];
-    }
-    return v;
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
 }
-
 // The 32 codewords of one chunk (four tiles' worth of one lane) times the activations: acc[t][h][a] += ...
 template <int K, int NT>
 __device__ __forceinline__ void consume_chunk(const uint32_t (&w)[K + 1], float (&acc)[NT][2][4][4], const int h,
@@ -311,14 +293,19 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     // small enough for two CTAs per SM also with sixteen rows
     float *red = reinterpret_cast<float *>(region);                  // [8 warps][8 rows][128]
     float *fin = red + kWarps * 8 * 128;                             // [NT*8][128]
-    const int unit = S.unit_begin + ob;
     const int ocl = tid & 127;
-    float *part = P.partial + S.partial_off + (size_t)ob * S.splitk * P.rows * 128;
-    // Split units: if every other slice of the unit has already arrived, this CTA is the last one.  It then
-    // need not publish its own sums and take a ticket: it adds the others' sums to its own, in slice order.
+    // Split units: the slices of a unit are the CTAs of one thread-block cluster (cluster rank = slice).  Every
+    // CTA writes its sums into the FIRST CTA's shared memory (distributed shared memory, plain remote stores),
+    // the cluster synchronises, and the first CTA adds the slices in slice order: no global scratch, no ticket,
+    // bitwise reproducible.  The first cluster barrier makes sure that the first CTA's warps have left their
+    // rings, which the slices' sums overwrite.
     const bool split = S.splitk > 1;
-    __shared__ unsigned s_last, s_fast;
-    if (split && tid == 0) s_fast = ld_acquire_u32(P.tickets + unit) == (unsigned)(S.splitk - 1);
+    float *slices = fin + NT * 8 * 128;                              // [splitk][rows][128], used in the first CTA only
+    uint32_t slices_remote = 0;
+    if (split) {
+        cluster_sync();
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(slices_remote) : "r"(smem_u32(slices)));
+    }
 #pragma unroll
     for (int t = 0; t < NT; ++t) {
         if (t) __syncthreads();                                      // the previous pass has been summed
@@ -342,24 +329,17 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
 #pragma unroll
             for (int r = 0; r < kWarps; ++r) v += red[((size_t)(r * 8 + nl)) * 128 + ocl];
             if (!split) fin[n * 128 + ocl] = v;
-            else if (s_fast) fin[n * 128 + ocl] = sum_slices(part, S.splitk, P.rows, n, ocl, ks, v);
-            else __stcg(part + ((size_t)ks * P.rows + n) * 128 + ocl, v);
+            else st_cluster_f32(slices_remote + (uint32_t)(((ks * P.rows + n) * 128 + ocl) * 4), v);
         }
     }
-    if (split && s_fast) {
-        if (tid == 0) P.tickets[unit] = 0u;     // ready for the next launch
-    } else if (split) {
-        __threadfence();
-        __syncthreads();
-        if (tid == 0) {
-            const unsigned prev = atomicAdd(P.tickets + unit, 1u);
-            s_last = (prev == (unsigned)(S.splitk - 1));
-            if (s_last) P.tickets[unit] = 0u;   // ready for the next launch
+    if (split) {
+        cluster_sync();                                              // every slice's sums have landed in the first CTA
+        if (ks != 0) return;
+        for (int n = tid >> 7; n < P.rows; n += 2) {
+            float v = 0.f;
+            for (int k2 = 0; k2 < S.splitk; ++k2) v += slices[(k2 * P.rows + n) * 128 + ocl];
+            fin[n * 128 + ocl] = v;
         }
-        __syncthreads();
-        if (!s_last) return;
-        __threadfence();
-        for (int n = tid >> 7; n < P.rows; n += 2) fin[n * 128 + ocl] = sum_slices(part, S.splitk, P.rows, n, ocl, -1, 0.f);
     }
     __syncthreads();
 
@@ -479,15 +459,13 @@ __global__ void __launch_bounds__(kThreads, 2) gemv_kernel(const __grid_constant
 // ---------------------------------------------------------------------------------------------
 // host-side plan: how the shards are cut into CTAs and how the scratch is laid out
 struct GemvPlan {
-    int nt, nb, xf_bytes, xf_blocks, region_bytes, total_ctas, total_units, kblocks;
-    long long partial_floats;
+    int nt, nb, xf_bytes, xf_blocks, region_bytes, total_ctas, total_units, kblocks, splitk;
     long long xf_words;
     long long xf_off[EXL3_MAX_SHARDS];
-    int splitk[EXL3_MAX_SHARDS], cta_begin[EXL3_MAX_SHARDS], unit_begin[EXL3_MAX_SHARDS], K[EXL3_MAX_SHARDS];
-    long long partial_off[EXL3_MAX_SHARDS];
+    int cta_begin[EXL3_MAX_SHARDS], unit_begin[EXL3_MAX_SHARDS], K[EXL3_MAX_SHARDS];
 };
 
-static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl) {
+static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl, int max_splitk = kMaxSplitK) {
     if (!sh) return EXL3_E_NULL;
     if (n < 1 || n > EXL3_MAX_SHARDS || rows < 1 || rows > EXL3_GEMV_MAX_ROWS || ic <= 0 || (ic & 127))
         return EXL3_E_SHAPE;
@@ -495,7 +473,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     pl.nt = rows > 8 ? 2 : 1;
     pl.nb = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
     const int frag_bytes_per_block = 8 * pl.nt * pl.nb * 64;
-    double total_bytes = 0;
+    int units = 0, ring = 0;
     for (int i = 0; i < n; ++i) {
         if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
         if (sh[i].mcg || sh[i].mul1) return EXL3_E_UNSUPPORTED;
@@ -504,53 +482,101 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         if (!sh[i].trellis || !sh[i].suh || !sh[i].svh) return EXL3_E_NULL;
         if (!aligned(sh[i].trellis, 16) || !aligned(sh[i].suh, 8) || !aligned(sh[i].svh, 8)) return EXL3_E_ALIGN;
         pl.K[i] = K;
-        total_bytes += (double)ic * sh[i].oc * K / 8.0;
-    }
-    int ctas = 0, units = 0, max_nblk = 0, ring = 0;
-    long long pf = 0;
-    for (int i = 0; i < n; ++i) {
-        const int ocb = sh[i].oc / 128;
-        const double share = (double)ic * sh[i].oc * pl.K[i] / 8.0 / total_bytes;
-        int sk = (int)(kTargetCtas * share / ocb + 0.5);
-        if (sk < 1) sk = 1;
-        if (sk > pl.kblocks) sk = pl.kblocks;
-        if (sk > kMaxSplitK) sk = kMaxSplitK;
-        pl.splitk[i] = sk;
-        pl.cta_begin[i] = ctas;
         pl.unit_begin[i] = units;
-        pl.partial_off[i] = pf;
-        ctas += ocb * sk;
-        units += ocb;
-        if (sk > 1) pf += (long long)ocb * sk * rows * 128;
-        const int nblk = (pl.kblocks + sk - 1) / sk;
-        max_nblk = nblk > max_nblk ? nblk : max_nblk;
-        const int r = kWarps * ring_depth(pl.K[i]) * 8 * 8 * pl.K[i] * 4;
+        units += sh[i].oc / 128;
+        const int r = kWarps * ring_depth(K) * 8 * 8 * K * 4;
         ring = r > ring ? r : ring;
     }
     if (units > kWsMaxUnits) return EXL3_E_SHAPE;
-    pl.total_ctas = ctas;
+    // Every unit (128 output channels) is cut into the same number of input slices: as many as fit two CTAs on
+    // every SM, at most one cluster's worth and at most one slice per 128 inputs.
+    // (The kernel is bound by the decode, not by bytes, so units of every bitrate weigh the same.)
+    int sk = kTargetCtas / units;                                    // never more than one wave of CTAs
+    if (sk < 1) sk = 1;
+    if (sk > pl.kblocks) sk = pl.kblocks;
+    if (sk > kMaxSplitK) sk = kMaxSplitK;
+    if (sk > max_splitk) sk = max_splitk < 1 ? 1 : max_splitk;
+    int max_nblk, max_slice;
+    for (;; --sk) {
+        max_nblk = (pl.kblocks + sk - 1) / sk;
+        // staging of one reduction pass, the summed rows, and (first CTA of a cluster) the slices' sums
+        const int red = (kWarps * 8 + pl.nt * 8) * 128 * 4 + (sk > 1 ? sk * rows * 128 * 4 : 0);
+        pl.region_bytes = ring > red ? ring : red;
+        // the activation fragments of as many 128-blocks at once as the rest of the CTA's shared memory holds
+        max_slice = (kCtaSmemBytes - kBarBytes - pl.region_bytes) / frag_bytes_per_block;
+        if (max_slice >= (max_nblk < 2 ? max_nblk : 2) || sk == 1) break;     // fewer slices leave more room
+    }
+    if (max_slice < 1) return EXL3_E_SHAPE;
+    pl.splitk = sk;
     pl.total_units = units;
-    pl.partial_floats = pf;
+    pl.total_ctas = units * sk;
     pl.xf_words = 0;
     for (int i = 0; i < n; ++i) {
+        pl.cta_begin[i] = pl.unit_begin[i] * sk;
         pl.xf_off[i] = pl.xf_words;
         pl.xf_words += (long long)pl.kblocks * frag_bytes_per_block / 4;
     }
-    const int red = (kWarps * 8 + pl.nt * 8) * 128 * 4;           // staging of one pass + the summed rows
-    pl.region_bytes = ring > red ? ring : red;
-    // the activation fragments of as many 128-blocks at once as the rest of the CTA's shared memory holds
-    const int max_slice = (kCtaSmemBytes - kBarBytes - pl.region_bytes) / frag_bytes_per_block;
-    if (max_slice < 1) return EXL3_E_SHAPE;
     pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
     pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
     return EXL3_OK;
 }
 
+// How many clusters of `c` CTAs of this kernel the current device can hold at once (cached; 0 on error).
+static int clusters_that_fit(void (*kernel)(GemvParams), int nt, int c, size_t smem) {
+    static std::mutex mu;
+    struct Entry { int dev, nt, c; size_t smem; int n; };
+    static Entry cache[64];
+    static int used = 0;
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return 0; }
+    const size_t key = (smem + 4095) & ~(size_t)4095;
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+        if (cache[i].dev == dev && cache[i].nt == nt && cache[i].c == c && cache[i].smem == key) return cache[i].n;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)key) != cudaSuccess) { cudaGetLastError(); return 0; }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)(c * 64));
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = key;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = (unsigned)c;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) { cudaGetLastError(); n = 0; }
+    if (used < 64) cache[used++] = Entry{dev, nt, c, key, n};
+    return n;
+}
+
 static size_t plan_workspace_bytes(const GemvPlan &pl) {
-    return kWsHeadBytes + (((size_t)pl.partial_floats * 4 + 255) & ~(size_t)255) + (size_t)pl.xf_words * 4;
+    return kWsHeadBytes + (size_t)pl.xf_words * 4;
+}
+
+// Shrink the plan's clusters until all of them can be resident on the current device at once.
+static int fit_clusters(const exl3_shard *shards, int nshards, int rows, int ic, GemvPlan &pl) {
+    void (*kernel)(GemvParams) = pl.nt == 1 ? gemv_kernel<1> : gemv_kernel<2>;
+    for (;;) {
+        const size_t need = (size_t)kBarBytes + pl.xf_bytes + pl.region_bytes;
+        if (pl.splitk == 1 || clusters_that_fit(kernel, pl.nt, pl.splitk, need) >= pl.total_units) return EXL3_OK;
+        const int rc = make_plan(shards, nshards, rows, ic, pl, pl.splitk - 1);
+        if (rc != EXL3_OK) return rc;
+    }
 }
 
 }  // namespace exl3
+
+extern "C" int exl3_gemv_plan(const exl3_shard *shards, int nshards, int rows, int ic, int *ctas_out, int *slices_out) {
+    exl3::GemvPlan pl;
+    int rc = exl3::make_plan(shards, nshards, rows, ic, pl);
+    if (rc == EXL3_OK) rc = exl3::fit_clusters(shards, nshards, rows, ic, pl);
+    if (rc != EXL3_OK) return rc;
+    if (ctas_out) *ctas_out = pl.total_ctas;
+    if (slices_out) *slices_out = pl.splitk;
+    return EXL3_OK;
+}
 
 extern "C" size_t exl3_gemv_workspace_bytes(const exl3_shard *shards, int nshards, int rows, int ic) {
     exl3::GemvPlan pl;
@@ -577,9 +603,7 @@ extern "C" int exl3_gemv_grouped_ex(const exl3_shard *shards, int nshards, const
     P.y = static_cast<__half *>(y);
     unsigned char *ws = static_cast<unsigned char *>(workspace);
     P.status = reinterpret_cast<unsigned *>(ws);
-    P.tickets = reinterpret_cast<unsigned *>(ws + kWsStatusBytes);
-    P.partial = reinterpret_cast<float *>(ws + kWsHeadBytes);
-    P.xfg = reinterpret_cast<uint32_t *>(ws + kWsHeadBytes + (((size_t)pl.partial_floats * 4 + 255) & ~(size_t)255));
+    P.xfg = reinterpret_cast<uint32_t *>(ws + kWsHeadBytes);
     P.rows = rows;
     P.ic = ic;
     P.ldy = ldy;
@@ -607,17 +631,28 @@ extern "C" int exl3_gemv_grouped_ex(const exl3_shard *shards, int nshards, const
         d.trellis = static_cast<const uint32_t *>(shards[i].trellis);
         d.suh = static_cast<const __half *>(shards[i].suh);
         d.svh = static_cast<const __half *>(shards[i].svh);
-        d.partial_off = pl.partial_off[i];
         d.xf_off = pl.xf_off[i];
         d.tiles_j = shards[i].oc / 16;
         d.K = pl.K[i];
         d.out_col = shards[i].out_col;
         d.cta_begin = pl.cta_begin[i];
-        d.splitk = pl.splitk[i];
+        d.splitk = pl.splitk;
         d.unit_begin = pl.unit_begin[i];
     }
-    const size_t smem = (size_t)kBarBytes + pl.xf_bytes + pl.region_bytes;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    // The slices of a unit form one thread-block cluster.  Clusters are placed whole inside one GPC, so not every
+    // cluster size lets all clusters of the grid run at once: take the largest size that does (the answer of the
+    // occupancy query is cached per kernel, size and shared-memory need).
+    void (*kernel)(GemvParams) = pl.nt == 1 ? gemv_kernel<1> : gemv_kernel<2>;
+    const int rc2 = fit_clusters(shards, nshards, rows, ic, pl);
+    if (rc2 != EXL3_OK) return rc2;
+    for (int i = 0; i < nshards; ++i) {
+        P.sh[i].cta_begin = pl.cta_begin[i];
+        P.sh[i].splitk = pl.splitk;
+    }
+    P.xf_bytes = pl.xf_bytes;
+    P.xf_blocks = pl.xf_blocks;
+    const size_t smem = (size_t)kBarBytes + pl.xf_bytes + pl.region_bytes;
     // launched with programmatic stream serialization: this grid may start (and prefetch weights)
     // while the previous kernel on the stream drains; it synchronises inside (griddepcontrol.wait)
     cudaLaunchConfig_t cfg = {};
@@ -625,30 +660,29 @@ extern "C" int exl3_gemv_grouped_ex(const exl3_shard *shards, int nshards, const
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
+    attr[1].id = cudaLaunchAttributeClusterDimension;                 // the slices of a unit form one cluster
+    attr[1].val.clusterDim.x = (unsigned)pl.splitk;
+    attr[1].val.clusterDim.y = 1;
+    attr[1].val.clusterDim.z = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = pl.splitk > 1 ? 2 : 1;
     cudaError_t e;
     {
         const int tasks = pl.nt * pl.nb * pl.kblocks * nshards;
         cudaLaunchConfig_t pc = cfg;
+        pc.numAttrs = 1;
         pc.gridDim = dim3((unsigned)((tasks + 7) / 8));
         pc.blockDim = dim3(256);
         pc.dynamicSmemBytes = 0;
         e = cudaLaunchKernelEx(&pc, xfrag_kernel, P, pl.nt);
         if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     }
-    if (pl.nt == 1) {
-        e = cudaFuncSetAttribute(gemv_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-        e = cudaLaunchKernelEx(&cfg, gemv_kernel<1>, P);
-    } else {
-        e = cudaFuncSetAttribute(gemv_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
-        e = cudaLaunchKernelEx(&cfg, gemv_kernel<2>, P);
-    }
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    e = cudaLaunchKernelEx(&cfg, kernel, P);
     if (e != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     return launch_status();
 }
@@ -698,8 +732,8 @@ extern "C" int exl3_gemv_selftest_wait(void *workspace, int polls, void *stream)
 // memory instead of a caller buffer.
 //
 // The array below is reserved on every GPU that loads the library and stays reserved until the
-// process exits; the loader zero-fills it, which is the state the kernel needs (status word and
-// tickets at zero) and the state every launch restores.  In HOST code its name is only a handle,
+// process exits; the loader zero-fills it, which is the state its status word needs (every launch overwrites
+// the rest before reading it).  In HOST code its name is only a handle,
 // not a device address, so the address is looked up once per device with cudaGetSymbolAddress
 // (with that device current) and cached.
 #define EXL3_STATIC_WS_BYTES_IMPL (2u << 20)

@@ -65,9 +65,9 @@ def test_static_scratch_matches_regular_entry_point(ext, ic, spec, rows):
 def test_static_scratch_rejects_oversized_request(ext):
     cap = ext.lib().exl3_gemv_static_capacity()
     assert 1 << 20 <= cap <= 16 << 20
-    shards, x, total = _layer(77, 17408, [(5120, 4)], 16)     # needs more split-K scratch than it holds
+    shards, x, total = _layer(77, 17408, [(128, 4)] * 8, 16)  # eight shards' rotated activations: more than it holds
     arr = ext._shard_array(x, shards)
-    need = ext.lib().exl3_gemv_workspace_bytes(arr, 1, 16, 17408)
+    need = ext.lib().exl3_gemv_workspace_bytes(arr, 8, 16, 17408)
     assert need > cap
     y = torch.zeros((16, total), dtype=torch.half, device="cuda")
     with pytest.raises(RuntimeError, match="workspace"):
