@@ -238,13 +238,15 @@ int exl3_int8_embed(const void *qweight, const void *scales, const void *ids, vo
                     void *stream);
 
 /*
- * int8 head:  logits[r][v] = scales[v] * sum_h x[r][h] * q[v][h]  for 1..16 rows, written as dt
- * with leading dimension ld_logits.  hidden must be a multiple of 64.  The table is streamed
- * once as int8 and never dequantised into memory.  Replaces Exl3EmbeddingMethod.apply
+ * int8 head:  logits[r][v] = scales[v] * sum_h x[r][h] * q[v][h]  for 1..64 rows per call, written as dt
+ * with leading dimension ld_logits.  hidden must be a multiple of 64 (of 256, with x 16-byte aligned,
+ * above 16 rows).  The table is streamed ONCE per call as int8 and never dequantised into memory: up to 16
+ * rows the activations stay resident in shared memory, above that they are staged chunk by chunk.  Replaces Exl3EmbeddingMethod.apply
  * (orcasaq2/heads.py:69-75), which materialises the dt table on every call; that version
  * rounds q*s to dt before the product, this one scales the exact integer dot product, so the
  * two agree within the layer tolerance, not bit for bit.
  */
+#define EXL3_INT8_HEAD_MAX_ROWS 64
 int exl3_int8_head(const void *qweight, const void *scales, const void *x, void *logits, int rows,
                    int vocab, int hidden, long long ld_logits, int is_bf16, void *stream);
 
@@ -302,6 +304,18 @@ int exl3_decode_attn_paged(const void *q, const void *k_pages, const void *v_pag
 int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, int cos_sin_batch_stride,
                      void *k_cache, void *v_cache, int batch, int q_heads, int kv_heads, int head_dim,
                      int pos, long long kv_batch_stride, long long kv_head_stride, void *stream);
+
+/*
+ * Measurement probe (no counterpart in the reference, not on the layer's path): the rate at which the GPU can
+ * decode the 3INST codebook with this library's decode routines and consume the codewords with mma.sync, on every
+ * SM.  mode 0: words never leave registers (the ceiling the integer decode sets for any kernel of this design);
+ * mode 1: words come from a shared-memory ring refilled by bulk async copies from a small L2-resident buffer,
+ * with the waits and loads of a real streaming loop.  Launches one kernel of `iters` iterations on `stream`;
+ * *weights_out receives the number of weights it decodes (time it with events).  scratch: at least 1 MiB + 8.5
+ * KiB of device memory, 256-byte aligned, first word zero (set non-zero if a bounded wait ran out).
+ */
+int exl3_probe_decode_rate(int k, int mode, int iters, void *scratch, size_t scratch_bytes, double *weights_out,
+                           void *stream);
 
 /*
  * One-shot all-reduce (sum) of fp16 partial results over peer memory, for the outputs of row-parallel layers

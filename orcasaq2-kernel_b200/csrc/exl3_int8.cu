@@ -203,6 +203,177 @@ static int launch_head(const void *q, const void *s, const void *x, void *out, i
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------ head, 17..64 rows
+// More rows than the kernel above keeps resident: the table is still streamed ONCE per call.  A CTA takes 256
+// vocabulary rows at a time (16 per warp, accumulators for all batch rows in registers) and walks the hidden
+// dimension in chunks of 256; the activations of a chunk -- [rows][256] fp16, converted once -- are staged in
+// shared memory for all sixteen warps (double-buffered: the next chunk is fetched from L2 into registers while
+// this one is multiplied).  Per call the table crosses HBM once and the activations cross L2 -> SM once per 256
+// vocabulary rows, i.e. about as many bytes as the table itself.
+constexpr int kRowsChunk = 256;            // hidden channels per staged chunk
+constexpr int kRowsPitch = kRowsChunk + 8; // halves per staged activation row (bank-conflict padding)
+
+template <typename T, int NT>
+__global__ void __launch_bounds__(kHeadThreads, 1)
+int8_head_rows_kernel(const int8_t *__restrict__ q, const T *__restrict__ s, const T *__restrict__ x,
+                      T *__restrict__ out, int rows, int vocab, int hidden, long long ldo) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    constexpr int kRowsPad = NT * 8;
+    __half *xs = reinterpret_cast<__half *>(smem_raw);                            // [2][kRowsPad][kRowsPitch]
+    float *rscale = reinterpret_cast<float *>(xs + 2 * kRowsPad * kRowsPitch);    // [kRowsPad] undo factors
+    float *rinv = rscale + kRowsPad;                                              // [kRowsPad] scale factors
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int g = lane >> 2, tig = lane & 3;
+
+    // power-of-two scale per bf16 row so that its largest magnitude fits fp16 (as in the resident kernel)
+    for (int r = warp; r < kRowsPad; r += kHeadWarps) {
+        float inv = 1.f, undo = 1.f;
+        if (r < rows && sizeof(T) == 2 && !std::is_same<T, __half>::value) {
+            float m = 0.f;
+            for (int h = lane; h < hidden; h += 32) m = fmaxf(m, fabsf(to_float<T>(x[(size_t)r * hidden + h])));
+#pragma unroll
+            for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+            int e = 0;
+            if (m > 16384.f && m < 3.0e38f) { frexpf(m, &e); e -= 14; }
+            inv = ldexpf(1.f, -e);
+            undo = ldexpf(1.f, e);
+        }
+        if (lane == 0) { rscale[r] = undo; rinv[r] = inv; }
+    }
+    __syncthreads();
+
+    // staging: a thread moves kPer pieces of eight values per chunk; piece p covers row p / 32, columns 8 * (p % 32)
+    constexpr int kPieces = kRowsPad * (kRowsChunk / 8);
+    constexpr int kPer = kPieces / kHeadThreads;
+    static_assert(kPieces % kHeadThreads == 0, "chunk pieces divide among the threads");
+    uint4 stage[kPer];
+    auto fetch = [&](int h0) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int p = threadIdx.x + i * kHeadThreads;
+            const int r = p >> 5, c = (p & 31) * 8;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < rows) {
+                const uint4 raw = *reinterpret_cast<const uint4 *>(x + (size_t)r * hidden + h0 + c);
+                if (std::is_same<T, __half>::value) v = raw;
+                else {
+                    const T *t8 = reinterpret_cast<const T *>(&raw);
+                    const float inv = rinv[r];
+                    __half2 *o = reinterpret_cast<__half2 *>(&v);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) o[k] = __floats2half2_rn(to_float<T>(t8[2 * k]) * inv, to_float<T>(t8[2 * k + 1]) * inv);
+                }
+            }
+            stage[i] = v;
+        }
+    };
+    auto put = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < kPer; ++i) {
+            const int p = threadIdx.x + i * kHeadThreads;
+            const int r = p >> 5, c = (p & 31) * 8;
+            *reinterpret_cast<uint4 *>(xs + ((size_t)buf * kRowsPad + r) * kRowsPitch + c) = stage[i];
+        }
+    };
+
+    const int nchunks = hidden / kRowsChunk;
+    const int batches = (vocab + 16 * kHeadWarps - 1) / (16 * kHeadWarps);
+    int buf = 0;
+    for (int b = blockIdx.x; b < batches; b += gridDim.x) {
+        const int v0 = (b * kHeadWarps + warp) * 16;
+        const int va = min(v0 + g, vocab - 1), vb = min(v0 + g + 8, vocab - 1);
+        const int8_t *ra = q + (size_t)va * hidden + 16 * tig;
+        const int8_t *rb = q + (size_t)vb * hidden + 16 * tig;
+        float acc[NT][4];
+#pragma unroll
+        for (int t = 0; t < NT; ++t)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[t][e] = 0.f;
+        fetch(0);
+        __syncthreads();                               // the previous batch's last chunk has been read
+        put(buf);
+        __syncthreads();
+        for (int c = 0; c < nchunks; ++c) {
+            const int h0 = c * kRowsChunk;
+            // this chunk's table bytes (four 64-channel steps), all loads in flight at once
+            uint4 wa[4], wb[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                wa[k] = __ldg(reinterpret_cast<const uint4 *>(ra + h0 + 64 * k));
+                wb[k] = __ldg(reinterpret_cast<const uint4 *>(rb + h0 + 64 * k));
+            }
+            if (c + 1 < nchunks) fetch(h0 + kRowsChunk);
+            const __half *xc = xs + (size_t)buf * kRowsPad * kRowsPitch;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const uint32_t aw[4] = {wa[k].x, wa[k].y, wa[k].z, wa[k].w};
+                const uint32_t bw[4] = {wb[k].x, wb[k].y, wb[k].z, wb[k].w};
+                uint32_t a0[4], a1[4], a2[4], a3[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    int8x4_to_half2x2(aw[j], a0[j], a2[j]);
+                    int8x4_to_half2x2(bw[j], a1[j], a3[j]);
+                }
+#pragma unroll
+                for (int t = 0; t < NT; ++t) {
+                    const __half *xr = xc + (size_t)(8 * t + g) * kRowsPitch + 64 * k + 16 * tig;
+                    const uint4 x0 = *reinterpret_cast<const uint4 *>(xr);
+                    const uint4 x1 = *reinterpret_cast<const uint4 *>(xr + 8);
+                    mma16816h(acc[t], a0[0], a1[0], a2[0], a3[0], x0.x, x0.y);
+                    mma16816h(acc[t], a0[1], a1[1], a2[1], a3[1], x0.z, x0.w);
+                    mma16816h(acc[t], a0[2], a1[2], a2[2], a3[2], x1.x, x1.y);
+                    mma16816h(acc[t], a0[3], a1[3], a2[3], a3[3], x1.z, x1.w);
+                }
+            }
+            if (c + 1 < nchunks) {
+                put(buf ^ 1);                          // nobody reads that buffer: its last readers passed the barrier below
+                __syncthreads();
+                buf ^= 1;
+            }
+        }
+        if (v0 < vocab) {
+            const float sa = to_float<T>(s[va]), sb = to_float<T>(s[vb]);
+#pragma unroll
+            for (int t = 0; t < NT; ++t) {
+                const int n0 = 8 * t + 2 * tig;
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int n = n0 + e;
+                    if (n < rows) {
+                        const float un = rscale[n];
+                        if (v0 + g < vocab) out[(size_t)n * ldo + v0 + g] = from_float<T>(acc[t][e] * sa * un);
+                        if (v0 + g + 8 < vocab) out[(size_t)n * ldo + v0 + g + 8] = from_float<T>(acc[t][2 + e] * sb * un);
+                    }
+                }
+            }
+        }
+    }
+}
+
+template <typename T, int NT>
+static int launch_head_rows_nt(const void *q, const void *s, const void *x, void *out, int rows, int vocab, int hidden,
+                               long long ldo, int sms, cudaStream_t st) {
+    const size_t smem = (size_t)2 * NT * 8 * kRowsPitch * 2 + (size_t)2 * NT * 8 * 4;
+    if (cudaFuncSetAttribute(int8_head_rows_kernel<T, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    const int batches = (vocab + 16 * kHeadWarps - 1) / (16 * kHeadWarps);
+    const int grid = batches < sms ? batches : sms;
+    int8_head_rows_kernel<T, NT><<<grid, kHeadThreads, smem, st>>>(
+        static_cast<const int8_t *>(q), static_cast<const T *>(s), static_cast<const T *>(x), static_cast<T *>(out),
+        rows, vocab, hidden, ldo);
+    return launch_status();
+}
+template <typename T>
+static int launch_head_rows(const void *q, const void *s, const void *x, void *out, int rows, int vocab, int hidden,
+                            long long ldo, cudaStream_t st) {
+    int dev = 0, sms = 148;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    return rows <= 32 ? launch_head_rows_nt<T, 4>(q, s, x, out, rows, vocab, hidden, ldo, sms, st)
+                      : launch_head_rows_nt<T, 8>(q, s, x, out, rows, vocab, hidden, ldo, sms, st);
+}
+
 }  // namespace exl3
 
 extern "C" int exl3_int8_embed(const void *qweight, const void *scales, const void *ids, void *out, int tokens,
@@ -233,9 +404,16 @@ extern "C" int exl3_int8_head(const void *qweight, const void *scales, const voi
                               int vocab, int hidden, long long ld_logits, int is_bf16, void *stream) {
     using namespace exl3;
     if (!qweight || !scales || !x || !logits) return EXL3_E_NULL;
-    if (rows < 1 || rows > 16 || vocab <= 0 || hidden <= 0 || (hidden & 63) || ld_logits < vocab) return EXL3_E_SHAPE;
+    if (rows < 1 || rows > EXL3_INT8_HEAD_MAX_ROWS || vocab <= 0 || hidden <= 0 || (hidden & 63) || ld_logits < vocab)
+        return EXL3_E_SHAPE;
     if (!aligned(qweight, 16)) return EXL3_E_ALIGN;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (rows > 16) {
+        // the staged form: hidden in chunks of 256, activation rows read 16 bytes at a time
+        if ((hidden & 255) || !aligned(x, 16)) return EXL3_E_SHAPE;
+        return is_bf16 ? launch_head_rows<__nv_bfloat16>(qweight, scales, x, logits, rows, vocab, hidden, ld_logits, st)
+                       : launch_head_rows<__half>(qweight, scales, x, logits, rows, vocab, hidden, ld_logits, st);
+    }
     return is_bf16 ? launch_head<__nv_bfloat16>(qweight, scales, x, logits, rows, vocab, hidden, ld_logits, st)
                    : launch_head<__half>(qweight, scales, x, logits, rows, vocab, hidden, ld_logits, st);
 }

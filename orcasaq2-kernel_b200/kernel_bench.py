@@ -9,6 +9,7 @@
     python kernel_bench.py attn --rows 32 --ctx 4096 [--qh 24 --kvh 4 --sdpa --page 16]   # decode attention, rows = batch
     python kernel_bench.py prefill        # BASELINE config 3: both shapes, M = 512 / 2048 / 8192
     python kernel_bench.py shards         # BASELINE configs 1 and 2: every shard, rows 1 / 4 / 16
+    python kernel_bench.py decode_rate    # ceiling of the 3INST decode + mma.sync on this GPU, per bitrate (no HBM involved)
 
 Each line reports the kernel's algorithmic bytes (or flops) per second.  `--iters N` launches
 (default 20) after 3 warm-ups; small cases (`--iters 3`) are what the ncu recipes use.
@@ -186,10 +187,40 @@ def bench_attn(batch, qh, kvh, ctx, iters, sdpa, page=0):
     return r
 
 
+def bench_decode_rate(iters=2000):
+    """exl3_probe_decode_rate per bitrate: registers only, and through a shared-memory ring fed by bulk copies."""
+    import ctypes
+    L = _ext.lib()
+    L.exl3_probe_decode_rate.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t,
+                                         ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]
+    scratch = torch.zeros((2 << 20,), dtype=torch.uint8, device=DEV)
+    out = []
+    for K in range(1, 9):
+        row = dict(kernel="decode_rate", K=K)
+        for mode, name in ((0, "registers_only_Tw_s"), (1, "smem_ring_Tw_s")):
+            w = ctypes.c_double(0)
+            st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+            best = 1e9
+            for rep in range(4):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                rc = L.exl3_probe_decode_rate(K, mode, iters, scratch.data_ptr(), scratch.numel(), ctypes.byref(w), st)
+                b.record()
+                torch.cuda.synchronize()
+                assert rc == 0, rc
+                if rep:
+                    best = min(best, a.elapsed_time(b))
+            row[name] = round(w.value / (best * 1e-3) / 1e12, 2)
+            row[name.replace("Tw_s", "GBs_at_this_bitrate")] = round(w.value * K / 8 / (best * 1e-3) / 1e9, 0)
+        row["status"] = int(scratch[:4].view(torch.int32).item())
+        out.append(row)
+    return out
+
+
 def main():
     global DEV
     ap = argparse.ArgumentParser()
-    ap.add_argument("what", choices=["gemv", "gemm_tc", "reconstruct", "int8_head", "int8_embed", "had", "prefill", "shards", "attn"])
+    ap.add_argument("what", choices=["gemv", "gemm_tc", "reconstruct", "int8_head", "int8_embed", "had", "prefill", "shards", "attn", "decode_rate"])
     ap.add_argument("--ic", type=int, default=5120)
     ap.add_argument("--oc", type=int, default=17408)
     ap.add_argument("--k", type=int, default=4)
@@ -226,6 +257,8 @@ def main():
         out.append(bench_had(a.rows, a.ic, a.iters))
     elif a.what == "attn":
         out.append(bench_attn(a.rows, a.qh, a.kvh, a.ctx, a.iters, a.sdpa, a.page))
+    elif a.what == "decode_rate":
+        out.extend(bench_decode_rate())
     elif a.what == "prefill":
         for ic, oc, K in ((5120, 17408, 3), (17408, 5120, 4)):
             for m in (512, 2048, 8192):

@@ -313,7 +313,7 @@ def hgemm_recon(a: torch.Tensor, w: torch.Tensor, y: torch.Tensor) -> None:
 
 
 _DT = (torch.float16, torch.bfloat16)
-HEAD_MAX_ROWS = 16
+HEAD_MAX_ROWS = 64          # rows per pass over the table (EXL3_INT8_HEAD_MAX_ROWS)
 
 
 def int8_embed(qweight: torch.Tensor, scales: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
@@ -351,8 +351,10 @@ def int8_head(qweight: torch.Tensor, scales: torch.Tensor, x: torch.Tensor) -> t
         raise RuntimeError("int8_head: shapes of x, qweight and scales do not agree")
     out = torch.empty((rows, vocab), dtype=x.dtype, device=x.device)
     L = lib()
-    for r0 in range(0, rows, HEAD_MAX_ROWS):
-        r1 = min(rows, r0 + HEAD_MAX_ROWS)
+    # one pass over the table serves up to 64 rows (16 when the hidden size is not a multiple of 256)
+    per_pass = HEAD_MAX_ROWS if hidden % 256 == 0 else 16
+    for r0 in range(0, rows, per_pass):
+        r1 = min(rows, r0 + per_pass)
         _check(L.exl3_int8_head(qweight.data_ptr(), scales.data_ptr(), x[r0:r1].data_ptr(),
                                 out[r0:r1].data_ptr(), r1 - r0, vocab, hidden, vocab,
                                 int(x.dtype == torch.bfloat16), _stream(x)), "exl3_int8_head")

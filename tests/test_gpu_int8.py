@@ -63,6 +63,38 @@ def test_head_vs_oracle(ext, coracle, name, rows, vocab, hidden):
     assert rel <= (2e-3 if name == "f16" else 1e-2) and cos >= 0.9999, (rel, cos)
 
 
+@pytest.mark.parametrize("name", ["f16", "bf16"])
+@pytest.mark.parametrize("rows,vocab,hidden", [(17, 1000, 256), (32, 515, 512), (33, 4099, 1024), (64, 2048 + 7, 5120), (300, 300, 768)])
+def test_head_many_rows_one_pass_over_the_table(ext, coracle, name, rows, vocab, hidden):
+    """17..64 rows are served by ONE pass over the int8 table (the staged kernel); more rows in passes of 64."""
+    q, s = R.make_int8_table(rows + vocab, vocab, hidden, DT[name])
+    x = torch.randn((rows, hidden), generator=torch.Generator().manual_seed(rows)).to(DT[name])
+    out = ext.int8_head(q.cuda(), s.cuda(), x.cuda())
+    assert out.shape == (rows, vocab) and out.dtype == DT[name]
+    ref = coracle.int8_head(q.numpy(), _bits(s), _bits(x), name == "bf16")
+    got = out.float().cpu().numpy()
+    rel = np.abs(got - ref).max() / np.abs(ref).max()
+    cos = float((got * ref).sum() / np.linalg.norm(got) / np.linalg.norm(ref))
+    assert rel <= (2e-3 if name == "f16" else 1e-2) and cos >= 0.9999, (rel, cos)
+    # the rows do not depend on how many others ride along: the first 5 rows alone (resident kernel) agree closely
+    few = ext.int8_head(q.cuda(), s.cuda(), x[:5].cuda()).float().cpu().numpy()
+    assert np.abs(few - got[:5]).max() / np.abs(ref).max() <= (2e-3 if name == "f16" else 1e-2)
+
+
+def test_head_many_rows_bf16_large_activations_and_direct_call_limits(ext, coracle):
+    q, s = R.make_int8_table(6, 512, 256, torch.bfloat16)
+    x = (torch.randn((40, 256), generator=torch.Generator().manual_seed(4)) * 3.0e5).to(torch.bfloat16)
+    out = ext.int8_head(q.cuda(), s.cuda(), x.cuda()).float().cpu().numpy()
+    ref = coracle.int8_head(q.numpy(), _bits(s), _bits(x), True)
+    assert np.isfinite(out).all() and np.abs(out - ref).max() / np.abs(ref).max() <= 1e-2
+    L = ext.lib()
+    lg = torch.empty((65, 512), dtype=torch.bfloat16, device="cuda")
+    xx = torch.zeros((65, 256), dtype=torch.bfloat16, device="cuda")
+    args = lambda r, h: (q.cuda().data_ptr(), s.cuda().data_ptr(), xx.data_ptr(), lg.data_ptr(), r, 512, h, 512, 1, None)  # noqa: E731
+    assert L.exl3_int8_head(*args(65, 256)) == -1        # more rows than one call takes
+    assert L.exl3_int8_head(*args(20, 192)) == -1        # above 16 rows the hidden size must be a multiple of 256
+
+
 def test_head_bf16_large_activations(ext, coracle):
     """bf16 rows beyond the fp16 range are rescaled inside the kernel, not clipped."""
     q, s = R.make_int8_table(5, 256, 128, torch.bfloat16)
