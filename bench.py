@@ -603,7 +603,7 @@ def prefill_block(torch, _ext, dev):
 # Decode + mma.sync rate of the 3INST codebook with no memory access at all (registers only, every SM busy),
 # in 10^12 weights per second on B200 at 1.9 GHz, per bitrate: the ceiling of any kernel that decodes this
 # codebook with integer instructions and consumes the codewords with mma.sync (profiles/decode_rate_b200.md).
-DECODE_CEILING_TWS = {2: 6.35, 3: 5.48, 4: 5.96, 5: 5.37, 6: 5.28}
+DECODE_CEILING_TWS = {2: 6.14, 3: 5.51, 4: 5.91, 5: 5.39, 6: 5.36}
 
 
 def roofline_by_k(torch, dist, _ext, dev, peak):
