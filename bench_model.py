@@ -85,7 +85,7 @@ def rms(x, eps=1e-6):
     return (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).half()
 
 
-def build(rank, world, batch, ctx, dev, layers, dims=None):
+def build(rank, world, batch, ctx, dev, layers, dims=None, kv="fp16"):
     """Random-init decoder of `layers` layers on this rank: [(qkv, o, gate_up, down, k_cache, v_cache)], the int8
     table and its scales, bytes of packed weights and of KV cache read per step, and the local head counts."""
     d = dims or DIMS_27B
@@ -103,9 +103,11 @@ def build(rank, world, batch, ctx, dev, layers, dims=None):
         down = Linear([rand_shard(FFN // world, HIDDEN, ks[6], dev, wgen)], batch, dev)
         kc = torch.randn((batch, kvh, ctx + 1, HD), device=dev, generator=wgen).half()
         vc = torch.randn((batch, kvh, ctx + 1, HD), device=dev, generator=wgen).half()
+        if kv == "fp8":                                               # e4m3 bytes, scale 1 (the engine's default)
+            kc, vc = kc.to(torch.float8_e4m3fn), vc.to(torch.float8_e4m3fn)
         model.append((qkv, o, gu, down, kc, vc))
         wbytes += qkv.bytes + o.bytes + gu.bytes + down.bytes
-        kvbytes += 2 * batch * kvh * ctx * HD * 2
+        kvbytes += 2 * batch * kvh * ctx * HD * kc.element_size()
     vslice = VOCAB // world
     table = torch.randint(-127, 128, (vslice, HIDDEN), dtype=torch.int8, device=dev, generator=wgen)
     scales = (torch.rand((vslice,), device=dev, generator=wgen) * 0.02 + 1e-3).half()
@@ -115,7 +117,7 @@ def build(rank, world, batch, ctx, dev, layers, dims=None):
 def default_args(**over):
     """The command-line defaults as a namespace (for callers that run the benchmark in-process)."""
     ns = argparse.Namespace(batch=1, ctx=4096, steps=20, warmup=3, layers=LAYERS, no_graph=False, attn="own", tc_from=9,
-                            allreduce="oneshot")
+                            allreduce="oneshot", kv="fp16")
     for k, v in over.items():
         setattr(ns, k, v)
     return ns
@@ -187,7 +189,10 @@ def run(args):
     from orcasaq2 import _ext
     _ext.lib()
     B, ctx = args.batch, args.ctx
-    model, table, scales, wbytes, kvbytes, qh, kvh = build(rank, world, B, ctx, dev, args.layers)
+    kv = getattr(args, "kv", "fp16")
+    if kv == "fp8" and args.attn != "own":
+        raise SystemExit("--kv fp8 needs this library's attention kernel (--attn own)")
+    model, table, scales, wbytes, kvbytes, qh, kvh = build(rank, world, B, ctx, dev, args.layers, kv=kv)
     ids = torch.randint(0, table.shape[0], (B,), device=dev)
     ar = None
     if world > 1 and getattr(args, "allreduce", "oneshot") == "oneshot":
@@ -243,7 +248,7 @@ def run(args):
         "allreduce": "one-shot kernel over peer memory" if ar is not None else ("nccl" if world > 1 else None),
         "per_gpu_bytes_per_step": {"packed_weights": wbytes, "kv_cache": kvbytes},
         "per_gpu_hbm_gbs": round(per_gpu, 1), "frac_of_measured_hbm": round(per_gpu / peak, 4),
-        "data": "synthetic (random-init weights, random KV cache)", "attention": "exl3_decode_attn" if args.attn == "own" else "torch SDPA (library)",
+        "kv_cache_dtype": kv, "data": "synthetic (random-init weights, random KV cache)", "attention": "exl3_decode_attn" if args.attn == "own" else "torch SDPA (library)",
     }
 
 
@@ -257,6 +262,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--attn", choices=["own", "sdpa"], default="own",
                     help="decode attention: this library's kernel, or torch's scaled_dot_product_attention")
+    ap.add_argument("--kv", choices=["fp16", "fp8"], default="fp16", help="KV cache: fp16, or e4m3 with scale 1")
     ap.add_argument("--tc-from", type=int, default=9, help="smallest batch that takes the tcgen05 path (9..17)")
     ap.add_argument("--allreduce", default="oneshot", choices=["oneshot", "nccl"],
                     help="tensor parallel: this library's one-shot all-reduce over peer memory, or the NCCL collective")

@@ -306,6 +306,33 @@ int exl3_rope_append(void *qkv, int ld_qkv, const void *cos, const void *sin, in
                      int pos, long long kv_batch_stride, long long kv_head_stride, void *stream);
 
 /*
+ * The same three steps over an fp8 cache (e4m3 bytes, one positive scale per tensor for K and one for V: the
+ * cache holds value / scale; the form the engine keeps under `--kv-cache-dtype fp8`, reference
+ * presets/16gb.env:17).  q and out stay fp16.  Arguments as for the fp16 entry points, except: cache strides are in
+ * elements = bytes and must be multiples of 16; the workspace size comes from exl3_decode_attn_fp8_workspace_bytes
+ * (rings are half as large, two CTAs share an SM, so the sequence is cut differently); k_scale and v_scale must be
+ * > 0.  The bytes are widened to fp16 exactly in registers, so the result equals the fp16 kernel's arithmetic on
+ * the dequantised cache (K . k_scale folded into the softmax scale, V . v_scale into the normalisation).
+ * exl3_rope_append_fp8 rounds the rotated key to fp16 first, then value / scale to e4m3 with saturation.
+ */
+size_t exl3_decode_attn_fp8_workspace_bytes(int batch, int q_heads, int kv_heads, int seq_len);
+int exl3_decode_attn_fp8(const void *q, const void *k_cache, const void *v_cache, void *out,
+                         void *workspace, size_t workspace_bytes, int batch, int q_heads, int kv_heads,
+                         int head_dim, int seq_len, long long q_batch_stride, long long out_batch_stride,
+                         long long kv_batch_stride, long long kv_head_stride, float scale, float k_scale,
+                         float v_scale, void *stream);
+int exl3_decode_attn_paged_fp8(const void *q, const void *k_pages, const void *v_pages, const void *block_table,
+                               const void *seq_lens, void *out, void *workspace, size_t workspace_bytes,
+                               int batch, int q_heads, int kv_heads, int head_dim, int max_seq_len,
+                               int page_size, int block_table_stride, long long q_batch_stride,
+                               long long out_batch_stride, long long page_stride, long long head_stride,
+                               long long token_stride, float scale, float k_scale, float v_scale, void *stream);
+int exl3_rope_append_fp8(void *qkv, int ld_qkv, const void *cos, const void *sin, int cos_sin_batch_stride,
+                         void *k_cache, void *v_cache, int batch, int q_heads, int kv_heads, int head_dim,
+                         int pos, long long kv_batch_stride, long long kv_head_stride, float k_scale,
+                         float v_scale, void *stream);
+
+/*
  * Measurement probe (no counterpart in the reference, not on the layer's path): the rate at which the GPU can
  * decode the 3INST codebook with this library's decode routines and consume the codewords with mma.sync, on every
  * SM.  mode 0: words never leave registers (the ceiling the integer decode sets for any kernel of this design);

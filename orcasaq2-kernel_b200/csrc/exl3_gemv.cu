@@ -175,6 +175,14 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     constexpr int kHalfWords = 4 * 8 * K;            // four tiles
     constexpr int kStageWords = 2 * kHalfWords;      // one tile row of the 128-column block
     constexpr uint32_t kStageBytes = kStageWords * 4;
+    // More than eight rows: the activation fragments of a step (1 KB per warp) no longer fit in shared memory for a
+    // whole slice, so they ride in the warp's own ring behind the packed words of the same step (a second bulk copy
+    // on the same barrier) instead of being fetched for the whole CTA in batches that every warp has to wait for.
+    constexpr bool kStreamX = NT == 2;
+    constexpr int kFragWords = kStreamX ? NT * 8 * 16 : 0;
+    constexpr uint32_t kFragBytes = kFragWords * 4;
+    constexpr int kSlotWords = kStageWords + kFragWords;
+    constexpr uint32_t kSlotBytes = kSlotWords * 4;
 
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -190,7 +198,7 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     uint64_t *bars = reinterpret_cast<uint64_t *>(smem);
     uint32_t *xf = reinterpret_cast<uint32_t *>(smem + kBarBytes);
     unsigned char *region = smem + kBarBytes + P.xf_bytes;
-    uint32_t *ring = reinterpret_cast<uint32_t *>(region) + warp * (kDepth * kStageWords);
+    uint32_t *ring = reinterpret_cast<uint32_t *>(region) + warp * (kDepth * kSlotWords);
     const uint32_t bar0 = smem_u32(bars + warp * 8);
     const uint32_t ring0 = smem_u32(ring);
 
@@ -211,8 +219,8 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     if (lane == 0) {
         const int pre = nblk < kDepth ? nblk : kDepth;
         for (int s = 0; s < pre; ++s) {
-            mbar_expect_tx(bar0 + 8 * s, kStageBytes);
-            bulk_g2s(ring0 + s * kStageBytes, src0 + s * src_step, kStageBytes, bar0 + 8 * s);
+            mbar_expect_tx(bar0 + 8 * s, kStageBytes + kFragBytes);   // the fragments follow after the dependency wait
+            bulk_g2s(ring0 + s * kSlotBytes, src0 + s * src_step, kStageBytes, bar0 + 8 * s);
         }
     }
 
@@ -230,7 +238,10 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     const int xf_tile_words = nrow * 16;             // words of fragments per tile
     const uint32_t *xf_lane = xf + ((g & (NB - 1)) * 4 + q) * 4 + warp * xf_tile_words;
     const int nxt_lane = (lane & 24) | ((lane + 1) & 7);
-    const int sub_max = P.xf_blocks;                 // blocks of fragments that fit at once
+    const int sub_max = kStreamX ? nblk : P.xf_blocks;   // blocks of fragments that fit at once
+    // streamed fragments: this warp's tile of block kb0 + s
+    const uint32_t *xsrc0 = P.xfg + S.xf_off + ((size_t)kb0 * 8 + warp) * xf_tile_words;
+    const size_t xsrc_step = (size_t)8 * xf_tile_words;
     int slot = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -241,31 +252,44 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
     // finish, and let the grid after this one begin its own weight prefetch.
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
+    if (kStreamX && lane == 0) {
+        const int pre = nblk < kDepth ? nblk : kDepth;
+        for (int s = 0; s < pre; ++s)
+            bulk_g2s(ring0 + s * kSlotBytes + kStageBytes, xsrc0 + s * xsrc_step, kFragBytes, bar0 + 8 * s);
+    }
 
     for (int b0 = 0; b0 < nblk; b0 += sub_max) {
         const int nb_sub = min(sub_max, nblk - b0);
-        if (b0) __syncthreads();                     // the previous fragments are no longer read
-        // ---- rotated activations of these blocks: one bulk copy from the fragment scratch
-        if (tid == 0) {
-            const uint32_t bytes = (uint32_t)nb_sub * 8u * (uint32_t)xf_tile_words * 4u;
-            mbar_expect_tx(xbar, bytes);
-            bulk_g2s(smem_u32(xf), P.xfg + S.xf_off + (size_t)(kb0 + b0) * 8 * xf_tile_words, bytes, xbar);
+        if constexpr (!kStreamX) {
+            if (b0) __syncthreads();                 // the previous fragments are no longer read
+            // ---- rotated activations of these blocks: one bulk copy from the fragment scratch
+            if (tid == 0) {
+                const uint32_t bytes = (uint32_t)nb_sub * 8u * (uint32_t)xf_tile_words * 4u;
+                mbar_expect_tx(xbar, bytes);
+                bulk_g2s(smem_u32(xf), P.xfg + S.xf_off + (size_t)(kb0 + b0) * 8 * xf_tile_words, bytes, xbar);
+            }
+            ok = mbar_wait(xbar, xphase, P.status) && ok;
+            xphase ^= 1u;
         }
-        ok = mbar_wait(xbar, xphase, P.status) && ok;
-        xphase ^= 1u;
 
         // ---- stream, decode, multiply
         const uint32_t *xfp = xf_lane;
         for (int s = b0; s < b0 + nb_sub && ok; ++s) {
             ok = mbar_wait(bar0 + 8 * slot, phase, P.status);
-            const uint32_t *stage = ring + slot * kStageWords + lane * K;
+            const uint32_t *stage = ring + slot * kSlotWords + lane * K;
             uint32_t wa[K + 1], wb[K + 1];
             load_words<K>(stage, wa);
             load_words<K>(stage + kHalfWords, wb);
             uint4 xa[NT];
+            if constexpr (kStreamX) {
+                const uint32_t *xs = ring + slot * kSlotWords + kStageWords + (g * 4 + q) * 4;
 #pragma unroll
-            for (int t = 0; t < NT; ++t) xa[t] = *reinterpret_cast<const uint4 *>(xfp + t * NB * 16);
-            xfp += 8 * xf_tile_words;
+                for (int t = 0; t < NT; ++t) xa[t] = *reinterpret_cast<const uint4 *>(xs + t * 8 * 16);
+            } else {
+#pragma unroll
+                for (int t = 0; t < NT; ++t) xa[t] = *reinterpret_cast<const uint4 *>(xfp + t * NB * 16);
+                xfp += 8 * xf_tile_words;
+            }
             wa[K] = __shfl_sync(0xffffffffu, wa[0], nxt_lane);
             wb[K] = __shfl_sync(0xffffffffu, wb[0], nxt_lane);
 
@@ -273,9 +297,12 @@ __device__ __forceinline__ void gemv_cta(const GemvParams &P, const GemvShardDev
             // every lane has consumed the slot (its words are in registers): refill it
             __syncwarp();
             if (lane == 0 && s + kDepth < nblk) {
-                mbar_expect_tx(bar0 + 8 * slot, kStageBytes);
-                bulk_g2s(ring0 + slot * kStageBytes, src0 + (size_t)(s + kDepth) * src_step, kStageBytes,
+                mbar_expect_tx(bar0 + 8 * slot, kStageBytes + kFragBytes);
+                bulk_g2s(ring0 + slot * kSlotBytes, src0 + (size_t)(s + kDepth) * src_step, kStageBytes,
                          bar0 + 8 * slot);
+                if constexpr (kStreamX)
+                    bulk_g2s(ring0 + slot * kSlotBytes + kStageBytes, xsrc0 + (size_t)(s + kDepth) * xsrc_step,
+                             kFragBytes, bar0 + 8 * slot);
             }
             consume_chunk<K, NT>(wb, acc, 1, xa, dc);
             if (++slot == kDepth) { slot = 0; phase ^= 1u; }
@@ -473,6 +500,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
     pl.nt = rows > 8 ? 2 : 1;
     pl.nb = rows <= 1 ? 1 : rows <= 2 ? 2 : rows <= 4 ? 4 : 8;
     const int frag_bytes_per_block = 8 * pl.nt * pl.nb * 64;
+    const bool stream_x = pl.nt == 2;                 // fragments ride in the warps' rings (1 KB per warp and step)
     int units = 0, ring = 0;
     for (int i = 0; i < n; ++i) {
         if (sh[i].oc <= 0 || (sh[i].oc & 127) || sh[i].out_col < 0 || (sh[i].out_col & 3)) return EXL3_E_SHAPE;
@@ -484,7 +512,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         pl.K[i] = K;
         pl.unit_begin[i] = units;
         units += sh[i].oc / 128;
-        const int r = kWarps * ring_depth(K) * 8 * 8 * K * 4;
+        const int r = kWarps * ring_depth(K) * (8 * 8 * K * 4 + (stream_x ? frag_bytes_per_block / 8 : 0));
         ring = r > ring ? r : ring;
     }
     if (units > kWsMaxUnits) return EXL3_E_SHAPE;
@@ -503,6 +531,11 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         const int red = (kWarps * 8 + pl.nt * 8) * 128 * 4 + (sk > 1 ? sk * rows * 128 * 4 : 0);
         pl.region_bytes = ring > red ? ring : red;
         // the activation fragments of as many 128-blocks at once as the rest of the CTA's shared memory holds
+        if (stream_x) {
+            max_slice = kBarBytes + pl.region_bytes <= kCtaSmemBytes ? max_nblk : 0;
+            if (max_slice || sk == 1) break;
+            continue;
+        }
         max_slice = (kCtaSmemBytes - kBarBytes - pl.region_bytes) / frag_bytes_per_block;
         if (max_slice >= (max_nblk < 2 ? max_nblk : 2) || sk == 1) break;     // fewer slices leave more room
     }
@@ -517,7 +550,7 @@ static int make_plan(const exl3_shard *sh, int n, int rows, int ic, GemvPlan &pl
         pl.xf_words += (long long)pl.kblocks * frag_bytes_per_block / 4;
     }
     pl.xf_blocks = max_nblk < max_slice ? max_nblk : max_slice;
-    pl.xf_bytes = pl.xf_blocks * frag_bytes_per_block;
+    pl.xf_bytes = stream_x ? 0 : pl.xf_blocks * frag_bytes_per_block;
     return EXL3_OK;
 }
 

@@ -148,17 +148,20 @@ def bench_had(rows, n, iters):
     return dict(kernel="had_r_128", rows=rows, n=n, us=round(t * 1e6, 1), GBs=round(rows * n * 4 / t / 1e9, 1))
 
 
-def bench_attn(batch, qh, kvh, ctx, iters, sdpa, page=0):
+def bench_attn(batch, qh, kvh, ctx, iters, sdpa, page=0, kv="fp16"):
     """Decode attention over `ctx` cached tokens; the caches are rotated so that every launch reads HBM."""
-    per = 2 * batch * kvh * ctx * 256 * 2
+    esize = 1 if kv == "fp8" else 2
+    per = 2 * batch * kvh * ctx * 256 * esize
     n = int(min(8, max(2, 400e6 // per + 1)))
     kcs = [torch.randn(batch, kvh, ctx, 256, device=DEV).half() for _ in range(n)]
     vcs = [torch.randn(batch, kvh, ctx, 256, device=DEV).half() for _ in range(n)]
+    if kv == "fp8":
+        kcs, vcs = [c.to(torch.float8_e4m3fn) for c in kcs], [c.to(torch.float8_e4m3fn) for c in vcs]
     q = torch.randn(batch, qh, 256, device=DEV).half()
     o = torch.empty_like(q)
     t = timeit(lambda i: _ext.decode_attn(q, kcs[i % n], vcs[i % n], ctx, out=o), max(iters, 2 * n), period=n)
     b = per + 2 * q.numel() * 2
-    r = dict(kernel="decode_attn", batch=batch, q_heads=qh, kv_heads=kvh, ctx=ctx, us=round(t * 1e6, 1),
+    r = dict(kernel="decode_attn", kv=kv, batch=batch, q_heads=qh, kv_heads=kvh, ctx=ctx, us=round(t * 1e6, 1),
              GBs=round(b / t / 1e9, 1))
     if page:
         # the same tokens in page pools [pages, kv_heads, page, 256], pages in shuffled order
@@ -169,17 +172,18 @@ def bench_attn(batch, qh, kvh, ctx, iters, sdpa, page=0):
         table = table.view(batch, npg)
 
         def pool(c):
-            pg = c.view(batch, kvh, npg, page, 256).permute(0, 2, 1, 3, 4).reshape(batch * npg, kvh, page, 256)
+            c8 = c.view(torch.uint8) if kv == "fp8" else c
+            pg = c8.view(batch, kvh, npg, page, 256).permute(0, 2, 1, 3, 4).reshape(batch * npg, kvh, page, 256)
             out = torch.empty_like(pg)
             out[table.view(-1).long()] = pg
-            return out
+            return out.view(c.dtype)
         kps, vps = [pool(c) for c in kcs], [pool(c) for c in vcs]
         tp = timeit(lambda i: _ext.decode_attn_paged(q, kps[i % n], vps[i % n], table, None, npg * page, out=o),
                     max(iters, 2 * n), period=n)
         same = bool(torch.equal(_ext.decode_attn_paged(q, kps[0], vps[0], table, None, npg * page),
                                 _ext.decode_attn(q, kcs[0], vcs[0], npg * page)))
         r.update(page=page, paged_us=round(tp * 1e6, 1), paged_GBs=round(b / tp / 1e9, 1), paged_equals_contiguous=same)
-    if sdpa:
+    if sdpa and kv == "fp16":
         import torch.nn.functional as F
         ts = timeit(lambda i: F.scaled_dot_product_attention(q.unsqueeze(2), kcs[i % n], vcs[i % n], enable_gqa=True),
                     max(iters, 2 * n), period=n)
@@ -232,6 +236,7 @@ def main():
     ap.add_argument("--qh", type=int, default=24)
     ap.add_argument("--kvh", type=int, default=4)
     ap.add_argument("--page", type=int, default=0, help="attn: also time the paged form with this page size (divides ctx)")
+    ap.add_argument("--kv", choices=["fp16", "fp8"], default="fp16", help="attn: cache element type")
     ap.add_argument("--sdpa", action="store_true", help="attn: also time torch's scaled_dot_product_attention")
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--graph", action="store_true", help="replay the launches from a CUDA graph")
@@ -256,7 +261,7 @@ def main():
     elif a.what == "had":
         out.append(bench_had(a.rows, a.ic, a.iters))
     elif a.what == "attn":
-        out.append(bench_attn(a.rows, a.qh, a.kvh, a.ctx, a.iters, a.sdpa, a.page))
+        out.append(bench_attn(a.rows, a.qh, a.kvh, a.ctx, a.iters, a.sdpa, a.page, a.kv))
     elif a.what == "decode_rate":
         out.extend(bench_decode_rate())
     elif a.what == "prefill":

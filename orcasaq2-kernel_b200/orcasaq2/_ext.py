@@ -95,6 +95,15 @@ def lib():
                 L.exl3_decode_attn_paged.restype = ci
                 L.exl3_rope_append.argtypes = [vp, ci, vp, vp, ci, vp, vp, ci, ci, ci, ci, ci, ll, ll, vp]
                 L.exl3_rope_append.restype = ci
+                L.exl3_decode_attn_fp8_workspace_bytes.restype = sz
+                L.exl3_decode_attn_fp8_workspace_bytes.argtypes = [ci, ci, ci, ci]
+                L.exl3_decode_attn_fp8.argtypes = [vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ll, ll, ll, ll, cf, cf, cf, vp]
+                L.exl3_decode_attn_fp8.restype = ci
+                L.exl3_decode_attn_paged_fp8.argtypes = [vp, vp, vp, vp, vp, vp, vp, sz, ci, ci, ci, ci, ci, ci, ci,
+                                                         ll, ll, ll, ll, ll, cf, cf, cf, vp]
+                L.exl3_decode_attn_paged_fp8.restype = ci
+                L.exl3_rope_append_fp8.argtypes = [vp, ci, vp, vp, ci, vp, vp, ci, ci, ci, ci, ci, ll, ll, cf, cf, vp]
+                L.exl3_rope_append_fp8.restype = ci
                 for name in ("exl3_reconstruct", "exl3_had_r_128", "exl3_gemv_grouped", "exl3_gemv",
                              "exl3_int8_embed", "exl3_int8_head"):
                     getattr(L, name).restype = ci
@@ -463,16 +472,28 @@ def gemm_tc_status() -> int:
 
 
 # --------------------------------------------------------------------------- decode attention
+FP8 = torch.float8_e4m3fn
+
+
+def _kv_dtype(q, k, v, names):
+    """fp16 query; caches both fp16 or both e4m3.  Returns True for an fp8 cache."""
+    for t, name in zip((q, k, v), names):
+        if not isinstance(t, torch.Tensor) or t.device.type != "cuda":
+            raise RuntimeError(f"{name} must be a CUDA tensor (this build has no CPU path)")
+    if q.dtype != torch.float16 or k.dtype != v.dtype or k.dtype not in (torch.float16, FP8):
+        raise RuntimeError(f"{names[0]} must be fp16, {names[1]} / {names[2]} both fp16 or both float8_e4m3fn")
+    return k.dtype == FP8
+
+
 def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, seq_len: int,
-                scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                scale: float | None = None, out: torch.Tensor | None = None, k_scale: float = 1.0,
+                v_scale: float = 1.0) -> torch.Tensor:
     """softmax(q K^T * scale) V for one query token per sequence.
 
     q [B, q_heads, 256] fp16 (last two dimensions contiguous); k_cache, v_cache [B, kv_heads, capacity, 256]
-    fp16 with contiguous rows, of which tokens 0 .. seq_len-1 are read; query head h uses KV head
-    h // (q_heads // kv_heads).  Returns [B, q_heads, 256] fp16."""
-    for t, name in ((q, "q"), (k_cache, "k_cache"), (v_cache, "v_cache")):
-        if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dtype != torch.float16:
-            raise RuntimeError(f"{name} must be a CUDA fp16 tensor (this build has no CPU path)")
+    fp16, or float8_e4m3fn holding value / k_scale and value / v_scale, with contiguous rows, of which tokens
+    0 .. seq_len-1 are read; query head h uses KV head h // (q_heads // kv_heads).  Returns [B, q_heads, 256] fp16."""
+    fp8 = _kv_dtype(q, k_cache, v_cache, ("q", "k_cache", "v_cache"))
     if q.dim() != 3 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape or v_cache.stride() != k_cache.stride():
         raise RuntimeError("decode_attn: q must be [B, heads, 256], the caches [B, kv_heads, capacity, 256] with equal strides")
     B, qh, hd = q.shape
@@ -485,23 +506,29 @@ def decode_attn(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, s
     elif out.shape != (B, qh, hd) or out.dtype != torch.float16 or out.stride(2) != 1 or out.stride(1) != hd:
         raise RuntimeError("decode_attn: out must be [B, heads, 256] fp16 with contiguous heads")
     L = lib()
-    need = L.exl3_decode_attn_workspace_bytes(B, qh, kvh, seq_len)
+    need = (L.exl3_decode_attn_fp8_workspace_bytes if fp8 else L.exl3_decode_attn_workspace_bytes)(B, qh, kvh, seq_len)
     ws = torch.empty((need,), dtype=torch.uint8, device=q.device) if need else None
-    _check(L.exl3_decode_attn(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                              ws.data_ptr() if ws is not None else None, need, B, qh, kvh, hd, int(seq_len),
-                              q.stride(0), out.stride(0), k_cache.stride(0), k_cache.stride(1),
-                              float(hd ** -0.5 if scale is None else scale), _stream(q)), "exl3_decode_attn")
+    args = (q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+            ws.data_ptr() if ws is not None else None, need, B, qh, kvh, hd, int(seq_len),
+            q.stride(0), out.stride(0), k_cache.stride(0), k_cache.stride(1),
+            float(hd ** -0.5 if scale is None else scale))
+    if fp8:
+        _check(L.exl3_decode_attn_fp8(*args, float(k_scale), float(v_scale), _stream(q)), "exl3_decode_attn_fp8")
+    else:
+        _check(L.exl3_decode_attn(*args, _stream(q)), "exl3_decode_attn")
     return out
 
 
 def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache: torch.Tensor,
-                v_cache: torch.Tensor, pos: int, q_heads: int) -> None:
+                v_cache: torch.Tensor, pos: int, q_heads: int, k_scale: float = 1.0, v_scale: float = 1.0) -> None:
     """Rotate the query and key heads of qkv [B, (q_heads + 2 kv_heads) * 256] in place (rotate-half form) and
     write the rotated keys and the values to k_cache / v_cache [B, kv_heads, capacity, 256] at token `pos`.
-    cos, sin: [128] fp16 (one position for all sequences) or [B, 128]."""
-    for t, name in ((qkv, "qkv"), (cos, "cos"), (sin, "sin"), (k_cache, "k_cache"), (v_cache, "v_cache")):
+    cos, sin: [128] fp16 (one position for all sequences) or [B, 128].  float8_e4m3fn caches receive
+    value / k_scale and value / v_scale."""
+    for t, name in ((qkv, "qkv"), (cos, "cos"), (sin, "sin")):
         if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dtype != torch.float16:
             raise RuntimeError(f"{name} must be a CUDA fp16 tensor (this build has no CPU path)")
+    fp8 = _kv_dtype(qkv, k_cache, v_cache, ("qkv", "k_cache", "v_cache"))
     if qkv.dim() != 2 or qkv.stride(1) != 1 or k_cache.dim() != 4 or v_cache.shape != k_cache.shape \
             or v_cache.stride() != k_cache.stride() or k_cache.stride(3) != 1 or k_cache.stride(2) != k_cache.shape[3]:
         raise RuntimeError("rope_append: qkv must be [B, n] with contiguous rows, the caches [B, kv_heads, capacity, 256]")
@@ -511,21 +538,22 @@ def rope_append(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, k_cache
     if cos.shape != sin.shape or cos.shape[-1] != hd // 2 or not cos.is_contiguous() or not sin.is_contiguous() \
             or (cos.dim() == 2 and cos.shape[0] != B) or cos.dim() > 2:
         raise RuntimeError("rope_append: cos / sin must be [128] or [B, 128], contiguous")
-    _check(lib().exl3_rope_append(qkv.data_ptr(), qkv.stride(0), cos.data_ptr(), sin.data_ptr(),
-                                  hd // 2 if cos.dim() == 2 else 0, k_cache.data_ptr(), v_cache.data_ptr(), B,
-                                  q_heads, kvh, hd, int(pos), k_cache.stride(0), k_cache.stride(1), _stream(qkv)),
-           "exl3_rope_append")
+    args = (qkv.data_ptr(), qkv.stride(0), cos.data_ptr(), sin.data_ptr(), hd // 2 if cos.dim() == 2 else 0,
+            k_cache.data_ptr(), v_cache.data_ptr(), B, q_heads, kvh, hd, int(pos), k_cache.stride(0), k_cache.stride(1))
+    if fp8:
+        _check(lib().exl3_rope_append_fp8(*args, float(k_scale), float(v_scale), _stream(qkv)), "exl3_rope_append_fp8")
+    else:
+        _check(lib().exl3_rope_append(*args, _stream(qkv)), "exl3_rope_append")
 
 
 def decode_attn_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, block_table: torch.Tensor,
                       seq_lens: torch.Tensor | None, max_seq_len: int, layout: str = "HND",
-                      scale: float | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+                      scale: float | None = None, out: torch.Tensor | None = None, k_scale: float = 1.0,
+                      v_scale: float = 1.0) -> torch.Tensor:
     """decode_attn over a paged cache.  k_pages / v_pages: [pages, kv_heads, page_size, 256] (layout "HND") or
-    [pages, page_size, kv_heads, 256] ("NHD"), fp16, rows contiguous; block_table int32 [B, >= ceil(max_seq_len /
-    page_size)]; seq_lens int32 [B] or None (every sequence has max_seq_len tokens)."""
-    for t, name in ((q, "q"), (k_pages, "k_pages"), (v_pages, "v_pages")):
-        if not isinstance(t, torch.Tensor) or t.device.type != "cuda" or t.dtype != torch.float16:
-            raise RuntimeError(f"{name} must be a CUDA fp16 tensor (this build has no CPU path)")
+    [pages, page_size, kv_heads, 256] ("NHD"), fp16 or float8_e4m3fn (value / scale), rows contiguous; block_table
+    int32 [B, >= ceil(max_seq_len / page_size)]; seq_lens int32 [B] or None (every sequence has max_seq_len tokens)."""
+    fp8 = _kv_dtype(q, k_pages, v_pages, ("q", "k_pages", "v_pages"))
     if layout not in ("HND", "NHD") or k_pages.dim() != 4 or v_pages.shape != k_pages.shape \
             or v_pages.stride() != k_pages.stride() or k_pages.stride(3) != 1:
         raise RuntimeError("decode_attn_paged: page pools must be 4-D with equal shapes and strides, layout HND or NHD")
@@ -545,13 +573,18 @@ def decode_attn_paged(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Ten
     elif out.shape != (B, qh, hd) or out.dtype != torch.float16 or out.stride(2) != 1 or out.stride(1) != hd:
         raise RuntimeError("decode_attn_paged: out must be [B, heads, 256] fp16 with contiguous heads")
     L = lib()
-    need = L.exl3_decode_attn_workspace_bytes(B, qh, kvh, int(max_seq_len))
+    need = (L.exl3_decode_attn_fp8_workspace_bytes if fp8 else L.exl3_decode_attn_workspace_bytes)(
+        B, qh, kvh, int(max_seq_len))
     ws = torch.empty((need,), dtype=torch.uint8, device=q.device) if need else None
-    _check(L.exl3_decode_attn_paged(q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
-                                    None if seq_lens is None else seq_lens.data_ptr(), out.data_ptr(),
-                                    ws.data_ptr() if ws is not None else None, need, B, qh, kvh, hd,
-                                    int(max_seq_len), page_size, block_table.stride(0) if B > 1 else block_table.shape[1],
-                                    q.stride(0), out.stride(0), k_pages.stride(0), k_pages.stride(hdim),
-                                    k_pages.stride(tdim), float(hd ** -0.5 if scale is None else scale), _stream(q)),
-           "exl3_decode_attn_paged")
+    args = (q.data_ptr(), k_pages.data_ptr(), v_pages.data_ptr(), block_table.data_ptr(),
+            None if seq_lens is None else seq_lens.data_ptr(), out.data_ptr(),
+            ws.data_ptr() if ws is not None else None, need, B, qh, kvh, hd,
+            int(max_seq_len), page_size, block_table.stride(0) if B > 1 else block_table.shape[1],
+            q.stride(0), out.stride(0), k_pages.stride(0), k_pages.stride(hdim),
+            k_pages.stride(tdim), float(hd ** -0.5 if scale is None else scale))
+    if fp8:
+        _check(L.exl3_decode_attn_paged_fp8(*args, float(k_scale), float(v_scale), _stream(q)),
+               "exl3_decode_attn_paged_fp8")
+    else:
+        _check(L.exl3_decode_attn_paged(*args, _stream(q)), "exl3_decode_attn_paged")
     return out

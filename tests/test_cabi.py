@@ -99,6 +99,27 @@ def test_decode_attn_argument_checks(lib):
     assert lib.exl3_decode_attn(*args(B=1, L=4096, hs=4096 * 256)) == -5                     # split, but no workspace
 
 
+def test_decode_attn_fp8_argument_checks(lib):
+    vp, ci, ll, cf = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float
+    lib.exl3_decode_attn_fp8_workspace_bytes.restype = ctypes.c_size_t
+    lib.exl3_decode_attn_fp8_workspace_bytes.argtypes = [ci] * 4
+    lib.exl3_decode_attn_fp8.argtypes = [vp] * 5 + [ctypes.c_size_t] + [ci] * 5 + [ll] * 4 + [cf, cf, cf, vp]
+    lib.exl3_rope_append_fp8.argtypes = [vp, ci, vp, vp, ci, vp, vp] + [ci] * 5 + [ll, ll, cf, cf, vp]
+    assert lib.exl3_decode_attn_fp8_workspace_bytes(1, 24, 4, 4096) > lib.exl3_decode_attn_workspace_bytes(1, 24, 4, 4096)
+    fake = vp(4096)
+    args = lambda **kw: [kw.get("q", fake), fake, fake, fake, None, 0, 512, 24, 4, kw.get("hd", 256), 64, 24 * 256,
+                         24 * 256, 4 * 64 * 256, kw.get("hs", 64 * 256), 0.0625, kw.get("ks", 1.0), kw.get("vs", 1.0), None]
+    assert lib.exl3_decode_attn_fp8(*args(q=None)) == -6
+    assert lib.exl3_decode_attn_fp8(*args(hd=128)) == -3
+    assert lib.exl3_decode_attn_fp8(*args(hs=64 * 256 + 8)) == -1             # byte strides must be multiples of 16
+    assert lib.exl3_decode_attn_fp8(*args(ks=0.0)) == -1
+    assert lib.exl3_decode_attn_fp8(*args(vs=-1.0)) == -1
+    assert lib.exl3_rope_append_fp8(fake, 32 * 256, fake, fake, 0, fake, fake, 1, 24, 4, 256, 3, 4 * 64 * 256, 64 * 256,
+                                    0.0, 1.0, None) == -1
+    assert lib.exl3_rope_append_fp8(fake, 32 * 256, fake, None, 0, fake, fake, 1, 24, 4, 256, 3, 4 * 64 * 256, 64 * 256,
+                                    1.0, 1.0, None) == -6
+
+
 def test_decode_attn_paged_argument_checks(lib):
     vp, ci, ll = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
     lib.exl3_decode_attn_paged.argtypes = [vp] * 7 + [ctypes.c_size_t] + [ci] * 7 + [ll] * 5 + [ctypes.c_float, vp]

@@ -166,3 +166,115 @@ def test_decode_attn_paged_rejects_bad_arguments(ext):
         ext.decode_attn_paged(q, kp, kp, table.long(), None, 64)
     with pytest.raises(RuntimeError):
         ext.decode_attn_paged(q, kp, kp, table, torch.zeros(3, device="cuda", dtype=torch.int32), 64)
+
+
+# --------------------------------------------------------------------------- fp8 (e4m3) caches
+def _quant(t, scale):
+    """What an fp8 cache holds for the values `t`: value / scale rounded to e4m3."""
+    return (t.float() / scale).to(torch.float8_e4m3fn)
+
+
+def _deq(t8, scale):
+    return (t8.float() * scale).half()          # exact: an e4m3 value times a power of two fits fp16
+
+
+@pytest.mark.parametrize("B,qh,kvh,seq_len,cap", [
+    (1, 24, 4, 4097, 4112),      # the 27B decoder at batch 1: many splits
+    (2, 24, 4, 1, 64),           # a single token
+    (3, 6, 1, 15, 16),           # less than one tile
+    (2, 12, 2, 17, 48),          # one tile and one token
+    (4, 3, 1, 1000, 1024),       # three query heads per KV head, ragged tail
+    (32, 24, 4, 513, 528),       # batch 32: few splits
+    (2, 8, 1, 333, 400),         # eight query heads on one KV head
+])
+def test_decode_attn_fp8_cache(ext, B, qh, kvh, seq_len, cap):
+    """fp8 cache against fp32 attention over the dequantised bytes (same tolerance as the fp16 kernel: the only
+    roundings are the fp16 probabilities and the fp16 output), and against the fp16 kernel on the dequantised
+    cache (same arithmetic, other summation order)."""
+    g = torch.Generator(device="cuda").manual_seed(B * 1000 + seq_len + 1)
+    ks, vs = 0.5, 2.0
+    q = torch.randn(B, qh, 256, device="cuda", generator=g).half()
+    k8 = _quant(torch.randn(B, kvh, cap, 256, device="cuda", generator=g), ks)
+    v8 = _quant(torch.randn(B, kvh, cap, 256, device="cuda", generator=g), vs)
+    k8.view(torch.uint8)[:, :, seq_len:] = 0x7F                       # NaN bytes beyond seq_len must not matter
+    v8.view(torch.uint8)[:, :, seq_len:] = 0x7F
+    out = ext.decode_attn(q, k8, v8, seq_len, k_scale=ks, v_scale=vs)
+    kd, vd = _deq(k8, ks), _deq(v8, vs)
+    _check(out, _ref(q, kd, vd, seq_len))
+    _check(out, ext.decode_attn(q, kd, vd, seq_len).float())
+    assert torch.equal(out, ext.decode_attn(q, k8, v8, seq_len, k_scale=ks, v_scale=vs))   # fixed summation order
+
+
+def test_decode_attn_fp8_every_dimension_lands_in_its_place(ext):
+    """One token, V = the dimension index pattern: the output must reproduce V exactly (softmax weight 1), which
+    pins the permuted accumulator -> dimension mapping; and a one-hot query picks single K dimensions."""
+    B, qh, kvh = 1, 8, 2
+    v = (torch.arange(256, device="cuda").float() % 15 - 7).view(1, 1, 1, 256).expand(B, kvh, 16, 256).contiguous()
+    v[:, 1] *= -1
+    k = torch.zeros(B, kvh, 16, 256, device="cuda")
+    q = torch.zeros(B, qh, 256, device="cuda").half()
+    out = ext.decode_attn(q, _quant(k, 1.0), _quant(v, 1.0), 1)
+    assert torch.equal(out[:, :4].float(), v[:, 0, 0].expand(B, 4, 256))
+    assert torch.equal(out[:, 4:].float(), v[:, 1, 0].expand(B, 4, 256))
+    # two tokens; K of token 1 is large in dimension d only; a query that is one-hot in d must pick token 1
+    for d in (0, 1, 2, 3, 5, 16, 17, 31, 100, 255):
+        k = torch.zeros(B, kvh, 16, 256, device="cuda")
+        k[:, :, 1, d] = 8.0
+        vv = torch.zeros(B, kvh, 16, 256, device="cuda")
+        vv[:, :, 1] = 1.0
+        q = torch.zeros(B, qh, 256, device="cuda")
+        q[:, :, d] = 16.0 * 16.0                                      # score 8 * 256 / 16 = 128: weight ~ 1
+        o = ext.decode_attn(q.half(), _quant(k, 1.0), _quant(vv, 1.0), 2)
+        assert torch.allclose(o.float(), torch.ones_like(o.float()), atol=1e-3), d
+        q = torch.zeros(B, qh, 256, device="cuda")
+        q[:, :, (d + 1) % 256] = 256.0                                # any other dimension: both tokens weigh 1/2
+        o = ext.decode_attn(q.half(), _quant(k, 1.0), _quant(vv, 1.0), 2)
+        assert torch.allclose(o.float(), torch.full_like(o.float(), 0.5), atol=1e-3), d
+
+
+@pytest.mark.parametrize("layout", ["HND", "NHD"])
+@pytest.mark.parametrize("B,qh,kvh,page,cap", [(1, 24, 4, 16, 2048), (3, 6, 1, 64, 512), (32, 12, 2, 32, 256)])
+def test_decode_attn_paged_fp8(ext, layout, B, qh, kvh, page, cap):
+    g = torch.Generator(device="cuda").manual_seed(B * 7 + page + 1)
+    ks, vs = 0.25, 1.0
+    q = torch.randn(B, qh, 256, device="cuda", generator=g).half()
+    kc = _deq(_quant(torch.randn(B, kvh, cap, 256, device="cuda", generator=g), ks), ks)
+    vc = _deq(_quant(torch.randn(B, kvh, cap, 256, device="cuda", generator=g), vs), vs)
+    kp, vp, table = _paginate(kc, vc, page, layout, g)               # fp16 pools with NaN in the unused pages
+    kp8, vp8 = _quant(kp, ks), _quant(vp, vs)
+    full = ext.decode_attn_paged(q, kp8, vp8, table, None, cap, layout=layout, k_scale=ks, v_scale=vs)
+    assert torch.equal(full, ext.decode_attn(q, _quant(kc, ks), _quant(vc, vs), cap, k_scale=ks, v_scale=vs))
+    lens = torch.randint(1, cap + 1, (B,), device="cuda", generator=g).to(torch.int32)
+    lens[0] = 1
+    table2 = table.clone()
+    for b in range(B):
+        table2[b, (int(lens[b]) + page - 1) // page:] = kp.shape[0] - 1
+    out = ext.decode_attn_paged(q, kp8, vp8, table2, lens, cap, layout=layout, k_scale=ks, v_scale=vs)
+    for b in range(B):
+        n = int(lens[b])
+        _check(out[b:b + 1], _ref(q[b:b + 1], kc[b:b + 1], vc[b:b + 1], n))
+
+
+@pytest.mark.parametrize("B,qh,kvh,per_seq", [(1, 24, 4, False), (5, 3, 1, True)])
+def test_rope_append_fp8(ext, B, qh, kvh, per_seq):
+    """fp8 append = the fp16 append's values divided by the scale and rounded to e4m3; the query is the same."""
+    g = torch.Generator(device="cuda").manual_seed(21 + B)
+    cap, pos, ks, vs = 48, 17, 0.5, 2.0
+    qkv = torch.randn(B, (qh + 2 * kvh) * 256, device="cuda", generator=g).half()
+    ang = torch.rand((B, 128) if per_seq else (128,), device="cuda", generator=g) * 6.28
+    cos, sin = torch.cos(ang).half(), torch.sin(ang).half()
+    k16 = torch.zeros(B, kvh, cap, 256, device="cuda", dtype=torch.half)
+    v16 = torch.zeros_like(k16)
+    q16 = qkv.clone()
+    ext.rope_append(q16, cos, sin, k16, v16, pos, qh)
+    k8 = torch.zeros(B, kvh, cap, 256, device="cuda", dtype=torch.uint8).view(torch.float8_e4m3fn)
+    v8 = torch.zeros(B, kvh, cap, 256, device="cuda", dtype=torch.uint8).view(torch.float8_e4m3fn)
+    q8 = qkv.clone()
+    ext.rope_append(q8, cos, sin, k8, v8, pos, qh, k_scale=ks, v_scale=vs)
+    assert torch.equal(q8, q16)
+    assert torch.equal(k8.view(torch.uint8), _quant(k16, ks).view(torch.uint8))
+    assert torch.equal(v8.view(torch.uint8), _quant(v16, vs).view(torch.uint8))
+    # a value beyond the e4m3 range saturates to +-448 instead of turning into NaN
+    big = torch.full_like(qkv, 1000.0)
+    ext.rope_append(big, torch.ones_like(cos), torch.zeros_like(sin), k8, v8, pos + 1, qh, k_scale=1.0, v_scale=1.0)
+    assert torch.all(v8[:, :, pos + 1].float() == 448.0) and torch.all(k8[:, :, pos + 1].float() == 448.0)

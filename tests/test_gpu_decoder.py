@@ -32,7 +32,11 @@ def _layer(co, x, shard):
     return R.layer_np(x.astype(np.float16), w, shard["suh"].cpu().numpy(), shard["svh"].cpu().numpy())
 
 
-def _oracle_step(co, model_cpu, table, scales, ids, ctx):
+def _e4m3(a):
+    return torch.from_numpy(np.asarray(a, np.float32)).to(torch.float8_e4m3fn).float().numpy().astype(np.float64)
+
+
+def _oracle_step(co, model_cpu, table, scales, ids, ctx, kv="fp16"):
     hd, qh, kvh = DIMS["hd"], DIMS["qh"], DIMS["kvh"]
     h = _f16(table[ids].astype(np.float64) * scales[ids][:, None])
     half = hd // 2
@@ -51,6 +55,8 @@ def _oracle_step(co, model_cpu, table, scales, ids, ctx):
         q = rope(y[:, :qh * hd].reshape(B, qh, hd))
         k = rope(y[:, qh * hd:(qh + kvh) * hd].reshape(B, kvh, hd))
         v = y[:, (qh + kvh) * hd:].reshape(B, kvh, hd)
+        if kv == "fp8":                                             # what an e4m3 cache (scale 1) keeps of the new token
+            k, v = _e4m3(k), _e4m3(v)
         K = np.concatenate([kc[:, :, :ctx], k[:, :, None]], 2)      # [B, kvh, ctx + 1, hd]
         V = np.concatenate([vc[:, :, :ctx], v[:, :, None]], 2)
         att = np.zeros((B, qh, hd))
@@ -70,12 +76,13 @@ def _oracle_step(co, model_cpu, table, scales, ids, ctx):
     return (x @ table.astype(np.float64).T) * scales[None, :]
 
 
-@pytest.mark.parametrize("attn", ["own", "sdpa"])
+@pytest.mark.parametrize("attn,kv", [("own", "fp16"), ("sdpa", "fp16"), ("own", "fp8")])
 @pytest.mark.parametrize("batch", [1, 9])
-def test_decoder_step_matches_oracle(ext, coracle, batch, attn):
+def test_decoder_step_matches_oracle(ext, coracle, batch, attn, kv):
     import bench_model as BM
     dev = torch.device("cuda", 0)
-    model, table, scales, _, _, qh, kvh = BM.build(0, 1, batch, CTX, dev, LAYERS, DIMS)
+    model, table, scales, _, _, qh, kvh = BM.build(0, 1, batch, CTX, dev, LAYERS, DIMS, kv=kv)
+    assert model[0][4].dtype == (torch.float8_e4m3fn if kv == "fp8" else torch.float16)
     assert (qh, kvh) == (DIMS["qh"], DIMS["kvh"]) and len(model) == LAYERS
     ids = torch.randint(0, DIMS["vocab"], (batch,), generator=torch.Generator().manual_seed(11)).to(dev)
     # the oracle's copy of the model, taken before the step appends to the caches
@@ -87,7 +94,7 @@ def test_decoder_step_matches_oracle(ext, coracle, batch, attn):
     torch.cuda.synchronize()
     assert ext.workspace_status(dev) == 0
     ref = _oracle_step(coracle, model_cpu, table.cpu().numpy(), scales.float().cpu().numpy().astype(np.float64),
-                       ids.cpu().numpy(), CTX)
+                       ids.cpu().numpy(), CTX, kv)
     got = logits.float().cpu().numpy().astype(np.float64)
     assert got.shape == ref.shape == (batch, DIMS["vocab"])
     rel = np.abs(got - ref).max() / np.abs(ref).max()
