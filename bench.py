@@ -658,7 +658,7 @@ def decoder_tok_s():
 
 # per-launch DRAM traffic of the gate_up kernel from ncu (dram__bytes_read.sum + write), keyed by
 # (rows, world); filled from the captures summarised under profiles/
-NCU_TRAFFIC_BYTES = {(1, 1): 67_521_280}     # profiles/gemv_kernel_gate_up_rows1.md: 67.03 MB read + 0.49 MB written
+NCU_TRAFFIC_BYTES = {(1, 1): 67_866_112, (16, 1): 68_354_816}     # profiles/gemv_kernel_gate_up_rows1.md: DRAM bytes read + written of one launch
 
 
 # ------------------------------------------------------------------------------------ CPU arms
