@@ -28,7 +28,7 @@ roofline      = the dominant kernel (gate_up grouped GEMV) alone, graph-replayed
                 one 5120->17408 shard at 2..6 bits per weight, 1 and 16 rows.
 
 decoder_27b = (N = 1 only, after the timed region, `--no-decoder` skips it) tokens/s of the random-init 27B
-          decoder of bench_model.py at batch 1 and 32 with a 4096-token cache, each run in a child
+          decoder of bench_model.py at batch 1 and 32 with a 4096-token cache (batch 32 also with an fp8 cache), each run in a child
           process; the second half of the headline metric, reported beside the GEMV figure and
           not part of `value`, `e2e` or `ms_per_step`; with the same decoder's token rate on the host
           cores extrapolated from per-layer CPU timings.
@@ -500,6 +500,15 @@ def run_gpu(args):
             tp_model = bench_model.run(bench_model.default_args(batch=64, ctx=8192, steps=10, warmup=2, allreduce=args.allreduce))
         except Exception as e:                                          # noqa: BLE001
             tp_model = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        torch.cuda.empty_cache()
+        try:                                                            # the same with an e4m3 KV cache (scale 1)
+            tp8 = bench_model.run(bench_model.default_args(batch=64, ctx=8192, steps=10, warmup=2, allreduce=args.allreduce,
+                                                           kv="fp8"))
+        except Exception as e:                                          # noqa: BLE001
+            tp8 = {"unavailable": f"{type(e).__name__}: {e}"[:200]}
+        if tp_model is not None and tp8 is not None:
+            tp_model["fp8_kv"] = {k: tp8[k] for k in ("value", "ms_per_step", "per_gpu_hbm_gbs", "status_word", "unavailable")
+                                  if k in tp8}
     if rank != 0:
         _leave(world)
         return
@@ -634,16 +643,16 @@ def roofline_by_k(torch, dist, _ext, dev, peak):
 
 def decoder_tok_s():
     """The second half of the headline metric, after the timed region and outside every figure above: the
-    random-init 27B decoder of bench_model.py at batch 1 and 32 (4096-token cache), each in a process of
-    its own.  Any failure or a run over its time limit is reported in place of the number; it never
+    random-init 27B decoder of bench_model.py at batch 1 and 32 (4096-token cache; batch 32 also with an e4m3
+    cache), each in a process of its own.  Any failure or a run over its time limit is reported in place of the number; it never
     fails the benchmark."""
     import subprocess
     out = {"unit": "tok/s", "ctx": 4096, "source": "bench_model.py (CUDA-graph replay, 64 layers)"}
     script = os.path.join(ROOT, "bench_model.py")
-    for batch in (1, 32):
-        key = f"bs{batch}"
+    for batch, kv in ((1, "fp16"), (32, "fp16"), (32, "fp8")):
+        key = f"bs{batch}" + ("" if kv == "fp16" else "_fp8_kv")
         try:
-            p = subprocess.run([sys.executable, script, "--batch", str(batch), "--ctx", "4096", "--steps", "10"],
+            p = subprocess.run([sys.executable, script, "--batch", str(batch), "--ctx", "4096", "--steps", "10", "--kv", kv],
                                capture_output=True, text=True, timeout=180)
             last = [ln for ln in p.stdout.splitlines() if ln.startswith("{")]
             if p.returncode != 0 or not last:
