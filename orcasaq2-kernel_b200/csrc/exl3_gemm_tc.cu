@@ -393,6 +393,312 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Many rows (>= kDenseMinRows): decode ONCE, then a dense tcgen05 GEMM on CTA pairs.
+//
+// With thousands of rows the in-kernel decode above repeats the integer decode of every weight once per 512 rows
+// and its sixteen decode warps cannot keep the tensor pipe fed (measured: the MMA-issuing thread waits for a
+// decoded tile in every step).  So from kDenseMinRows rows the weight is rebuilt once, transposed (Wt[oc][ic], the
+// K-major form tcgen05 wants), and this kernel multiplies it with the rotated activations:
+//     Yt[oc][tokens] += Wt[oc][ic] . Xh[tokens][ic]^T        (fp16 in, fp32 in tensor memory, fp16 out)
+// One MMA spans two SMs (tcgen05.mma.cta_group::2, M = 256 output channels, N = 256 tokens): each CTA of the pair
+// loads its own 128 rows of Wt and HALF of the token tile (128 of the 256 rows), so the token tile crosses
+// L2 -> shared memory once per 256 output channels and each SM reads 8 KB of operands per MMA instead of 12.
+// All loads are plain per-CTA 2-D TMA loads of this GPU's own memory (no multicast).  Warps: 0 = producer (one
+// lane: three TMA loads per stage on one barrier), 1 = MMA issue in the first CTA of the pair / relay in the
+// second (tells the first CTA when this CTA's stage has landed; the first CTA's commits arrive on the barriers of
+// both), 2..9 = epilogue (tcgen05.ld of their lane quadrant, fp16 stores).  Four stages of 48 KB.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// Arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster.  Default semantics (release at
+// CTA scope): what this announces was written by the async proxy and observed complete inside the announcing CTA
+// before the arrive is issued; a cluster-scope release here costs about a microsecond per arrive (measured).
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t cta) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_bar), "r"(cta));
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+}
+__device__ __forceinline__ void umma2(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a), "l"(b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair
+__device__ __forceinline__ void umma2_commit(uint32_t bar) {
+    const unsigned short mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"(mask) : "memory");
+}
+// kind::f16, fp16 A and B (both K-major), fp32 accumulate, M = 256 (128 per CTA), N = n
+__device__ __forceinline__ uint32_t umma2_idesc(int n) {
+    return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+constexpr int kDenseMinRows = 1024;
+constexpr int kDenseFoldRows = 4096;                                  // from here the output rotation is folded into the rebuilt weight
+constexpr int kDenseStages = 4;
+constexpr int kDenseBand = 8;                                          // channel pairs (of 256 channels) per L2 band
+constexpr int kDenseHalfBytes = (kBN / 2) * kBK * 2;                   // this CTA's 128 token rows of one accumulator: 16 KB
+constexpr int kDenseStageBytes = kABytes + kMaxHalves * kDenseHalfBytes;   // 48 KB
+constexpr int kDenseEpiWarps = 8;
+constexpr int kDenseThreads = 32 * (2 + kDenseEpiWarps);
+constexpr size_t kDenseSmem = (size_t)kDenseStages * kDenseStageBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+
+struct DenseParams {
+    __half *y;             // [tokens][ldy]
+    int tokens, ic, oc, ldy;
+    int tile_tokens;       // tokens per CTA: 512 (two accumulators) or 256
+};
+struct DenseBarriers {
+    uint64_t full[kDenseStages], empty[kDenseStages], peer_full[kDenseStages];
+    uint64_t acc_full;
+    uint32_t tmem_base;
+};
+
+__global__ void __launch_bounds__(kDenseThreads, 1)
+gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                       const DenseParams P) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char *smem_raw = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);   // swizzled tiles: 1024-byte alignment
+    DenseBarriers &S = *reinterpret_cast<DenseBarriers *>(smem_raw + (size_t)kDenseStages * kDenseStageBytes);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t crank = cluster_ctarank();                     // 0 issues the MMAs of the pair
+    // Launch order -> tile: pairs that run at the same time should share operands in L2.  In launch order (x
+    // fastest) one wave would sweep ALL output channels for one token tile, streaming the whole rebuilt weight from
+    // HBM once per token tile; instead bands of kDenseBand channel pairs are walked token tile by token tile, so a
+    // band's weight rows stay in L2 while the token tiles pass.
+    int ob, ty;
+    {
+        const int npx = gridDim.x >> 1, nty = gridDim.y;
+        const int L = blockIdx.y * npx + (blockIdx.x >> 1);
+        const int full_bands = npx / kDenseBand;
+        const int in_full = full_bands * kDenseBand * nty;
+        int px;
+        if (L < in_full) {
+            const int band = L / (kDenseBand * nty), r = L - band * (kDenseBand * nty);
+            px = band * kDenseBand + r % kDenseBand;
+            ty = r / kDenseBand;
+        } else {                                                  // the last, narrower band
+            const int w = npx - full_bands * kDenseBand, r = L - in_full;
+            px = full_bands * kDenseBand + r % w;
+            ty = r / w;
+        }
+        ob = 2 * px + (int)crank;                                 // 128-channel block of outputs
+    }
+    const int tok0 = ty * P.tile_tokens;
+    const int tok_here = min(P.tokens - tok0, P.tile_tokens);
+    const int halves = tok_here > kBN ? 2 : 1;
+    const int nsteps = P.ic / kBK;
+    constexpr uint32_t kTmemCols = kBN * kMaxHalves;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kDenseStages; ++s) {
+            mbar_init(s32(&S.full[s]), 1);
+            mbar_init(s32(&S.empty[s]), 1);
+            mbar_init(s32(&S.peer_full[s]), 1);
+        }
+        mbar_init(s32(&S.acc_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {   // tensor memory of the pair: one warp of each CTA, together
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(&S.tmem_base)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                  // the other CTA's barriers exist before anything is signalled across
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = S.tmem_base;
+
+    if (warp == 0) {
+        // ---------------- producer: Wt rows of this CTA, and this CTA's half of each 256-token tile
+        if (lane == 0) {
+            bool ok = true;
+            Cursor c(0, kDenseStages);
+            for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
+                if (c.wrapped) ok = mbar_wait(s32(&S.empty[c.idx]), c.phase ^ 1u, 20);
+                if (!ok) break;
+                const uint32_t bar = s32(&S.full[c.idx]);
+                const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
+                mbar_expect_tx(bar, kABytes + halves * kDenseHalfBytes);
+                tma_2d(st, &wmap, s * kBK, ob * kBM, bar);
+                for (int h = 0; h < halves; ++h)     // token rows out of range arrive as zeros
+                    tma_2d(st + kABytes + h * kDenseHalfBytes, &xmap, s * kBK, tok0 + h * kBN + (int)crank * (kBN / 2), bar);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && crank != 0) {
+            // ---------------- second CTA: tell the first when a stage has landed here
+            bool ok = true;
+            Cursor c(0, kDenseStages);
+            for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
+                ok = mbar_wait(s32(&S.full[c.idx]), c.phase);
+                if (ok) mbar_arrive_remote(s32(&S.peer_full[c.idx]), 0);
+            }
+        } else if (lane == 0) {
+            // ---------------- first CTA: MMA issue for the pair
+            bool ok = true;
+            const uint32_t idesc = umma2_idesc(kBN);
+            Cursor c(0, kDenseStages);
+            for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
+                ok = mbar_wait(s32(&S.full[c.idx]), c.phase);
+                if (ok) ok = mbar_wait(s32(&S.peer_full[c.idx]), c.phase);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t a0 = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
+                for (int h = 0; h < halves; ++h) {
+                    const uint32_t b0 = a0 + kABytes + h * kDenseHalfBytes;
+#pragma unroll
+                    for (int k = 0; k < kBK / 16; ++k)
+                        umma2(tmem + h * kBN, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (s | k) ? 1u : 0u);
+                }
+                umma2_commit(s32(&S.empty[c.idx]));      // both CTAs' stage is free once these MMAs have read it
+            }
+            umma2_commit(s32(&S.acc_full));
+        }
+    } else {
+        // ---------------- epilogue: TMEM -> fp16 -> y[token][oc]
+        const bool ok = mbar_wait(s32(&S.acc_full), 0, 200);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
+        const int oc_row = ob * kBM + 32 * quad + lane;
+        const int col_part = (warp - 2) >> 2;                       // the two warps of a quadrant split the columns
+        for (int h = 0; h < halves; ++h) {
+            const int ncols = min(kBN, tok_here - h * kBN);
+            for (int c0 = col_part * 32; c0 < ncols; c0 += 64) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(h * kBN + c0);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (ok) {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j)
+                        if (c0 + j < ncols)
+                            P.y[(size_t)(tok0 + h * kBN + c0 + j) * P.ldy + oc_row] = __float2half_rn(__uint_as_float(v[j]));
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                  // neither CTA leaves (or frees tensor memory) while the other may still use it
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+// Wt[oc][ic'] = svh[oc] * (H128 over each block of 128 output channels of the decoded weight) / sqrt(128), transposed
+// (ic' = the permuted order of the rotated activations).  Rebuilding the weight once per call leaves room to fold
+// the layer's OUTPUT rotation and signs into it:  H (W^T xh) = (H W^T) xh,  so the GEMM's epilogue writes the final
+// result and no pass over the [tokens][oc] output follows.  One CTA = 128 output channels x 64 input channels: warp w
+// decodes the four tiles (lane = 8*tile + chunk) of output tile w that follow each other along the input
+// dimension and stages them transposed in shared memory; then the CTA multiplies the block by the 128 x 128 sign
+// matrix on the tensor cores (mma.sync, fp32 accumulation: exact), scales, rounds to fp16 ONCE, and writes 128 rows of 64 contiguous input channels (128 bytes) with 16-byte stores.
+constexpr int kRecTPitch = 72;
+template <int K, bool FOLD>
+__global__ void __launch_bounds__(256)
+reconstruct_t_kernel(const uint32_t *__restrict__ trellis, const __half *__restrict__ svh, __half *__restrict__ wt,
+                     int tiles_j, int ic) {
+    __shared__ __align__(16) __half stage[8][16][kRecTPitch];       // [output tile][output channel][input channel]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // A fragments of the sign matrix for this warp's 16 output rows: H[r][c] = (-1)^popcount(r & c), generated once
+    uint32_t afr[8][4];
+#pragma unroll
+    for (int kt = 0; kt < 8; ++kt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int r = 16 * warp + (lane >> 2) + (e & 1) * 8, c = 16 * kt + 2 * (lane & 3) + (e >> 1) * 8;
+            const uint32_t lo = (__popc(r & c) & 1) ? 0xBC00u : 0x3C00u;
+            const uint32_t hi = (__popc(r & (c + 1)) & 1) ? 0xBC00u : 0x3C00u;
+            afr[kt][e] = lo | (hi << 16);
+        }
+    for (int cy = blockIdx.y; cy < ic / 64; cy += gridDim.y) {      // 64 input channels per pass
+    {
+        const int u = lane >> 3, c = lane & 7;
+        const int tj = blockIdx.x * 8 + warp;                       // oc is a multiple of 128: always in range
+        const int ti = cy * 4 + u;
+        uint32_t wd[K + 1];
+        const uint32_t *src = trellis + ((size_t)ti * tiles_j + tj) * (size_t)(8 * K) + c * K;
+#pragma unroll
+        for (int k = 0; k < K; ++k) wd[k] = __ldg(src + k);
+        wd[K] = __shfl_sync(0xffffffffu, wd[0], (lane & 24) | ((c + 1) & 7));
+        uint32_t z[32];
+        decode_chunk<K>(wd, z);
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+            // the K order inside a 16-channel tile is the one xh_permute_kernel writes: channel 8b + 4h + q at 4q + 2b + h
+            const int r = tile_row(c, i);
+            stage[warp][tile_col(c, i)][16 * u + 4 * (r & 3) + 2 * (r >> 3) + ((r >> 2) & 1)] = codeword_to_half(z[i]);
+        }
+    }
+    __syncthreads();
+    if constexpr (FOLD) {
+        // H (128 x 128, entries +-1) times the staged block (128 output channels x 64 input channels) on the tensor
+        // cores: warp w produces output rows 16w .. 16w+15; the staged block is the B operand through transposing
+        // ldmatrix loads.
+        const int g = lane >> 2, q = lane & 3;
+        float acc[8][4];
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[nt][e] = 0.f;
+        const int lj = lane >> 3, lr = lane & 7;
+#pragma unroll
+        for (int kt = 0; kt < 8; ++kt) {
+            const uint32_t (&a)[4] = afr[kt];
+#pragma unroll
+            for (int np = 0; np < 4; ++np) {
+                const int k = 16 * kt + (lj & 1) * 8 + lr, n0 = 16 * np + (lj >> 1) * 8;
+                uint32_t b[4];
+                asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                             : "=r"(b[0]), "=r"(b[1]), "=r"(b[2]), "=r"(b[3]) : "r"(s32(&stage[k >> 4][k & 15][n0])));
+#pragma unroll
+                for (int h = 0; h < 2; ++h)
+                    asm volatile(
+                        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                        : "+f"(acc[2 * np + h][0]), "+f"(acc[2 * np + h][1]), "+f"(acc[2 * np + h][2]), "+f"(acc[2 * np + h][3])
+                        : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[2 * h]), "r"(b[2 * h + 1]));
+            }
+        }
+        __syncthreads();                                            // every warp has read the whole block
+        const float s0 = kHadScale * __half2float(__ldg(svh + (size_t)blockIdx.x * 128 + 16 * warp + g));
+        const float s1 = kHadScale * __half2float(__ldg(svh + (size_t)blockIdx.x * 128 + 16 * warp + g + 8));
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt) {
+            *reinterpret_cast<__half2 *>(&stage[warp][g][8 * nt + 2 * q]) = __floats2half2_rn(acc[nt][0] * s0, acc[nt][1] * s0);
+            *reinterpret_cast<__half2 *>(&stage[warp][g + 8][8 * nt + 2 * q]) = __floats2half2_rn(acc[nt][2] * s1, acc[nt][3] * s1);
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int it = 0; it < 4; ++it) {
+        const int idx = it * 32 + lane;
+        const int r = idx >> 3, seg = idx & 7;
+        const uint4 val = *reinterpret_cast<const uint4 *>(&stage[warp][r][seg * 8]);
+        *reinterpret_cast<uint4 *>(wt + (size_t)(128 * blockIdx.x + 16 * warp + r) * ic + 64 * cy + seg * 8) = val;
+    }
+    __syncthreads();                                                // the block is re-staged by the next pass
+    }
+}
+
 // The elementwise neighbours of the layer that the pre-pass can absorb (see exl3_gemv_fusion).
 struct XhFusion {
     int in_mode;            // 0 plain, 1 RMSNorm, 2 silu(x[:, :ic]) * x[:, ic:]
@@ -696,11 +1002,48 @@ static int choose_splitk(int rows, int ic, int oc) {
     return sk < 1 ? 1 : sk;
 }
 static size_t xh_bytes(int rows, int ic) { return (((size_t)rows * ic * 2) + 255) & ~(size_t)255; }
+// the decode-once route: enough rows to amortise rebuilding the weight, and output blocks that pair up
+static bool use_dense(int rows, int oc) { return rows >= kDenseMinRows && ((oc / kBM) & 1) == 0; }
+
+template <int K>
+static int launch_reconstruct_t(const void *trellis, const void *svh, void *wt, int ic, int oc, bool fold, cudaStream_t st) {
+    const int tiles_j = oc / 16;
+    dim3 grid(oc / 128, (ic / 64 + 3) / 4);                          // four passes per CTA: the sign fragments are reused
+    if (fold)
+        reconstruct_t_kernel<K, true><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(trellis), static_cast<const __half *>(svh),
+                                                            static_cast<__half *>(wt), tiles_j, ic);
+    else
+        reconstruct_t_kernel<K, false><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(trellis), static_cast<const __half *>(svh),
+                                                             static_cast<__half *>(wt), tiles_j, ic);
+    return launch_status();
+}
+
+static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, const DenseParams &P, cudaStream_t st) {
+    if (cudaFuncSetAttribute(gemm_dense_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem) != cudaSuccess) {
+        cudaGetLastError();
+        return EXL3_E_LAUNCH;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(P.oc / kBM, (P.tokens + P.tile_tokens - 1) / P.tile_tokens, 1);
+    cfg.blockDim = dim3(kDenseThreads);
+    cfg.dynamicSmemBytes = kDenseSmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;                 // the two CTAs of a pair
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, gemm_dense_pair_kernel, wmap, xmap, P) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    return launch_status();
+}
 } }
 
 extern "C" size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc) {
     if (rows < 1 || ic <= 0 || oc <= 0) return 0;
     if (exl3::ts::eligible(rows, ic, oc)) return exl3::ts::scratch_bytes(rows, ic, oc);
+    if (exl3::tc::use_dense(rows, oc)) return exl3::tc::xh_bytes(rows, ic) + (size_t)ic * oc * 2;   // + the rebuilt weight
     const int sk = exl3::tc::choose_splitk(rows, ic, oc);
     return exl3::tc::xh_bytes(rows, ic) + (sk > 1 ? (size_t)sk * rows * oc * 4 : 0);
 }
@@ -796,6 +1139,58 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
             return EXL3_E_LAUNCH;
         }
         return EXL3_OK;
+    }
+    if (use_dense(rows, oc)) {
+        // ---- many rows: rotate the activations, rebuild the weight once (transposed, with the output rotation and
+        // signs folded in), dense tcgen05 GEMM on CTA pairs whose epilogue writes the final result
+        // Folding costs a fixed ~80 us per call for a 5120 x 17408 weight (128 x 128 sign-matrix products on the
+        // legacy tensor path), the separate output rotation ~13 us per 1024 rows of that width: fold from 4096 rows.
+        const bool fold = rows >= kDenseFoldRows;
+        if (residual || (!fold && ldy != oc)) return EXL3_E_UNSUPPORTED;
+        if (oc / 128 > 65535 || ic / 64 > 65535 || (rows + 511) / 512 > 65535) return EXL3_E_SHAPE;
+        __half *xh = static_cast<__half *>(scratch);
+        __half *wt = reinterpret_cast<__half *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic));
+        const long long nblocks = (long long)rows * (ic / 128);
+        const unsigned g1 = (unsigned)((nblocks + 7) / 8);
+        if (x_is_bf16)
+            xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F);
+        else
+            xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F);
+        if (cudaGetLastError() != cudaSuccess) return EXL3_E_LAUNCH;
+        int rc;
+        switch (K) {
+            case 1: rc = launch_reconstruct_t<1>(trellis, svh, wt, ic, oc, fold, st); break;
+            case 2: rc = launch_reconstruct_t<2>(trellis, svh, wt, ic, oc, fold, st); break;
+            case 3: rc = launch_reconstruct_t<3>(trellis, svh, wt, ic, oc, fold, st); break;
+            case 4: rc = launch_reconstruct_t<4>(trellis, svh, wt, ic, oc, fold, st); break;
+            case 5: rc = launch_reconstruct_t<5>(trellis, svh, wt, ic, oc, fold, st); break;
+            case 6: rc = launch_reconstruct_t<6>(trellis, svh, wt, ic, oc, fold, st); break;
+            case 7: rc = launch_reconstruct_t<7>(trellis, svh, wt, ic, oc, fold, st); break;
+            default: rc = launch_reconstruct_t<8>(trellis, svh, wt, ic, oc, fold, st); break;
+        }
+        if (rc != EXL3_OK) return rc;
+        CUtensorMap wmap, xmap;
+        const cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)(kBN / 2)};
+        const cuuint32_t estr[2] = {1, 1};
+        const cuuint64_t gstr[1] = {(cuuint64_t)ic * 2};
+        const cuuint64_t wdim[2] = {(cuuint64_t)ic, (cuuint64_t)oc};
+        const cuuint64_t xdim[2] = {(cuuint64_t)ic, (cuuint64_t)rows};
+        if (enc(&wmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, wt, wdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS ||
+            enc(&xmap, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, xh, xdim, gstr, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return EXL3_E_LAUNCH;
+        DenseParams D;
+        D.y = static_cast<__half *>(y);
+        D.tokens = rows; D.ic = ic; D.oc = oc; D.ldy = ldy;
+        // 512 tokens per CTA.  256-token tiles (twice as many, shorter CTAs) were measured where they fill the last
+        // wave better (17408 -> 5120): slower all the same, 725 against 747 and 936 against 1085 TFLOP/s at 2048 and
+        // 8192 rows: a weight tile then serves four MMAs instead of eight and L2 -> shared-memory traffic limits.
+        D.tile_tokens = kBN * kMaxHalves;
+        if ((rows + D.tile_tokens - 1) / D.tile_tokens > 65535) return EXL3_E_SHAPE;
+        rc = launch_dense(wmap, xmap, D, st);
+        if (rc != EXL3_OK || fold) return rc;
+        return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
     }
     const int splitk = choose_splitk(rows, ic, oc);
     // the unsplit shared-memory kernel writes y itself and rotates it in place: no pitch, no residual

@@ -102,6 +102,43 @@ def test_single_rank_and_argument_checks(ext):
         L.exl3_comm_free(buf)
 
 
+@pytest.mark.parametrize("world", [3, 4, 8])
+@pytest.mark.parametrize("n", [5120, 48 * 5120])
+def test_more_ranks_played_in_turn(ext, world, n):
+    """The same on one GPU with 3, 4 and 8 ranks (both forms of the exchange): ranks world-1 .. 1 go first and give
+    up (each has published its partial and signalled everybody), rank 0 then finds everything and completes, and
+    the others complete when called again.  Every rank must produce the same bytes."""
+    from orcasaq2 import comm
+    L = _lib(ext)
+    nbytes = L.exl3_allreduce_buffer_bytes(64 * 5120)
+    bufs = [_alloc(L, nbytes) for _ in range(world)]
+    ptrs = (ctypes.c_void_p * 8)(*bufs)
+    g = torch.Generator().manual_seed(n + world)
+    p = [torch.randn((n,), generator=g).half().cuda() for _ in range(world)]
+    want = comm.allreduce_reference(p)
+    outs = [torch.full((n,), 7.0, dtype=torch.half, device="cuda") for _ in range(world)]
+    try:
+        for gen in range(3):                                              # three generations: both slots and a reuse
+            for r in range(world - 1, 0, -1):
+                assert _call(L, ptrs, r, world, nbytes, p[r], outs[r], 500) == 0
+            torch.cuda.synchronize()
+            assert all(torch.all(o == 7.0) for o in outs[1:])             # nobody could finish yet
+            assert all(_status(L, b) != 0 for b in bufs[1:]) and _status(L, bufs[0]) == 0
+            for r in range(world):
+                assert _call(L, ptrs, r, world, nbytes, p[r], outs[r], 1 << 20) == 0
+            torch.cuda.synchronize()
+            for o in outs:
+                assert torch.equal(o, want)
+            p = [(t.float() * 0.75 + 0.125 * (gen + 1)).half() for t in p]
+            want = comm.allreduce_reference(p)
+            for o in outs:
+                o.fill_(7.0)
+    finally:
+        torch.cuda.synchronize()
+        for b_ in bufs:
+            L.exl3_comm_free(b_)
+
+
 _CHILD = r"""
 import os, sys, torch, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])

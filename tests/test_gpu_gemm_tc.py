@@ -49,6 +49,11 @@ def test_gemm_tmem_operand_path_vs_oracle(ext, coracle, K, rows, ic, oc):
 @pytest.mark.parametrize("rows,ic,oc,K,dtype", [
     (32, 5120, 1024, 3, torch.float16), (64, 17408, 512, 4, torch.bfloat16), (128, 2048, 5120, 5, torch.float16),
     (512, 5120, 1024, 3, torch.bfloat16), (700, 2048, 5120, 4, torch.float16), (2048, 1024, 2048, 4, torch.bfloat16),
+    # from 1024 rows CTA pairs (tcgen05.mma.cta_group::2) when the number of 128-channel output blocks is even:
+    # full tiles, a last tile of one ragged half (the second CTA's token rows all out of range), a last tile with a
+    # ragged second half, split input dimension; and an odd number of output blocks, which stays on single CTAs
+    (1024, 512, 256, 3, torch.float16), (1100, 256, 512, 5, torch.float16), (1500, 384, 256, 2, torch.bfloat16),
+    (1024, 4096, 256, 4, torch.float16), (1300, 256, 384, 6, torch.float16), (4096, 512, 1024, 3, torch.float16),
 ])
 def test_gemm_tc_vs_reconstruct_route(ext, rows, ic, oc, K, dtype):
     """Larger shapes against reconstruct + dense matmul on the GPU (the reference's own route)."""
