@@ -558,8 +558,9 @@ def run_gpu(args):
 
 def prefill_block(torch, _ext, dev):
     """BASELINE config 3: M tokens x (5120 -> 17408 at 3 bpw, 17408 -> 5120 at 4 bpw), bf16 activations: TFLOPS of the
-    in-kernel-decode tcgen05 path (exl3_gemm_tc) and of the reference's own route for many rows (rotate, rebuild
-    the weight, library GEMM, rotate back: orcasaq2/ops.py:50-59), CUDA events over 8 calls after 2 warm-ups."""
+    library's tcgen05 path (exl3_gemm_tc: in-kernel decode up to 1023 rows; from 1024 rows the weight is rebuilt once
+    and a dense GEMM runs on CTA pairs) and of the reference's own route for many rows with a library GEMM (rotate,
+    rebuild the weight, torch.matmul, rotate back: orcasaq2/ops.py:50-59), CUDA events over 8 calls after 2 warm-ups."""
     peaks = {"burst": 1679.6, "sustained": 1385.7}
     try:
         mp = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))
@@ -598,10 +599,11 @@ def prefill_block(torch, _ext, dev):
             t_rt = timed(route)
             fl = 2.0 * m * ic * oc
             out["cases"].append({"shape": f"{ic}->{oc} @{K}bpw", "M": m,
-                                 "tcgen05_decode_gemm_tflops": round(fl / t_tc / 1e12, 1),
+                                 "tcgen05_tflops": round(fl / t_tc / 1e12, 1),
                                  "tcgen05_frac_of_burst_peak": round(fl / t_tc / 1e12 / peaks["burst"], 3),
                                  "rotate_reconstruct_library_gemm_tflops": round(fl / t_rt / 1e12, 1),
-                                 "plugin_dispatch": "tcgen05" if m <= 1023 else "rotate + reconstruct + library GEMM"})
+                                 "plugin_dispatch": "tcgen05: in-kernel decode" if m <= 1023 else
+                                 "tcgen05: decode once + dense GEMM on CTA pairs"})
             del x, y
         del sh
         torch.cuda.empty_cache()

@@ -1145,8 +1145,9 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         // signs folded in), dense tcgen05 GEMM on CTA pairs whose epilogue writes the final result
         // Folding costs a fixed ~80 us per call for a 5120 x 17408 weight (128 x 128 sign-matrix products on the
         // legacy tensor path), the separate output rotation ~13 us per 1024 rows of that width: fold from 4096 rows.
-        const bool fold = rows >= kDenseFoldRows;
-        if (residual || (!fold && ldy != oc)) return EXL3_E_UNSUPPORTED;
+        // A pitched output (a column block of a fused layer's result) cannot be rotated in place afterwards: fold.
+        const bool fold = rows >= kDenseFoldRows || ldy != oc;
+        if (residual) return EXL3_E_UNSUPPORTED;
         if (oc / 128 > 65535 || ic / 64 > 65535 || (rows + 511) / 512 > 65535) return EXL3_E_SHAPE;
         __half *xh = static_cast<__half *>(scratch);
         __half *wt = reinterpret_cast<__half *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic));

@@ -6,10 +6,12 @@ used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, wr
 into the concatenated output.
 
 Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
-streaming of the packed trellis; a single shard moves to the tensor-memory kernel below from 9 rows).  17 rows up to TC_MAX_ROWS: `exl3_gemm_tc`, one pass over the
-packed weights with no dense copy in memory -- up to 128 rows the decoded weights go from registers into tensor memory and are the A operand of
-tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  Above that the reference's own route wins on B200 and is kept: rotate, rebuild the
-weight once into a scratch buffer, dense library GEMM, rotate back.  GEMM_MAX_ROWS keeps the
+streaming of the packed trellis; a single shard moves to the tensor-memory kernel below from 9 rows).  From 17 rows: `exl3_gemm_tc`.  Up to 1023 rows that is
+one pass over the packed weights with no dense copy in memory -- up to 128 rows the decoded weights go from registers into tensor memory and are the A
+operand of tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  From 1024 rows the library decodes once (the reference's own idea
+for many rows, ops.py:50-59: rotate, rebuild the weight into scratch, dense GEMM, rotate back) and runs its own dense tcgen05 GEMM on CTA pairs, with the
+output rotation folded into the rebuilt weight from 4096 rows.  The reference's route with a library GEMM (`_dense_path`) remains for shapes the pair kernel
+does not take (an odd number of 128-channel output blocks) and behind ORCA_EXL3_TC_MAX_ROWS.  GEMM_MAX_ROWS keeps the
 reference's name and default; it is the bound up to which the packed trellis is read directly
 when the tcgen05 path is switched off (ORCA_EXL3_TC=0).
 """
@@ -27,7 +29,13 @@ PACK_LAYOUT = "orcasaq2-b200-3inst-v1"
 
 GEMM_MAX_ROWS = int(os.environ.get("ORCA_EXL3_GEMM_MAX_ROWS", "144"))
 USE_TC = os.environ.get("ORCA_EXL3_TC", "1") != "0"
-TC_MAX_ROWS = int(os.environ.get("ORCA_EXL3_TC_MAX_ROWS", "1023"))
+TC_MAX_ROWS = int(os.environ.get("ORCA_EXL3_TC_MAX_ROWS", str(1 << 30)))
+TC_PAIR_MIN_ROWS = 1024          # from here exl3_gemm_tc wants an even number of 128-channel output blocks
+
+
+def _tc_takes(rows: int, oc: int) -> bool:
+    """Whether exl3_gemm_tc is the route for this many rows of a shard with `oc` outputs."""
+    return USE_TC and rows <= TC_MAX_ROWS and (rows < TC_PAIR_MIN_ROWS or (oc // 128) % 2 == 0)
 # 9..16 rows, measured on B200 (us per call, GEMV against the tensor-memory kernel): a single shard with many
 # input channels is faster on the tensor-memory kernel (17408 -> 5120 at 4 bpw: 40.5 / 45.0 against 40.3 / 40.6 at
 # 9 / 16 rows), a fused layer on the grouped GEMV (2 x 5120 -> 17408 at 3 bpw: 64.8 / 67.7 against 74.3 / 74.7;
@@ -71,7 +79,7 @@ def shard_gemm(x: Tensor, trellis: Tensor, suh: Tensor, svh: Tensor,
     small_tc = USE_TC and TC_MIN_ROWS_SINGLE <= rows <= _ext.GEMV_MAX_ROWS
     if (rows <= _ext.GEMV_MAX_ROWS and not small_tc) or (not USE_TC and rows <= GEMM_MAX_ROWS):
         _ext.exl3_gemm(x, trellis, y, suh, x, svh, -1, mcg, mul1, 0)
-    elif USE_TC and rows <= TC_MAX_ROWS:
+    elif _tc_takes(rows, oc):
         _ext.gemm_tc(x, trellis, y, suh, svh, mcg, mul1)
     else:
         _dense_path(x, trellis, suh, svh, k, mcg, mul1, y)
@@ -101,7 +109,7 @@ def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Te
     if (USE_TC and tc_from <= rows <= TC_MAX_ROWS and n <= _ext.MAX_SHARDS
             and _ext.gemm_tc_grouped(x, shards, y)):
         pass
-    elif rows > _ext.GEMV_MAX_ROWS and USE_TC and rows <= TC_MAX_ROWS:
+    elif rows > _ext.GEMV_MAX_ROWS and all(_tc_takes(rows, oc) for oc in ocs):
         col = 0
         for i in range(n):
             # every shard writes its own column block of y (no torch.cat, reference config.py:242)

@@ -47,6 +47,28 @@ def test_layer_gemm_fused(ops, coracle, rows):
     _check(y, np.concatenate(refs, 1))
 
 
+@pytest.mark.parametrize("rows", [1030, 4100])
+def test_many_rows_take_the_pair_kernel(ops, coracle, rows):
+    """From 1024 rows with an even number of 128-channel output blocks: decode once + dense tcgen05 GEMM on CTA pairs,
+    as a single shard (output rotated in place below 4096 rows, folded into the rebuilt weight from there) and as a
+    fused layer (every shard writes its column block of the result: pitched output, always folded)."""
+    ic, oc, K = 256, 512, 3
+    tr, suh, svh, x = R.make_layer(rows, ic, oc, K, rows)
+    y = torch.ops.orcasaq2.shard_gemm(x.cuda(), tr.cuda(), suh.cuda(), svh.cuda(), oc, float(K), False, False)
+    _check(y, coracle.layer(x.numpy(), coracle.reconstruct(tr.numpy()), suh.numpy(), svh.numpy()))
+    spec = [(256, 4), (512, 5), (256, 6)]
+    trs, suhs, svhs, refs = [], [], [], []
+    for i, (o, k) in enumerate(spec):
+        t, su, sv, _ = R.make_layer(300 + i, ic, o, k, 1)
+        trs.append(t.cuda()); suhs.append(su.cuda()); svhs.append(sv.cuda())
+        refs.append(coracle.layer(x.numpy(), coracle.reconstruct(t.numpy()), su.numpy(), sv.numpy()))
+    yl = torch.ops.orcasaq2.layer_gemm(x.cuda(), trs, suhs, svhs, [o for o, _ in spec], [float(k) for _, k in spec],
+                                       [False] * 3, [False] * 3)
+    _check(yl, np.concatenate(refs, 1))
+    from orcasaq2 import _ext
+    assert _ext.gemm_tc_status() == 0
+
+
 def test_empty_batch(ops):
     tr, suh, svh, _ = R.make_layer(1, 128, 128, 4, 1)
     x = torch.empty((0, 128), dtype=torch.half, device="cuda")
