@@ -535,6 +535,10 @@ def run_gpu(args):
         "cuda_graph": used_graph,
         "clocks": clocks, "roofline": roof,
     }
+    if isinstance(clocks, dict) and clocks.get("sm_mhz"):
+        # clock-normalised step time (us x GHz = thousands of SM cycles per step): comparable between runs whose
+        # sampled clocks differ
+        line["timing"]["kcycles_per_step"] = round(ms_step * 1e3 * float(clocks["sm_mhz"]) / 1e3, 1)
     if by_k is not None:
         line["roofline_by_k"] = by_k
     if prefill is not None:

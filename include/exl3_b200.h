@@ -127,15 +127,21 @@ int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, cons
               size_t workspace_bytes, void *stream);
 
 /*
- * Many-row form (mid-batch and prefill):  y[rows][oc] = H(H(x*suh) W) * svh  with the trellis
- * decoded inside the kernel into shared-memory fp16 tiles that feed tcgen05.mma (fp32
- * accumulators in tensor memory); the decoded weight is never written to global memory.
+ * Many-row form (mid-batch and prefill):  y[rows][oc] = H(H(x*suh) W) * svh  on tcgen05.mma (fp32
+ * accumulators in tensor memory).  Up to 1023 rows the trellis is decoded inside the kernel (into tensor
+ * memory up to 128 rows, into shared-memory fp16 tiles above) and the decoded weight is never written to
+ * global memory.  From 1024 rows, when oc / 128 is even, the weight is rebuilt ONCE per call into the scratch
+ * (transposed; from 4096 rows or with a pitched output the output rotation and svh are folded into it, which
+ * changes the rounding of the result by about one fp16 ulp of the weights) and a dense GEMM runs on CTA pairs
+ * (tcgen05.mma.cta_group::2): the reference's own many-row idea, orcasaq2/ops.py:50-59, with this library's
+ * GEMM in the place of hgemm_recon.
  * x is fp16 (or bf16 when x_is_bf16; it is narrowed to fp16 as the reference does,
  * orcasaq2/config.py:233), y fp16, scratch a caller buffer of exl3_gemm_tc_scratch_bytes() bytes,
  * 256-byte aligned: the rotated activations (the reference's `xh`, orcasaq2/ops.py:53) and, when the
- * output grid alone cannot fill the GPU, fp32 partial sums of the input slices.  Replaces the rows > GEMM_MAX_ROWS branch
+ * output grid alone cannot fill the GPU, fp32 partial sums of the input slices; from 1024 rows the rebuilt
+ * weight (ic*oc*2 bytes, the reference's `w`, ops.py:55-56).  Replaces the rows > GEMM_MAX_ROWS branch
  * had_r_128 -> reconstruct -> hgemm_recon -> had_r_128 of orcasaq2/ops.py:50-59 (and serves
- * 17..144 rows, which the reference sends to exl3_gemm).  Three launches on `stream`.
+ * 17..144 rows, which the reference sends to exl3_gemm).  Three or four launches on `stream`.
  * exl3_gemm_tc_status() returns a sticky device word that is non-zero only if a bounded wait
  * inside the kernel ran out (it synchronises the device; for diagnosis and tests).
  */
@@ -151,7 +157,8 @@ int exl3_gemm_tc(const void *x, const void *trellis, void *y, const void *suh, c
  * of 4 (this is what removes the torch.cat of orcasaq2/config.py:236-242 for fused layers).
  * fusion == NULL and ldy == oc is exl3_gemm_tc.  Up to 128 rows every
  * combination is served; beyond that a pitch or a residual is refused with EXL3_E_UNSUPPORTED when
- * the shape runs unsplit (the caller then applies them itself).
+ * the shape runs unsplit (the caller then applies them itself); the pair kernel (from 1024 rows) takes
+ * a pitch, no residual.
  */
 int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, const void *suh, const void *svh,
                     void *scratch, size_t scratch_bytes, int rows, int ic, int oc, int k_times_2, int mcg,
