@@ -404,10 +404,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
 // One MMA spans two SMs (tcgen05.mma.cta_group::2, M = 256 output channels, N = 256 tokens): each CTA of the pair
 // loads its own 128 rows of Wt and HALF of the token tile (128 of the 256 rows), so the token tile crosses
 // L2 -> shared memory once per 256 output channels and each SM reads 8 KB of operands per MMA instead of 12.
-// All loads are plain per-CTA 2-D TMA loads of this GPU's own memory (no multicast).  Warps: 0 = producer (one
-// lane: three TMA loads per stage on one barrier), 1 = MMA issue in the first CTA of the pair / relay in the
-// second (tells the first CTA when this CTA's stage has landed; the first CTA's commits arrive on the barriers of
-// both), 2..9 = epilogue (tcgen05.ld of their lane quadrant, fp16 stores).  Four stages of 48 KB.
+// All loads are per-CTA 2-D TMA loads of this GPU's own memory (no multicast); both CTAs' loads are counted on the
+// first CTA's barrier (the cta_group::2 form of the load), the first CTA's commits arrive on the barriers of both.
+// Warps: 0 = producer (one lane: three TMA loads per stage), 1 = MMA issue (first CTA of the pair only),
+// 2..9 = epilogue (tcgen05.ld of their lane quadrant, fp16 stores).  Four stages of 48 KB.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
     asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
@@ -417,13 +417,15 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
-// Arrive on the barrier at the same shared-memory offset in CTA `cta` of the cluster.  Default semantics (release at
-// CTA scope): what this announces was written by the async proxy and observed complete inside the announcing CTA
-// before the arrive is issued; a cluster-scope release here costs about a microsecond per arrive (measured).
-__device__ __forceinline__ void mbar_arrive_remote(uint32_t local_bar, uint32_t cta) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_bar), "r"(cta));
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(remote) : "memory");
+// 2-D tiled TMA load into THIS CTA's shared memory whose bytes are counted on a barrier of the pair's first CTA
+// (`bar_cluster`: a shared::cluster address).  Not a multicast load: one CTA's own tile of this GPU's memory.
+__device__ __forceinline__ void tma_2d_pair(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar_cluster) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
+}
+__device__ __forceinline__ void tma_2d_prefetch(const CUtensorMap *map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void umma2(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -445,6 +447,7 @@ __device__ __forceinline__ uint32_t umma2_idesc(int n) {
 constexpr int kDenseMinRows = 1024;
 constexpr int kDenseFoldRows = 4096;                                  // from here the output rotation is folded into the rebuilt weight
 constexpr int kDenseStages = 4;
+constexpr int kDensePrefetch = 4;                                      // L2 prefetch distance beyond the ring, in steps
 constexpr int kDenseBand = 8;                                          // channel pairs (of 256 channels) per L2 band
 constexpr int kDenseHalfBytes = (kBN / 2) * kBK * 2;                   // this CTA's 128 token rows of one accumulator: 16 KB
 constexpr int kDenseStageBytes = kABytes + kMaxHalves * kDenseHalfBytes;   // 48 KB
@@ -458,7 +461,7 @@ struct DenseParams {
     int tile_tokens;       // tokens per CTA: 512 (two accumulators) or 256
 };
 struct DenseBarriers {
-    uint64_t full[kDenseStages], empty[kDenseStages], peer_full[kDenseStages];
+    uint64_t full[kDenseStages], empty[kDenseStages];
     uint64_t acc_full;
     uint32_t tmem_base;
 };
@@ -503,7 +506,6 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
         for (int s = 0; s < kDenseStages; ++s) {
             mbar_init(s32(&S.full[s]), 1);
             mbar_init(s32(&S.empty[s]), 1);
-            mbar_init(s32(&S.peer_full[s]), 1);
         }
         mbar_init(s32(&S.acc_full), 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -520,38 +522,39 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     const uint32_t tmem = S.tmem_base;
 
     if (warp == 0) {
-        // ---------------- producer: Wt rows of this CTA, and this CTA's half of each 256-token tile
+        // ---------------- producer: Wt rows of this CTA, and this CTA's half of each 256-token tile.  The bytes of
+        // BOTH CTAs of the pair are counted on the first CTA's `full` barrier (which that CTA arms with the sum), so
+        // the MMA-issuing lane learns of the second CTA's tiles without a relay.  Tiles four steps further on are
+        // prefetched into L2.
         if (lane == 0) {
             bool ok = true;
+            uint32_t full0;                                          // full[0] of the pair's first CTA
+            asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(full0) : "r"(s32(&S.full[0])));
             Cursor c(0, kDenseStages);
             for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
                 if (c.wrapped) ok = mbar_wait(s32(&S.empty[c.idx]), c.phase ^ 1u, 20);
                 if (!ok) break;
-                const uint32_t bar = s32(&S.full[c.idx]);
+                const uint32_t bar = full0 + 8 * c.idx;
                 const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
-                mbar_expect_tx(bar, kABytes + halves * kDenseHalfBytes);
-                tma_2d(st, &wmap, s * kBK, ob * kBM, bar);
+                if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), 2 * (kABytes + halves * kDenseHalfBytes));
+                tma_2d_pair(st, &wmap, s * kBK, ob * kBM, bar);
                 for (int h = 0; h < halves; ++h)     // token rows out of range arrive as zeros
-                    tma_2d(st + kABytes + h * kDenseHalfBytes, &xmap, s * kBK, tok0 + h * kBN + (int)crank * (kBN / 2), bar);
+                    tma_2d_pair(st + kABytes + h * kDenseHalfBytes, &xmap, s * kBK, tok0 + h * kBN + (int)crank * (kBN / 2), bar);
+                if (s + kDensePrefetch < nsteps) {
+                    tma_2d_prefetch(&wmap, (s + kDensePrefetch) * kBK, ob * kBM);
+                    for (int h = 0; h < halves; ++h)
+                        tma_2d_prefetch(&xmap, (s + kDensePrefetch) * kBK, tok0 + h * kBN + (int)crank * (kBN / 2));
+                }
             }
         }
     } else if (warp == 1) {
-        if (lane == 0 && crank != 0) {
-            // ---------------- second CTA: tell the first when a stage has landed here
-            bool ok = true;
-            Cursor c(0, kDenseStages);
-            for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
-                ok = mbar_wait(s32(&S.full[c.idx]), c.phase);
-                if (ok) mbar_arrive_remote(s32(&S.peer_full[c.idx]), 0);
-            }
-        } else if (lane == 0) {
+        if (lane == 0 && crank == 0) {
             // ---------------- first CTA: MMA issue for the pair
             bool ok = true;
             const uint32_t idesc = umma2_idesc(kBN);
             Cursor c(0, kDenseStages);
             for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
-                ok = mbar_wait(s32(&S.full[c.idx]), c.phase);
-                if (ok) ok = mbar_wait(s32(&S.peer_full[c.idx]), c.phase);
+                ok = mbar_wait(s32(&S.full[c.idx]), c.phase);        // both CTAs' tiles of this stage have landed
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t a0 = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
@@ -721,6 +724,49 @@ __device__ __forceinline__ void load4(const void *x, size_t off, float (&v)[4]) 
         const uint2 raw = *reinterpret_cast<const uint2 *>(static_cast<const __half *>(x) + off);
         const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw.x), h23 = *reinterpret_cast<const __half2 *>(&raw.y);
         v[0] = __low2float(h01); v[1] = __high2float(h01); v[2] = __low2float(h23); v[3] = __high2float(h23);
+    }
+}
+
+// The plain case (no fused norm / activation) of the pre-pass below for many rows: the kernel moves 4 bytes per element
+// and little else, so each warp takes four consecutive 128-blocks and issues all of their loads before the first
+// butterfly (one block per warp: 2.6 TB/s on B200).  Same arithmetic, same output order.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+xh_permute4_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __half *__restrict__ xh,
+                   long long nblocks, int blocks_per_row, int ldx) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int lane = threadIdx.x & 31;
+    const long long wid0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 4;
+    if (wid0 >= nblocks) return;
+    uint2 raw[4], sg[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        const long long wid = wid0 + u < nblocks ? wid0 + u : wid0;
+        const int blk = (int)(wid % blocks_per_row);
+        const long long row = wid / blocks_per_row;
+        raw[u] = *reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(x) + (size_t)row * ldx + (size_t)blk * 128 + 4 * lane);
+        sg[u] = *reinterpret_cast<const uint2 *>(suh + blk * 128 + 4 * lane);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+        if (wid0 + u >= nblocks) break;
+        float v[4];
+        if (BF16) {
+            v[0] = __uint_as_float(raw[u].x << 16); v[1] = __uint_as_float(raw[u].x & 0xFFFF0000u);
+            v[2] = __uint_as_float(raw[u].y << 16); v[3] = __uint_as_float(raw[u].y & 0xFFFF0000u);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] = __half2float(__float2half_rn(v[k]));
+        } else {
+            const __half2 h01 = *reinterpret_cast<const __half2 *>(&raw[u].x), h23 = *reinterpret_cast<const __half2 *>(&raw[u].y);
+            v[0] = __low2float(h01); v[1] = __high2float(h01); v[2] = __low2float(h23); v[3] = __high2float(h23);
+        }
+        const __half2 s01 = *reinterpret_cast<const __half2 *>(&sg[u].x), s23 = *reinterpret_cast<const __half2 *>(&sg[u].y);
+        v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
+        fwht128_warp(v, lane);
+        __half *dst = xh + (size_t)(wid0 + u) * 128 + 16 * (lane >> 2) + (lane & 3);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) dst[4 * j] = __float2half_rn(v[j] * kHadScale);
     }
 }
 
@@ -1153,10 +1199,17 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         __half *wt = reinterpret_cast<__half *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic));
         const long long nblocks = (long long)rows * (ic / 128);
         const unsigned g1 = (unsigned)((nblocks + 7) / 8);
-        if (x_is_bf16)
+        if (F.in_mode == 0) {
+            const unsigned g4 = (unsigned)((nblocks + 31) / 32);
+            if (x_is_bf16)
+                xh_permute4_kernel<true><<<g4, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F.ldx);
+            else
+                xh_permute4_kernel<false><<<g4, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F.ldx);
+        } else if (x_is_bf16) {
             xh_permute_kernel<true><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F);
-        else
+        } else {
             xh_permute_kernel<false><<<g1, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F);
+        }
         if (cudaGetLastError() != cudaSuccess) return EXL3_E_LAUNCH;
         int rc;
         switch (K) {
