@@ -446,11 +446,11 @@ __device__ __forceinline__ uint32_t umma2_idesc(int n) {
 
 constexpr int kDenseMinRows = 1024;
 constexpr int kDenseFoldRows = 4096;                                  // from here the output rotation is folded into the rebuilt weight
-constexpr int kDenseStages = 4;
-constexpr int kDensePrefetch = 4;                                      // L2 prefetch distance beyond the ring, in steps
+constexpr int kDenseStages = 6;
+constexpr int kDensePrefetch = 6;                                      // L2 prefetch distance beyond the ring, in steps
 constexpr int kDenseBand = 8;                                          // channel pairs (of 256 channels) per L2 band
-constexpr int kDenseHalfBytes = (kBN / 2) * kBK * 2;                   // this CTA's 128 token rows of one accumulator: 16 KB
-constexpr int kDenseStageBytes = kABytes + kMaxHalves * kDenseHalfBytes;   // 48 KB
+constexpr int kDenseHalfBytes = (kBN / 2) * kBK * 2;                   // this CTA's 128 token rows of a 256-token tile: 16 KB
+constexpr int kDenseStageBytes = kABytes + kDenseHalfBytes;            // 32 KB
 constexpr int kDenseEpiWarps = 8;
 constexpr int kDenseThreads = 32 * (2 + kDenseEpiWarps);
 constexpr size_t kDenseSmem = (size_t)kDenseStages * kDenseStageBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
@@ -458,14 +458,33 @@ constexpr size_t kDenseSmem = (size_t)kDenseStages * kDenseStageBytes + 1024 /*b
 struct DenseParams {
     __half *y;             // [tokens][ldy]
     int tokens, ic, oc, ldy;
-    int tile_tokens;       // tokens per CTA: 512 (two accumulators) or 256
+    int npx, nty;          // tiles: pairs of 128-channel blocks x 256-token tiles
+    int npairs;            // CTA pairs launched (each walks tiles pair, pair + npairs, ...)
 };
 struct DenseBarriers {
     uint64_t full[kDenseStages], empty[kDenseStages];
-    uint64_t acc_full;
+    uint64_t acc_full[2], acc_empty[2];
     uint32_t tmem_base;
 };
 
+// tile number (in launch order) -> (channel pair, token tile): bands of kDenseBand channel pairs are walked token
+// tile by token tile, so that the pairs running at the same time share a band's weight rows in L2
+__device__ __forceinline__ void dense_tile(const DenseParams &P, int L, int &px, int &ty) {
+    const int full_bands = P.npx / kDenseBand;
+    const int in_full = full_bands * kDenseBand * P.nty;
+    if (L < in_full) {
+        const int band = L / (kDenseBand * P.nty), r = L - band * (kDenseBand * P.nty);
+        px = band * kDenseBand + r % kDenseBand;
+        ty = r / kDenseBand;
+    } else {                                                      // the last, narrower band
+        const int w = P.npx - full_bands * kDenseBand, r = L - in_full;
+        px = full_bands * kDenseBand + r % w;
+        ty = r / w;
+    }
+}
+
+// Persistent: every CTA pair walks its share of the 256-channel x 256-token tiles.  Tensor memory holds two
+// accumulators (2 x 256 columns): while the epilogue warps drain one tile, the MMAs of the next tile fill the other.
 __global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                        const DenseParams P) {
@@ -474,40 +493,20 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     DenseBarriers &S = *reinterpret_cast<DenseBarriers *>(smem_raw + (size_t)kDenseStages * kDenseStageBytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t crank = cluster_ctarank();                     // 0 issues the MMAs of the pair
-    // Launch order -> tile: pairs that run at the same time should share operands in L2.  In launch order (x
-    // fastest) one wave would sweep ALL output channels for one token tile, streaming the whole rebuilt weight from
-    // HBM once per token tile; instead bands of kDenseBand channel pairs are walked token tile by token tile, so a
-    // band's weight rows stay in L2 while the token tiles pass.
-    int ob, ty;
-    {
-        const int npx = gridDim.x >> 1, nty = gridDim.y;
-        const int L = blockIdx.y * npx + (blockIdx.x >> 1);
-        const int full_bands = npx / kDenseBand;
-        const int in_full = full_bands * kDenseBand * nty;
-        int px;
-        if (L < in_full) {
-            const int band = L / (kDenseBand * nty), r = L - band * (kDenseBand * nty);
-            px = band * kDenseBand + r % kDenseBand;
-            ty = r / kDenseBand;
-        } else {                                                  // the last, narrower band
-            const int w = npx - full_bands * kDenseBand, r = L - in_full;
-            px = full_bands * kDenseBand + r % w;
-            ty = r / w;
-        }
-        ob = 2 * px + (int)crank;                                 // 128-channel block of outputs
-    }
-    const int tok0 = ty * P.tile_tokens;
-    const int tok_here = min(P.tokens - tok0, P.tile_tokens);
-    const int halves = tok_here > kBN ? 2 : 1;
+    const int pair = blockIdx.x >> 1;
+    const int ntiles = P.npx * P.nty;
     const int nsteps = P.ic / kBK;
-    constexpr uint32_t kTmemCols = kBN * kMaxHalves;
+    constexpr uint32_t kTmemCols = 2 * kBN;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kDenseStages; ++s) {
             mbar_init(s32(&S.full[s]), 1);
             mbar_init(s32(&S.empty[s]), 1);
         }
-        mbar_init(s32(&S.acc_full), 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(s32(&S.acc_full[b]), 1);
+            mbar_init(s32(&S.acc_empty[b]), 2 * kDenseEpiWarps);   // the epilogue warps of both CTAs
+        }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -522,28 +521,31 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     const uint32_t tmem = S.tmem_base;
 
     if (warp == 0) {
-        // ---------------- producer: Wt rows of this CTA, and this CTA's half of each 256-token tile.  The bytes of
-        // BOTH CTAs of the pair are counted on the first CTA's `full` barrier (which that CTA arms with the sum), so
-        // the MMA-issuing lane learns of the second CTA's tiles without a relay.  Tiles four steps further on are
-        // prefetched into L2.
+        // ---------------- producer: this CTA's 128 weight rows and its half of the 256-token tile, every step of
+        // every tile of the pair.  The bytes of BOTH CTAs are counted on the first CTA's `full` barrier (which that
+        // CTA arms with the sum), so the MMA-issuing lane learns of the second CTA's tiles without a relay.  Tiles a
+        // ring's length further on are prefetched into L2.
         if (lane == 0) {
             bool ok = true;
             uint32_t full0;                                          // full[0] of the pair's first CTA
             asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(full0) : "r"(s32(&S.full[0])));
             Cursor c(0, kDenseStages);
-            for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
-                if (c.wrapped) ok = mbar_wait(s32(&S.empty[c.idx]), c.phase ^ 1u, 20);
-                if (!ok) break;
-                const uint32_t bar = full0 + 8 * c.idx;
-                const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
-                if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), 2 * (kABytes + halves * kDenseHalfBytes));
-                tma_2d_pair(st, &wmap, s * kBK, ob * kBM, bar);
-                for (int h = 0; h < halves; ++h)     // token rows out of range arrive as zeros
-                    tma_2d_pair(st + kABytes + h * kDenseHalfBytes, &xmap, s * kBK, tok0 + h * kBN + (int)crank * (kBN / 2), bar);
-                if (s + kDensePrefetch < nsteps) {
-                    tma_2d_prefetch(&wmap, (s + kDensePrefetch) * kBK, ob * kBM);
-                    for (int h = 0; h < halves; ++h)
-                        tma_2d_prefetch(&xmap, (s + kDensePrefetch) * kBK, tok0 + h * kBN + (int)crank * (kBN / 2));
+            for (int L = pair; L < ntiles && ok; L += P.npairs) {
+                int px, ty;
+                dense_tile(P, L, px, ty);
+                const int row_w = (2 * px + (int)crank) * kBM, row_x = ty * kBN + (int)crank * (kBN / 2);
+                for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
+                    if (c.wrapped) ok = mbar_wait(s32(&S.empty[c.idx]), c.phase ^ 1u, 20);
+                    if (!ok) break;
+                    const uint32_t bar = full0 + 8 * c.idx;
+                    const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
+                    if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), 2 * kDenseStageBytes);
+                    tma_2d_pair(st, &wmap, s * kBK, row_w, bar);
+                    tma_2d_pair(st + kABytes, &xmap, s * kBK, row_x, bar);     // token rows out of range arrive as zeros
+                    if (s + kDensePrefetch < nsteps) {
+                        tma_2d_prefetch(&wmap, (s + kDensePrefetch) * kBK, row_w);
+                        tma_2d_prefetch(&xmap, (s + kDensePrefetch) * kBK, row_x);
+                    }
                 }
             }
         }
@@ -553,33 +555,46 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
             bool ok = true;
             const uint32_t idesc = umma2_idesc(kBN);
             Cursor c(0, kDenseStages);
-            for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
-                ok = mbar_wait(s32(&S.full[c.idx]), c.phase);        // both CTAs' tiles of this stage have landed
+            int i = 0;                                               // tiles of this pair so far
+            for (int L = pair; L < ntiles && ok; L += P.npairs, ++i) {
+                const int b = i & 1, use = i >> 1;
+                // the epilogue warps of both CTAs have drained this accumulator's previous tile
+                if (use > 0) ok = mbar_wait(s32(&S.acc_empty[b]), (uint32_t)(use - 1) & 1u);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t a0 = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
-                for (int h = 0; h < halves; ++h) {
-                    const uint32_t b0 = a0 + kABytes + h * kDenseHalfBytes;
+                for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
+                    ok = mbar_wait(s32(&S.full[c.idx]), c.phase);    // both CTAs' tiles of this stage have landed
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t a0 = s32(smem_raw + (size_t)c.idx * kDenseStageBytes), b0 = a0 + kABytes;
 #pragma unroll
                     for (int k = 0; k < kBK / 16; ++k)
-                        umma2(tmem + h * kBN, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (s | k) ? 1u : 0u);
+                        umma2(tmem + b * kBN, umma_desc(a0 + k * 32), umma_desc(b0 + k * 32), idesc, (s | k) ? 1u : 0u);
+                    umma2_commit(s32(&S.empty[c.idx]));  // both CTAs' stage is free once these MMAs have read it
                 }
-                umma2_commit(s32(&S.empty[c.idx]));      // both CTAs' stage is free once these MMAs have read it
+                umma2_commit(s32(&S.acc_full[b]));       // both CTAs' epilogue warps may read the accumulator
             }
-            umma2_commit(s32(&S.acc_full));
         }
     } else {
-        // ---------------- epilogue: TMEM -> fp16 -> y[token][oc]
-        const bool ok = mbar_wait(s32(&S.acc_full), 0, 200);
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // ---------------- epilogue: TMEM -> fp16 -> y[token][oc], tile after tile, one accumulator behind the MMAs
         const int quad = warp & 3;                                  // TMEM lanes 32*quad .. +31
-        const int oc_row = ob * kBM + 32 * quad + lane;
         const int col_part = (warp - 2) >> 2;                       // the two warps of a quadrant split the columns
-        for (int h = 0; h < halves; ++h) {
-            const int ncols = min(kBN, tok_here - h * kBN);
-            for (int c0 = col_part * 32; c0 < ncols; c0 += 64) {
+        uint32_t acc_empty0;                                        // acc_empty[0] of the pair's first CTA
+        asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(acc_empty0) : "r"(s32(&S.acc_empty[0])));
+        bool ok = true;
+        int i = 0;
+        for (int L = pair; L < ntiles && ok; L += P.npairs, ++i) {
+            const int b = i & 1, use = i >> 1;
+            int px, ty;
+            dense_tile(P, L, px, ty);
+            const int oc_row = (2 * px + (int)crank) * kBM + 32 * quad + lane;
+            const int tok0 = ty * kBN;
+            const int ncols = min(kBN, P.tokens - tok0);
+            ok = mbar_wait(s32(&S.acc_full[b]), (uint32_t)use & 1u, 100);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            for (int c0 = col_part * 32; c0 < kBN; c0 += 64) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(h * kBN + c0);
+                const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(b * kBN + c0);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
@@ -593,9 +608,13 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
 #pragma unroll
                     for (int j = 0; j < 32; ++j)
                         if (c0 + j < ncols)
-                            P.y[(size_t)(tok0 + h * kBN + c0 + j) * P.ldy + oc_row] = __float2half_rn(__uint_as_float(v[j]));
+                            P.y[(size_t)(tok0 + c0 + j) * P.ldy + oc_row] = __float2half_rn(__uint_as_float(v[j]));
                 }
             }
+            // this warp's reads of the accumulator are complete: hand it back to the MMAs (first CTA's barrier)
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(acc_empty0 + 8 * b) : "memory");
         }
     }
 
@@ -1064,13 +1083,12 @@ static int launch_reconstruct_t(const void *trellis, const void *svh, void *wt, 
     return launch_status();
 }
 
-static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, const DenseParams &P, cudaStream_t st) {
+static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseParams P, cudaStream_t st) {
     if (cudaFuncSetAttribute(gemm_dense_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
     }
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(P.oc / kBM, (P.tokens + P.tile_tokens - 1) / P.tile_tokens, 1);
     cfg.blockDim = dim3(kDenseThreads);
     cfg.dynamicSmemBytes = kDenseSmem;
     cfg.stream = st;
@@ -1081,6 +1099,22 @@ static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, const 
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+    // as many pairs as the device holds at once (cached per device), each walking its share of the tiles
+    static int pairs_on[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    int fit = dev >= 0 && dev < 64 ? pairs_on[dev] : 0;
+    if (fit == 0) {
+        cfg.gridDim = dim3(2 * 1024);
+        if (cudaOccupancyMaxActiveClusters(&fit, gemm_dense_pair_kernel, &cfg) != cudaSuccess || fit < 1) {
+            cudaGetLastError();
+            return EXL3_E_LAUNCH;
+        }
+        if (dev >= 0 && dev < 64) pairs_on[dev] = fit;
+    }
+    const int ntiles = P.npx * P.nty;
+    P.npairs = ntiles < fit ? ntiles : fit;
+    cfg.gridDim = dim3((unsigned)(2 * P.npairs));
     if (cudaLaunchKernelEx(&cfg, gemm_dense_pair_kernel, wmap, xmap, P) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     return launch_status();
 }
@@ -1194,7 +1228,7 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         // A pitched output (a column block of a fused layer's result) cannot be rotated in place afterwards: fold.
         const bool fold = rows >= kDenseFoldRows || ldy != oc;
         if (residual) return EXL3_E_UNSUPPORTED;
-        if (oc / 128 > 65535 || ic / 64 > 65535 || (rows + 511) / 512 > 65535) return EXL3_E_SHAPE;
+        if (oc / 128 > 65535 || ic / 64 > 65535) return EXL3_E_SHAPE;
         __half *xh = static_cast<__half *>(scratch);
         __half *wt = reinterpret_cast<__half *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic));
         const long long nblocks = (long long)rows * (ic / 128);
@@ -1237,11 +1271,10 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         DenseParams D;
         D.y = static_cast<__half *>(y);
         D.tokens = rows; D.ic = ic; D.oc = oc; D.ldy = ldy;
-        // 512 tokens per CTA.  256-token tiles (twice as many, shorter CTAs) were measured where they fill the last
-        // wave better (17408 -> 5120): slower all the same, 725 against 747 and 936 against 1085 TFLOP/s at 2048 and
-        // 8192 rows: a weight tile then serves four MMAs instead of eight and L2 -> shared-memory traffic limits.
-        D.tile_tokens = kBN * kMaxHalves;
-        if ((rows + D.tile_tokens - 1) / D.tile_tokens > 65535) return EXL3_E_SHAPE;
+        D.npx = oc / kBM / 2;
+        D.nty = (rows + kBN - 1) / kBN;
+        D.npairs = 0;
+        if ((long long)D.npx * D.nty > 0x3fffffffLL) return EXL3_E_SHAPE;
         rc = launch_dense(wmap, xmap, D, st);
         if (rc != EXL3_OK || fold) return rc;
         return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
