@@ -445,9 +445,8 @@ __device__ __forceinline__ uint32_t umma2_idesc(int n) {
 }
 
 constexpr int kDenseMinRows = 1024;
-constexpr int kDenseFoldRows = 4096;                                  // from here the output rotation is folded into the rebuilt weight
-constexpr int kDenseStages = 6;
-constexpr int kDensePrefetch = 6;                                      // L2 prefetch distance beyond the ring, in steps
+constexpr int kDenseStages = 7;
+constexpr int kDensePrefetch = 12;                                     // L2 prefetch distance beyond the ring, in steps
 constexpr int kDenseBand = 8;                                          // channel pairs (of 256 channels) per L2 band
 constexpr int kDenseHalfBytes = (kBN / 2) * kBK * 2;                   // this CTA's 128 token rows of a 256-token tile: 16 KB
 constexpr int kDenseStageBytes = kABytes + kDenseHalfBytes;            // 32 KB
@@ -1223,10 +1222,12 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
     if (use_dense(rows, oc)) {
         // ---- many rows: rotate the activations, rebuild the weight once (transposed, with the output rotation and
         // signs folded in), dense tcgen05 GEMM on CTA pairs whose epilogue writes the final result
-        // Folding costs a fixed ~80 us per call for a 5120 x 17408 weight (128 x 128 sign-matrix products on the
-        // legacy tensor path), the separate output rotation ~13 us per 1024 rows of that width: fold from 4096 rows.
+        // Folding costs 0.83 us per 2^20 weights (128 x 128 sign-matrix products on the legacy tensor path: +74 us for
+        // 5120 x 17408); the separate output rotation costs 0.49 us per 2^20 outputs while the output stays in L2
+        // (17.6 us for 2048 x 17408) and 1.22 us beyond that (174 us for 8192 x 17408).  Fold when that is cheaper.
         // A pitched output (a column block of a fused layer's result) cannot be rotated in place afterwards: fold.
-        const bool fold = rows >= kDenseFoldRows || ldy != oc;
+        const double had_per = (double)rows * oc * 2 > 96.0 * 1048576.0 ? 1.22 : 0.49;
+        const bool fold = had_per * rows > 0.83 * ic || ldy != oc;
         if (residual) return EXL3_E_UNSUPPORTED;
         if (oc / 128 > 65535 || ic / 64 > 65535) return EXL3_E_SHAPE;
         __half *xh = static_cast<__half *>(scratch);
