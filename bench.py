@@ -560,6 +560,13 @@ def run_gpu(args):
     _leave(world)
 
 
+def _takes_pair_kernel(rows, ic, oc):
+    """The library's own choice between its two many-row kernels (exl3_gemm_tc.cu, use_dense), restated for the label."""
+    if (oc // 128) % 2:
+        return False
+    return rows >= 1024 or (oc >= 2048 and (rows >= 640 or (rows >= 384 and ic >= 2 * oc)))
+
+
 def prefill_block(torch, _ext, dev):
     """BASELINE config 3: M tokens x (5120 -> 17408 at 3 bpw, 17408 -> 5120 at 4 bpw), bf16 activations: TFLOPS of the
     library's tcgen05 path (exl3_gemm_tc: in-kernel decode up to 1023 rows; from 1024 rows the weight is rebuilt once
@@ -606,8 +613,8 @@ def prefill_block(torch, _ext, dev):
                                  "tcgen05_tflops": round(fl / t_tc / 1e12, 1),
                                  "tcgen05_frac_of_burst_peak": round(fl / t_tc / 1e12 / peaks["burst"], 3),
                                  "rotate_reconstruct_library_gemm_tflops": round(fl / t_rt / 1e12, 1),
-                                 "plugin_dispatch": "tcgen05: in-kernel decode" if m <= 1023 else
-                                 "tcgen05: decode once + dense GEMM on CTA pairs"})
+                                 "plugin_dispatch": "tcgen05: decode once + dense GEMM on CTA pairs" if _takes_pair_kernel(m, ic, oc)
+                                 else "tcgen05: in-kernel decode"})
             del x, y
         del sh
         torch.cuda.empty_cache()

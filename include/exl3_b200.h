@@ -130,7 +130,7 @@ int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, cons
  * Many-row form (mid-batch and prefill):  y[rows][oc] = H(H(x*suh) W) * svh  on tcgen05.mma (fp32
  * accumulators in tensor memory).  Up to 1023 rows the trellis is decoded inside the kernel (into tensor
  * memory up to 128 rows, into shared-memory fp16 tiles above) and the decoded weight is never written to
- * global memory.  From 1024 rows, when oc / 128 is even, the weight is rebuilt ONCE per call into the scratch
+ * global memory.  From 1024 rows (from 384 .. 640 rows for wide layers), when oc / 128 is even, the weight is rebuilt ONCE per call into the scratch
  * (transposed; where that is cheaper than rotating the output afterwards, or with a pitched output, the output rotation and svh are folded into it, which
  * changes the rounding of the result by about one fp16 ulp of the weights) and a dense GEMM runs on CTA pairs
  * (tcgen05.mma.cta_group::2): the reference's own many-row idea, orcasaq2/ops.py:50-59, with this library's

@@ -444,7 +444,7 @@ __device__ __forceinline__ uint32_t umma2_idesc(int n) {
     return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
 }
 
-constexpr int kDenseMinRows = 1024;
+constexpr int kDenseMinRows = 1024;                                    // from here always (given an even number of output blocks)
 constexpr int kDenseStages = 7;
 constexpr int kDensePrefetch = 12;                                     // L2 prefetch distance beyond the ring, in steps
 constexpr int kDenseBand = 8;                                          // channel pairs (of 256 channels) per L2 band
@@ -1066,8 +1066,16 @@ static int choose_splitk(int rows, int ic, int oc) {
     return sk < 1 ? 1 : sk;
 }
 static size_t xh_bytes(int rows, int ic) { return (((size_t)rows * ic * 2) + 255) & ~(size_t)255; }
-// the decode-once route: enough rows to amortise rebuilding the weight, and output blocks that pair up
-static bool use_dense(int rows, int oc) { return rows >= kDenseMinRows && ((oc / kBM) & 1) == 0; }
+// The decode-once route: output blocks that pair up, and enough rows to amortise rebuilding the weight.  Crossover
+// with the in-kernel-decode kernel, measured on B200 (us per call, decode-once against in-kernel decode):
+//   5120 -> 17408 @3: 141 / 122 at 512 rows, 178 / 195 at 768;   17408 -> 5120 @4: 154 / 131 at 256, 161 / 181 at 384,
+//   166 / 193 at 512;   5120 -> 6144 @4: 74 / 63 at 512, 80 / 99 at 768;   5120 -> 1024 @5: 60 / 47 at 1000 (too few tiles).
+static bool use_dense(int rows, int ic, int oc) {
+    if ((oc / kBM) & 1) return false;
+    if (rows >= kDenseMinRows) return true;
+    if (oc < 2048) return false;
+    return rows >= 640 || (rows >= 384 && ic >= 2 * oc);
+}
 
 template <int K>
 static int launch_reconstruct_t(const void *trellis, const void *svh, void *wt, int ic, int oc, bool fold, cudaStream_t st) {
@@ -1122,7 +1130,7 @@ static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseP
 extern "C" size_t exl3_gemm_tc_scratch_bytes(int rows, int ic, int oc) {
     if (rows < 1 || ic <= 0 || oc <= 0) return 0;
     if (exl3::ts::eligible(rows, ic, oc)) return exl3::ts::scratch_bytes(rows, ic, oc);
-    if (exl3::tc::use_dense(rows, oc)) return exl3::tc::xh_bytes(rows, ic) + (size_t)ic * oc * 2;   // + the rebuilt weight
+    if (exl3::tc::use_dense(rows, ic, oc)) return exl3::tc::xh_bytes(rows, ic) + (size_t)ic * oc * 2;   // + the rebuilt weight
     const int sk = exl3::tc::choose_splitk(rows, ic, oc);
     return exl3::tc::xh_bytes(rows, ic) + (sk > 1 ? (size_t)sk * rows * oc * 4 : 0);
 }
@@ -1219,7 +1227,7 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         }
         return EXL3_OK;
     }
-    if (use_dense(rows, oc)) {
+    if (use_dense(rows, ic, oc)) {
         // ---- many rows: rotate the activations, rebuild the weight once (transposed, with the output rotation and
         // signs folded in), dense tcgen05 GEMM on CTA pairs whose epilogue writes the final result
         // Folding costs 0.83 us per 2^20 weights (128 x 128 sign-matrix products on the legacy tensor path: +74 us for

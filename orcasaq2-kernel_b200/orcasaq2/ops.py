@@ -6,9 +6,9 @@ used by `Exl3LinearMethod.apply`: every shard of a fused layer in one launch, wr
 into the concatenated output.
 
 Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GEMV (HBM-bound
-streaming of the packed trellis; a single shard moves to the tensor-memory kernel below from 9 rows).  From 17 rows: `exl3_gemm_tc`.  Up to 1023 rows that is
+streaming of the packed trellis; a single shard moves to the tensor-memory kernel below from 9 rows).  From 17 rows: `exl3_gemm_tc`.  For few hundred rows that is
 one pass over the packed weights with no dense copy in memory -- up to 128 rows the decoded weights go from registers into tensor memory and are the A
-operand of tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  From 1024 rows the library decodes once (the reference's own idea
+operand of tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  From 1024 rows (from 384 .. 640 rows for wide layers, where it measured faster) the library decodes once (the reference's own idea
 for many rows, ops.py:50-59: rotate, rebuild the weight into scratch, dense GEMM, rotate back) and runs its own dense tcgen05 GEMM on CTA pairs, with the
 output rotation folded into the rebuilt weight where that is cheaper.  The reference's route with a library GEMM (`_dense_path`) remains for shapes the pair kernel
 does not take (an odd number of 128-channel output blocks) and behind ORCA_EXL3_TC_MAX_ROWS.  GEMM_MAX_ROWS keeps the
