@@ -14,9 +14,10 @@ metric  = algorithmic bytes (trellis + activations in + out) moved per second, w
 value   = inputs resident in HBM: ONE CUDA graph of exactly `--steps` steps, replayed >= 100 times and
           for >= 250 ms, every replay timed with CUDA events (max over ranks); the median replay is
           reported, its spread is in `timing`.  `by_rows` repeats this at 1 / 4 / 16 rows.
-e2e     = same metric through the plugin's custom op with HOST activations: pinned host x ->
-          device, three `orcasaq2::layer_gemm` calls, outputs back to pinned host, every step;
-          replayed from a CUDA graph (the plugin's serving mode), the eager time is reported beside it.
+e2e     = same metric through the plugin's custom op with HOST activations, every step: the step's activations
+          from one pinned host buffer -> device, three `orcasaq2::layer_gemm` calls, the results gathered on
+          the device -> one pinned host buffer; replayed from a CUDA graph (the plugin's serving mode).  The
+          eager time (per layer: copy in, op, copy out) is reported beside it.
 N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
           down_proj followed by this library's one-shot all-reduce over peer memory; `--allreduce nccl`
           uses the library collective instead), strong scaling: the job's total bytes are fixed.
@@ -398,15 +399,28 @@ def run_gpu(args):
         # The serving mode of the plugin (the op is built to replay inside CUDA graphs): per weight set
         # one graph of [pinned host x -> device, the three plugin ops, outputs -> pinned host]; a step
         # rewrites the host activations, replays the graph and waits for the outputs.
-        dx = {ic: torch.empty_like(x) for ic, x in xs.items()}
+        # All host activations of a step sit in ONE pinned buffer and all results return in one: two copies per step
+        # instead of six (a copy of a few tens of KB costs its latency, not its bytes).
+        ics = sorted(xs)
+        xoff = {ic: sum(rows * j for j in ics[:k]) for k, ic in enumerate(ics)}
+        hx_all = torch.empty((sum(rows * ic for ic in ics),), dtype=torch.half).pin_memory()
+        for ic in ics:
+            hx_all[xoff[ic]:xoff[ic] + rows * ic] = hx[ic].reshape(-1)
+        dx_all = torch.empty_like(hx_all, device=dev)
+        dxv = {ic: dx_all[xoff[ic]:xoff[ic] + rows * ic].view(rows, ic) for ic in ics}
+        tots = [tot for (_, _, _, tot) in sets[0]]
+        yoff = [sum(rows * t for t in tots[:k]) for k in range(len(tots))]
+        dy_all = torch.empty((sum(rows * t for t in tots),), dtype=torch.half, device=dev)
+        hy_all = torch.empty(dy_all.shape, dtype=torch.half).pin_memory()
 
         def e2e_body(si):
-            for li, (name, ic_r, _, _) in enumerate(sets[si]):
-                dx[ic_r].copy_(hx[ic_r], non_blocking=True)
-                y = torch.ops.orcasaq2.layer_gemm(dx[ic_r], *lay_args[si][li])
+            dx_all.copy_(hx_all, non_blocking=True)
+            for li, (name, ic_r, _, tot) in enumerate(sets[si]):
+                y = torch.ops.orcasaq2.layer_gemm(dxv[ic_r], *lay_args[si][li])
                 if world > 1 and name == "down_proj":
                     all_reduce(y)
-                hy[li].copy_(y, non_blocking=True)
+                dy_all[yoff[li]:yoff[li] + rows * tot].view(rows, tot).copy_(y)
+            hy_all.copy_(dy_all, non_blocking=True)
 
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -424,8 +438,8 @@ def run_gpu(args):
         torch.cuda.synchronize()
 
         def e2e_graph_step(i):
-            for h in hx.values():
-                h[0, 0] = 0.001 * (i % 7)          # the host inputs are live, not baked into the graph
+            for ic in ics:
+                hx_all[xoff[ic]] = 0.001 * (i % 7)  # the host inputs are live, not baked into the graph
             e2e_graphs[i % N_SETS].replay()
             torch.cuda.synchronize()
 
@@ -437,15 +451,18 @@ def run_gpu(args):
             e2e_graph_step(i)
         barrier()
         e2e_s = (time.perf_counter() - t0) / n_e2e
-        e2e_mode = ("CUDA-graph replay per step of [pinned host x -> device, three orcasaq2::layer_gemm ops, "
-                    "outputs -> pinned host], host inputs rewritten before and one sync after every replay; "
-                    f"{n_e2e} steps timed on the host clock")
+        e2e_mode = ("CUDA-graph replay per step of [one pinned host buffer with the step's activations -> device, three "
+                    "orcasaq2::layer_gemm ops, results gathered on the device -> one pinned host buffer], host inputs "
+                    f"rewritten before and one sync after every replay; {n_e2e} steps timed on the host clock")
+        e2e_graph_bytes = (hx_all.numel() * 2, hy_all.numel() * 2)
     if world > 1:
         t = torch.tensor([e2e_s, e2e_eager_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s, e2e_eager_s = float(t[0].item()), float(t[1].item())
     h2d = sum(rows * ic_r * 2 for (_, ic_r, _, _) in sets[0])
     d2h = sum(rows * tot * 2 for (_, _, _, tot) in sets[0])
+    if not args.no_graph:
+        h2d, d2h = e2e_graph_bytes                 # what the graph mode copies: distinct inputs once, all results
 
     # ---- roofline of the dominant kernel (the gate_up grouped GEMV), alone: a graph of N_SETS launches over
     # the rotated weight sets (3 x 67 MB > L2), replayed; duration per launch from CUDA events around each replay
