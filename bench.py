@@ -14,10 +14,11 @@ metric  = algorithmic bytes (trellis + activations in + out) moved per second, w
 value   = inputs resident in HBM: ONE CUDA graph of exactly `--steps` steps, replayed >= 100 times and
           for >= 250 ms, every replay timed with CUDA events (max over ranks); the median replay is
           reported, its spread is in `timing`.  `by_rows` repeats this at 1 / 4 / 16 rows.
-e2e     = same metric through the plugin's custom op with HOST activations, every step: the step's activations
-          from one pinned host buffer -> device, three `orcasaq2::layer_gemm` calls, the results gathered on
-          the device -> one pinned host buffer; replayed from a CUDA graph (the plugin's serving mode).  The
-          eager time (per layer: copy in, op, copy out) is reported beside it.
+e2e     = same metric through the plugin's custom op with HOST activations, every step: pinned host activations
+          -> device, three `orcasaq2::layer_gemm` calls, every result -> pinned host; replayed from a CUDA
+          graph (the plugin's serving mode) in which the copies of later inputs and earlier results run on
+          side branches beside the layers.  The eager time (per layer: copy in, op, copy out, one stream) is
+          reported beside it.
 N > 1   = the same layer under tensor parallelism (column-parallel qkv / gate_up, row-parallel
           down_proj followed by this library's one-shot all-reduce over peer memory; `--allreduce nccl`
           uses the library collective instead), strong scaling: the job's total bytes are fixed.
@@ -399,28 +400,39 @@ def run_gpu(args):
         # The serving mode of the plugin (the op is built to replay inside CUDA graphs): per weight set
         # one graph of [pinned host x -> device, the three plugin ops, outputs -> pinned host]; a step
         # rewrites the host activations, replays the graph and waits for the outputs.
-        # All host activations of a step sit in ONE pinned buffer and all results return in one: two copies per step
-        # instead of six (a copy of a few tens of KB costs its latency, not its bytes).
+        # Inside the graph the copies run on two side branches: the input of a later layer arrives while the earlier
+        # layers compute, and a layer's result leaves for the host while the next layer computes.  Only the first
+        # input copy and the last result copy are exposed.  Every layer still gets its activations from pinned host
+        # memory and every result is read back, every step.
         ics = sorted(xs)
-        xoff = {ic: sum(rows * j for j in ics[:k]) for k, ic in enumerate(ics)}
-        hx_all = torch.empty((sum(rows * ic for ic in ics),), dtype=torch.half).pin_memory()
-        for ic in ics:
-            hx_all[xoff[ic]:xoff[ic] + rows * ic] = hx[ic].reshape(-1)
-        dx_all = torch.empty_like(hx_all, device=dev)
-        dxv = {ic: dx_all[xoff[ic]:xoff[ic] + rows * ic].view(rows, ic) for ic in ics}
-        tots = [tot for (_, _, _, tot) in sets[0]]
-        yoff = [sum(rows * t for t in tots[:k]) for k in range(len(tots))]
-        dy_all = torch.empty((sum(rows * t for t in tots),), dtype=torch.half, device=dev)
-        hy_all = torch.empty(dy_all.shape, dtype=torch.half).pin_memory()
+        hxs = {ic: hx[ic] for ic in ics}                      # pinned host activations, one per distinct input
+        dxv = {ic: torch.empty_like(xs[ic]) for ic in ics}
+        hys = [torch.empty((rows, tot), dtype=torch.half).pin_memory() for (_, _, _, tot) in sets[0]]
+        cin, cout = torch.cuda.Stream(), torch.cuda.Stream()
 
         def e2e_body(si):
-            dx_all.copy_(hx_all, non_blocking=True)
+            main = torch.cuda.current_stream()
+            first_ic = sets[si][0][1]
+            dxv[first_ic].copy_(hxs[first_ic], non_blocking=True)
+            cin.wait_stream(main)
+            with torch.cuda.stream(cin):
+                for ic in ics:
+                    if ic != first_ic:
+                        dxv[ic].copy_(hxs[ic], non_blocking=True)
+            arrived = {first_ic}
             for li, (name, ic_r, _, tot) in enumerate(sets[si]):
+                if ic_r not in arrived:
+                    main.wait_stream(cin)
+                    arrived.update(ics)
                 y = torch.ops.orcasaq2.layer_gemm(dxv[ic_r], *lay_args[si][li])
                 if world > 1 and name == "down_proj":
                     all_reduce(y)
-                dy_all[yoff[li]:yoff[li] + rows * tot].view(rows, tot).copy_(y)
-            hy_all.copy_(dy_all, non_blocking=True)
+                cout.wait_stream(main)
+                with torch.cuda.stream(cout):
+                    hys[li].copy_(y, non_blocking=True)
+                    y.record_stream(cout)
+            main.wait_stream(cin)
+            main.wait_stream(cout)
 
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
@@ -439,7 +451,7 @@ def run_gpu(args):
 
         def e2e_graph_step(i):
             for ic in ics:
-                hx_all[xoff[ic]] = 0.001 * (i % 7)  # the host inputs are live, not baked into the graph
+                hxs[ic][0, 0] = 0.001 * (i % 7)     # the host inputs are live, not baked into the graph
             e2e_graphs[i % N_SETS].replay()
             torch.cuda.synchronize()
 
@@ -451,10 +463,11 @@ def run_gpu(args):
             e2e_graph_step(i)
         barrier()
         e2e_s = (time.perf_counter() - t0) / n_e2e
-        e2e_mode = ("CUDA-graph replay per step of [one pinned host buffer with the step's activations -> device, three "
-                    "orcasaq2::layer_gemm ops, results gathered on the device -> one pinned host buffer], host inputs "
-                    f"rewritten before and one sync after every replay; {n_e2e} steps timed on the host clock")
-        e2e_graph_bytes = (hx_all.numel() * 2, hy_all.numel() * 2)
+        e2e_mode = ("CUDA-graph replay per step of [pinned host activations -> device, three orcasaq2::layer_gemm ops, "
+                    "every result -> pinned host]; the copies of later inputs and earlier results run on side branches "
+                    "of the graph beside the layers; host inputs rewritten before and one sync after every replay; "
+                    f"{n_e2e} steps timed on the host clock")
+        e2e_graph_bytes = (sum(h.numel() * 2 for h in hxs.values()), sum(h.numel() * 2 for h in hys))
     if world > 1:
         t = torch.tensor([e2e_s, e2e_eager_s], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
