@@ -458,7 +458,12 @@ struct DenseParams {
     __half *y;             // [tokens][ldy]
     int tokens, ic, oc, ldy;
     int npx, nty;          // tiles: pairs of 128-channel blocks x 256-token tiles
-    int npairs;            // CTA pairs launched (each walks tiles pair, pair + npairs, ...)
+    int npairs;            // CTA pairs launched (each walks work items pair, pair + npairs, ...)
+    // The tiles beyond the last full round of `npairs` are cut into `tail_f` (1, 2 or 4) narrower items of
+    // 256 / tail_f tokens each, so that the last round is shorter instead of mostly idle.
+    int full_items;        // items that are whole tiles
+    int items;             // full_items + (tiles - full_items) * tail_f
+    int tail_f;
 };
 struct DenseBarriers {
     uint64_t full[kDenseStages], empty[kDenseStages];
@@ -482,18 +487,33 @@ __device__ __forceinline__ void dense_tile(const DenseParams &P, int L, int &px,
     }
 }
 
+// work item (in launch order) -> tile, first token and width of its slice of the tile
+__device__ __forceinline__ void dense_item(const DenseParams &P, int L, int &px, int &tok0, int &ntok) {
+    int ty;
+    if (L < P.full_items) {
+        dense_tile(P, L, px, ty);
+        tok0 = ty * kBN;
+        ntok = kBN;
+    } else {
+        const int t = L - P.full_items;
+        dense_tile(P, P.full_items + t / P.tail_f, px, ty);
+        ntok = kBN / P.tail_f;
+        tok0 = ty * kBN + (t % P.tail_f) * ntok;
+    }
+}
+
 // Persistent: every CTA pair walks its share of the 256-channel x 256-token tiles.  Tensor memory holds two
 // accumulators (2 x 256 columns): while the epilogue warps drain one tile, the MMAs of the next tile fill the other.
 __global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                       const DenseParams P) {
+                       const __grid_constant__ CUtensorMap xmap_tail, const DenseParams P) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char *smem_raw = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);   // swizzled tiles: 1024-byte alignment
     DenseBarriers &S = *reinterpret_cast<DenseBarriers *>(smem_raw + (size_t)kDenseStages * kDenseStageBytes);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t crank = cluster_ctarank();                     // 0 issues the MMAs of the pair
     const int pair = blockIdx.x >> 1;
-    const int ntiles = P.npx * P.nty;
+    const int nitems = P.items;
     const int nsteps = P.ic / kBK;
     constexpr uint32_t kTmemCols = 2 * kBN;
 
@@ -529,21 +549,23 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
             uint32_t full0;                                          // full[0] of the pair's first CTA
             asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(full0) : "r"(s32(&S.full[0])));
             Cursor c(0, kDenseStages);
-            for (int L = pair; L < ntiles && ok; L += P.npairs) {
-                int px, ty;
-                dense_tile(P, L, px, ty);
-                const int row_w = (2 * px + (int)crank) * kBM, row_x = ty * kBN + (int)crank * (kBN / 2);
+            for (int L = pair; L < nitems && ok; L += P.npairs) {
+                int px, tok0, ntok;
+                dense_item(P, L, px, tok0, ntok);
+                const CUtensorMap *xm = ntok == kBN ? &xmap : &xmap_tail;          // box of ntok / 2 token rows
+                const int row_w = (2 * px + (int)crank) * kBM, row_x = tok0 + (int)crank * (ntok / 2);
+                const uint32_t bytes = 2 * (kABytes + (ntok / 2) * kBK * 2);
                 for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
                     if (c.wrapped) ok = mbar_wait(s32(&S.empty[c.idx]), c.phase ^ 1u, 20);
                     if (!ok) break;
                     const uint32_t bar = full0 + 8 * c.idx;
                     const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
-                    if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), 2 * kDenseStageBytes);
+                    if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), bytes);
                     tma_2d_pair(st, &wmap, s * kBK, row_w, bar);
-                    tma_2d_pair(st + kABytes, &xmap, s * kBK, row_x, bar);     // token rows out of range arrive as zeros
+                    tma_2d_pair(st + kABytes, xm, s * kBK, row_x, bar);        // token rows out of range arrive as zeros
                     if (s + kDensePrefetch < nsteps) {
                         tma_2d_prefetch(&wmap, (s + kDensePrefetch) * kBK, row_w);
-                        tma_2d_prefetch(&xmap, (s + kDensePrefetch) * kBK, row_x);
+                        tma_2d_prefetch(xm, (s + kDensePrefetch) * kBK, row_x);
                     }
                 }
             }
@@ -552,11 +574,11 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
         if (lane == 0 && crank == 0) {
             // ---------------- first CTA: MMA issue for the pair
             bool ok = true;
-            const uint32_t idesc = umma2_idesc(kBN);
             Cursor c(0, kDenseStages);
-            int i = 0;                                               // tiles of this pair so far
-            for (int L = pair; L < ntiles && ok; L += P.npairs, ++i) {
+            int i = 0;                                               // items of this pair so far
+            for (int L = pair; L < nitems && ok; L += P.npairs, ++i) {
                 const int b = i & 1, use = i >> 1;
+                const uint32_t idesc = umma2_idesc(L < P.full_items ? kBN : kBN / P.tail_f);
                 // the epilogue warps of both CTAs have drained this accumulator's previous tile
                 if (use > 0) ok = mbar_wait(s32(&S.acc_empty[b]), (uint32_t)(use - 1) & 1u);
                 if (!ok) break;
@@ -582,16 +604,15 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
         asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(acc_empty0) : "r"(s32(&S.acc_empty[0])));
         bool ok = true;
         int i = 0;
-        for (int L = pair; L < ntiles && ok; L += P.npairs, ++i) {
+        for (int L = pair; L < nitems && ok; L += P.npairs, ++i) {
             const int b = i & 1, use = i >> 1;
-            int px, ty;
-            dense_tile(P, L, px, ty);
+            int px, tok0, ntok;
+            dense_item(P, L, px, tok0, ntok);
             const int oc_row = (2 * px + (int)crank) * kBM + 32 * quad + lane;
-            const int tok0 = ty * kBN;
-            const int ncols = min(kBN, P.tokens - tok0);
+            const int ncols = min(ntok, P.tokens - tok0);
             ok = mbar_wait(s32(&S.acc_full[b]), (uint32_t)use & 1u, 100);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            for (int c0 = col_part * 32; c0 < kBN; c0 += 64) {
+            for (int c0 = col_part * 32; c0 < ntok; c0 += 64) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(b * kBN + c0);
                 asm volatile(
@@ -1090,7 +1111,9 @@ static int launch_reconstruct_t(const void *trellis, const void *svh, void *wt, 
     return launch_status();
 }
 
-static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseParams P, cudaStream_t st) {
+typedef int (*DenseTailMapFn)(void *ctx, int box_rows, CUtensorMap *out);
+static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseTailMapFn tail_map, void *tail_ctx,
+                        DenseParams P, cudaStream_t st) {
     if (cudaFuncSetAttribute(gemm_dense_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
@@ -1121,8 +1144,18 @@ static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseP
     }
     const int ntiles = P.npx * P.nty;
     P.npairs = ntiles < fit ? ntiles : fit;
+    // the tiles left over after the last full round: cut them in 2 or 4 when the pieces still fit one round
+    const int tail = ntiles % P.npairs;
+    P.tail_f = tail == 0 ? 1 : 4 * tail <= P.npairs ? 4 : 2 * tail <= P.npairs ? 2 : 1;
+    P.full_items = ntiles - (P.tail_f > 1 ? tail : 0);
+    P.items = P.full_items + (ntiles - P.full_items) * P.tail_f;
+    CUtensorMap xtail = xmap;
+    if (P.tail_f > 1) {
+        const int rc = tail_map(tail_ctx, kBN / 2 / P.tail_f, &xtail);
+        if (rc != EXL3_OK) return rc;
+    }
     cfg.gridDim = dim3((unsigned)(2 * P.npairs));
-    if (cudaLaunchKernelEx(&cfg, gemm_dense_pair_kernel, wmap, xmap, P) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    if (cudaLaunchKernelEx(&cfg, gemm_dense_pair_kernel, wmap, xmap, xtail, P) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     return launch_status();
 }
 } }
@@ -1284,7 +1317,16 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         D.nty = (rows + kBN - 1) / kBN;
         D.npairs = 0;
         if ((long long)D.npx * D.nty > 0x3fffffffLL) return EXL3_E_SHAPE;
-        rc = launch_dense(wmap, xmap, D, st);
+        struct TailCtx { EncodeTiledFn enc; void *xh; cuuint64_t xdim[2]; cuuint64_t gstr[1]; } tctx = {enc, xh, {xdim[0], xdim[1]}, {gstr[0]}};
+        auto tail_map = [](void *c, int box_rows, CUtensorMap *out) -> int {
+            TailCtx *t = static_cast<TailCtx *>(c);
+            const cuuint32_t tbox[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+            const cuuint32_t one[2] = {1, 1};
+            return t->enc(out, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, t->xh, t->xdim, t->gstr, tbox, one, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
+                       ? EXL3_OK : EXL3_E_LAUNCH;
+        };
+        rc = launch_dense(wmap, xmap, tail_map, &tctx, D, st);
         if (rc != EXL3_OK || fold) return rc;
         return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
     }

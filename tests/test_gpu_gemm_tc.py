@@ -54,7 +54,10 @@ def test_gemm_tmem_operand_path_vs_oracle(ext, coracle, K, rows, ic, oc):
     # ragged second half, split input dimension; and an odd number of output blocks, which stays on single CTAs
     (1024, 512, 256, 3, torch.float16), (1100, 256, 512, 5, torch.float16), (1500, 384, 256, 2, torch.bfloat16),
     (1024, 4096, 256, 4, torch.float16), (1300, 256, 384, 6, torch.float16), (4096, 512, 1024, 3, torch.float16),
-    (1200, 2048, 512, 5, torch.bfloat16),      # many input channels per row: the output is rotated in place afterwards, not folded
+    (1200, 2048, 512, 5, torch.bfloat16),
+    # more tiles than the 74 CTA pairs of a B200 hold at once: the tiles beyond the last full round are cut into
+    # quarter- (80 and 90 tiles) or half-width (110 tiles) work items; 2100 rows leave a ragged last token tile
+    (2048, 256, 2560, 3, torch.float16), (2100, 256, 2560, 4, torch.bfloat16), (2816, 384, 2560, 2, torch.float16),      # many input channels per row: the output is rotated in place afterwards, not folded
 ])
 def test_gemm_tc_vs_reconstruct_route(ext, rows, ic, oc, K, dtype):
     """Larger shapes against reconstruct + dense matmul on the GPU (the reference's own route)."""
