@@ -406,7 +406,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap xmap, const Params P) {
 // L2 -> shared memory once per 256 output channels and each SM reads 8 KB of operands per MMA instead of 12.
 // All loads are per-CTA 2-D TMA loads of this GPU's own memory (no multicast); both CTAs' loads are counted on the
 // first CTA's barrier (the cta_group::2 form of the load), the first CTA's commits arrive on the barriers of both.
-// Warps: 0 = producer (one lane: three TMA loads per stage), 1 = MMA issue (first CTA of the pair only),
+// Warps: 0 and 10 = producers (one lane each: weight rows / token rows), 1 = MMA issue (first CTA of the pair only),
 // 2..9 = epilogue (tcgen05.ld of their lane quadrant, fp16 stores).  Four stages of 48 KB.
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;
@@ -423,9 +423,6 @@ __device__ __forceinline__ void tma_2d_pair(uint32_t dst, const CUtensorMap *map
     asm volatile(
         "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(map), "r"(x), "r"(y), "r"(bar_cluster) : "memory");
-}
-__device__ __forceinline__ void tma_2d_prefetch(const CUtensorMap *map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void umma2(uint32_t d_tmem, uint64_t a, uint64_t b, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
@@ -446,12 +443,12 @@ __device__ __forceinline__ uint32_t umma2_idesc(int n) {
 
 constexpr int kDenseMinRows = 1024;                                    // from here always (given an even number of output blocks)
 constexpr int kDenseStages = 7;
-constexpr int kDensePrefetch = 12;                                     // L2 prefetch distance beyond the ring, in steps
 constexpr int kDenseBand = 8;                                          // channel pairs (of 256 channels) per L2 band
 constexpr int kDenseHalfBytes = (kBN / 2) * kBK * 2;                   // this CTA's 128 token rows of a 256-token tile: 16 KB
 constexpr int kDenseStageBytes = kABytes + kDenseHalfBytes;            // 32 KB
 constexpr int kDenseEpiWarps = 8;
-constexpr int kDenseThreads = 32 * (2 + kDenseEpiWarps);
+constexpr int kDenseBWarp = 2 + kDenseEpiWarps;                        // the token-tile producer (after the epilogue warps)
+constexpr int kDenseThreads = 32 * (3 + kDenseEpiWarps);
 constexpr size_t kDenseSmem = (size_t)kDenseStages * kDenseStageBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
 
 struct DenseParams {
@@ -539,12 +536,15 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = S.tmem_base;
 
-    if (warp == 0) {
-        // ---------------- producer: this CTA's 128 weight rows and its half of the 256-token tile, every step of
-        // every tile of the pair.  The bytes of BOTH CTAs are counted on the first CTA's `full` barrier (which that
-        // CTA arms with the sum), so the MMA-issuing lane learns of the second CTA's tiles without a relay.  Tiles a
-        // ring's length further on are prefetched into L2.
+    if (warp == 0 || warp == kDenseBWarp) {
+        // ---------------- producers: warp 0 loads this CTA's 128 weight rows, warp kDenseBWarp its half of the token
+        // tile, every step of every work item of the pair (two warps: issuing a TMA load costs its thread a few
+        // dozen cycles, and one thread issuing everything was measured to hold the ring back; L2 prefetches issued
+        // from here cost more than they gained).  The bytes of BOTH CTAs are counted on the first CTA's `full`
+        // barrier (which that CTA's weight producer arms with the sum), so the MMA-issuing lane learns of the
+        // second CTA's tiles without a relay.
         if (lane == 0) {
+            const bool is_a = warp == 0;
             bool ok = true;
             uint32_t full0;                                          // full[0] of the pair's first CTA
             asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(full0) : "r"(s32(&S.full[0])));
@@ -560,12 +560,11 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
                     if (!ok) break;
                     const uint32_t bar = full0 + 8 * c.idx;
                     const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
-                    if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), bytes);
-                    tma_2d_pair(st, &wmap, s * kBK, row_w, bar);
-                    tma_2d_pair(st + kABytes, xm, s * kBK, row_x, bar);        // token rows out of range arrive as zeros
-                    if (s + kDensePrefetch < nsteps) {
-                        tma_2d_prefetch(&wmap, (s + kDensePrefetch) * kBK, row_w);
-                        tma_2d_prefetch(xm, (s + kDensePrefetch) * kBK, row_x);
+                    if (is_a) {
+                        if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), bytes);
+                        tma_2d_pair(st, &wmap, s * kBK, row_w, bar);
+                    } else {
+                        tma_2d_pair(st + kABytes, xm, s * kBK, row_x, bar);    // token rows out of range arrive as zeros
                     }
                 }
             }
