@@ -175,6 +175,55 @@ def test_int8_embedding_table_api():
         apply()
 
 
+def test_int8_embedding_apply_hooks_a_stand_in_engine(monkeypatch):
+    """`apply()` (reference patches/int8_embedding.py:46-86) against a stand-in for the engine module it patches:
+    an Embedding whose store holds `<key>.qweight` / `<key>.scales` gets an Int8EmbeddingTable from eager reads,
+    one without them goes to the stock loader, and a second apply() is a no-op."""
+    import sys
+    import types
+    from orcasaq2.patches import int8_embedding as P
+
+    calls = []
+
+    class Store:
+        def __init__(self, tensors):
+            self.t = tensors
+
+        def has_tensor(self, key):
+            return key in self.t
+
+        def get_tensor(self, key, device, **kw):
+            calls.append((key, kw))
+            return self.t[key]
+
+    class Embedding:
+        def __init__(self, key, store):
+            self.key, self.out_dtype, self.embedding = key, torch.half, None
+            self.config = types.SimpleNamespace(stc=store)
+
+        def load(self, device, **kwargs):
+            self.embedding = "stock"
+            return "stock"
+
+    eng = types.ModuleType("exllamav3")
+    mods = types.ModuleType("exllamav3.modules")
+    emb = types.ModuleType("exllamav3.modules.embedding")
+    emb.Embedding = Embedding
+    eng.modules, mods.embedding = mods, emb
+    for name, m in (("exllamav3", eng), ("exllamav3.modules", mods), ("exllamav3.modules.embedding", emb)):
+        monkeypatch.setitem(sys.modules, name, m)
+
+    assert P.apply() is True and P.apply() is False
+    q, s = R.make_int8_table(3, 8, 16)
+    e = Embedding("model.embed_tokens", Store({"model.embed_tokens.qweight": q, "model.embed_tokens.scales": s}))
+    assert e.load("cpu") is None
+    assert isinstance(e.embedding, P.Int8EmbeddingTable) and e._numel == q.numel() and e.device == "cpu"
+    assert torch.equal(e.embedding.qweight, q) and e.embedding.scales.shape == (8, 1)
+    assert all(kw.get("no_defer") for _, kw in calls[-2:]) and calls[-1][1].get("allow_bf16")
+    plain = Embedding("model.embed_tokens", Store({"model.embed_tokens.weight": q}))
+    assert plain.load("cpu") == "stock" and plain.embedding == "stock"
+
+
 def _loaded_layer(cfgmod, K=4, flag=None, width=None):
     """A one-shard layer with its tensors captured, ready for process_weights_after_loading."""
     m = cfgmod.Exl3LinearMethod(cfgmod.Exl3Config.from_config({}), "l.o_proj")
