@@ -138,7 +138,8 @@ def write_synthetic_checkpoint(path: str, *, layers: int, hidden: int, ffn: int,
     arch = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": hidden,
             "intermediate_size": ffn, "num_hidden_layers": layers, "num_attention_heads": q_heads,
             "num_key_value_heads": kv_heads, "head_dim": head_dim, "vocab_size": vocab, "rms_norm_eps": 1e-6,
-            "tie_word_embeddings": True, "torch_dtype": "float16",
+            "tie_word_embeddings": True, "torch_dtype": "float16", "rope_theta": 10000.0,
+            "max_position_embeddings": 4096,
             "quantization_config": {k: v for k, v in qcfg.items() if k != "tensor_storage"}}
     with open(os.path.join(path, "config.json"), "w") as f:
         json.dump(arch, f, indent=1)
