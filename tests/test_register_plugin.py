@@ -54,3 +54,12 @@ def test_register_and_constructor_patch():
     p = subprocess.run([sys.executable, "-c", SCRIPT, os.path.join(ROOT, "orcasaq2-kernel_b200")],
                        capture_output=True, text=True, timeout=600, env=env)
     assert p.returncode == 0 and "REGISTER-OK" in p.stdout, (p.stdout[-2000:], p.stderr[-4000:])
+
+
+def test_package_declares_the_reference_entry_point():
+    """vLLM discovers the plugin through the entry-point group the reference declares (its pyproject.toml:19-20)."""
+    import tomllib
+    with open(os.path.join(ROOT, "orcasaq2-kernel_b200", "pyproject.toml"), "rb") as f:
+        meta = tomllib.load(f)
+    assert meta["project"]["entry-points"]["vllm.general_plugins"] == {"orcasaq2": "orcasaq2:register"}
+    assert "orcasaq2" in meta["tool"]["setuptools"]["packages"]
