@@ -62,7 +62,7 @@ class Exl3EmbeddingMethod(QuantizeMethodBase):
     def embedding(self, layer, input_: torch.Tensor) -> torch.Tensor:
         if layer.exl3_embed_q is None:
             return layer.exl3_embed[input_]
-        return _ext.int8_embed(layer.exl3_embed_q, layer.exl3_embed_s, input_)
+        return torch.ops.orcasaq2.int8_embed(layer.exl3_embed_q, layer.exl3_embed_s, input_)
 
     def apply(self, layer, x: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
         if layer.exl3_embed_q is None:
@@ -72,7 +72,7 @@ class Exl3EmbeddingMethod(QuantizeMethodBase):
             x2 = x.reshape(rows, x.shape[-1])
             if x2.dtype not in (torch.float16, torch.bfloat16):
                 x2 = x2.to(layer.exl3_embed_s.dtype)
-            out = _ext.int8_head(layer.exl3_embed_q, layer.exl3_embed_s, x2.contiguous()).to(x.dtype)
+            out = torch.ops.orcasaq2.int8_head(layer.exl3_embed_q, layer.exl3_embed_s, x2.contiguous()).to(x.dtype)
             out = out.reshape(*x.shape[:-1], out.shape[-1])
         return out + bias if bias is not None else out
 
@@ -126,6 +126,6 @@ class Exl3LMHeadMethod(Exl3LinearMethod):
         x2 = x.reshape(rows, x.shape[-1])
         if x2.dtype not in (torch.float16, torch.bfloat16):
             x2 = x2.to(layer.exl3_embed_s.dtype)
-        out = _ext.int8_head(layer.exl3_embed_q, layer.exl3_embed_s, x2.contiguous()).to(x.dtype)
+        out = torch.ops.orcasaq2.int8_head(layer.exl3_embed_q, layer.exl3_embed_s, x2.contiguous()).to(x.dtype)
         out = out.reshape(*x.shape[:-1], out.shape[-1])
         return out + bias if bias is not None else out

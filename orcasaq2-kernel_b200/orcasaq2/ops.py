@@ -140,3 +140,27 @@ def layer_gemm(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Te
 def _layer_gemm_fake(x: Tensor, trellis: List[Tensor], suh: List[Tensor], svh: List[Tensor],
                      ocs: List[int], ks: List[float], mcg: List[bool], mul1: List[bool]) -> Tensor:
     return x.new_empty((x.shape[0], sum(ocs)), dtype=torch.half)
+
+
+# The int8 embedding gather and the int8 head as opaque ops, for the same reason as shard_gemm (reference ops.py:3-16):
+# the kernels are reached through ctypes, which Dynamo cannot trace, and the embedding sits INSIDE the model's
+# compiled forward (vllm/model_executor/layers/vocab_parallel_embedding.py:484).  The reference's own gather is plain
+# torch indexing (heads.py:61-67) and needs no op.
+@torch.library.custom_op("orcasaq2::int8_embed", mutates_args=())
+def int8_embed(qweight: Tensor, scales: Tensor, ids: Tensor) -> Tensor:
+    return _ext.int8_embed(qweight, scales, ids)
+
+
+@int8_embed.register_fake
+def _int8_embed_fake(qweight: Tensor, scales: Tensor, ids: Tensor) -> Tensor:
+    return scales.new_empty((*ids.shape, qweight.shape[1]))
+
+
+@torch.library.custom_op("orcasaq2::int8_head", mutates_args=())
+def int8_head(qweight: Tensor, scales: Tensor, x: Tensor) -> Tensor:
+    return _ext.int8_head(qweight, scales, x)
+
+
+@int8_head.register_fake
+def _int8_head_fake(qweight: Tensor, scales: Tensor, x: Tensor) -> Tensor:
+    return x.new_empty((x.shape[0], qweight.shape[0]))

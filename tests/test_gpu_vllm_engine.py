@@ -4,7 +4,9 @@ kernels, greedy generation from token ids.  The engine runs in a child process (
 of GPU memory go away with it); the parent compares what it returned with an oracle forward pass of the same
 checkpoint (CPU oracle's trellis decode, float64 layer algebra and attention with the fp16 roundings of the real
 chain): the first generated token, and the log-probabilities the engine reports for its top candidates at the first
-and at the second generated position (the second one exercises decode against vLLM's own KV cache).
+and at the second generated position (the second one exercises decode against vLLM's own KV cache).  Both with
+`enforce_eager` and in vLLM's default mode (torch.compile + CUDA graphs), in which the reference says its own
+plugin must run (orcasaq2/ops.py:3-16, presets/16gb.env:21).
 
 The reference is served exactly like this (`vllm serve` + `quant_method: "exl3"`, reference README.md, presets/*.env);
 it ships no test of it."""
@@ -34,11 +36,13 @@ sys.path.insert(0, sys.argv[1])
 import orcasaq2
 from orcasaq2 import checkpoint as C
 dims, seed, prompts, path = json.loads(sys.argv[2]), int(sys.argv[3]), json.loads(sys.argv[4]), sys.argv[5]
+eager = sys.argv[6] == "eager"
 C.write_synthetic_checkpoint(path, seed=seed, **dims)
 orcasaq2.register()
 from vllm import LLM, SamplingParams
-llm = LLM(model=path, skip_tokenizer_init=True, quantization="exl3", dtype="float16", enforce_eager=True,
-          max_model_len=128, gpu_memory_utilization=0.08, max_num_seqs=4, enable_prefix_caching=False)
+extra = {} if eager else {"compilation_config": {"cudagraph_capture_sizes": [1, 2, 4]}}
+llm = LLM(model=path, skip_tokenizer_init=True, quantization="exl3", dtype="float16", enforce_eager=eager,
+          max_model_len=128, gpu_memory_utilization=0.08, max_num_seqs=4, enable_prefix_caching=False, **extra)
 sp = SamplingParams(max_tokens=3, temperature=0.0, logprobs=5, detokenize=False)
 outs = llm.generate([{"prompt_token_ids": p} for p in prompts], sp)
 res = []
@@ -107,15 +111,18 @@ def _oracle_logprobs(co, tensors, ids):
     return z - np.log(np.exp(z).sum()), logits[0]
 
 
-@pytest.fixture(scope="module")
-def engine_result(ext, tmp_path_factory):
-    tmp = tmp_path_factory.mktemp("engine")
+@pytest.fixture(scope="module", params=["eager", "compiled"])
+def engine_result(request, ext, tmp_path_factory):
+    """`eager`: enforce_eager.  `compiled`: vLLM's default serving mode, the model's forward compiled with
+    torch.compile (the plugin's kernels are opaque custom ops in it: orcasaq2::layer_gemm, ::int8_embed) and replayed
+    from CUDA graphs (piecewise for prefill, full for decode)."""
+    tmp = tmp_path_factory.mktemp("engine_" + request.param)
     script = tmp / "child.py"
     script.write_text(_CHILD)
     pkg = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "orcasaq2-kernel_b200")
     try:
         p = subprocess.run([sys.executable, str(script), pkg, json.dumps(DIMS), str(SEED), json.dumps(PROMPTS),
-                            str(tmp / "ckpt")], capture_output=True, text=True, timeout=900)
+                            str(tmp / "ckpt"), request.param], capture_output=True, text=True, timeout=900)
     except subprocess.TimeoutExpired:
         pytest.skip("the vLLM engine did not come up within 15 minutes on this machine")
     line = [ln for ln in p.stdout.splitlines() if ln.startswith("ENGINE_RESULT ")]

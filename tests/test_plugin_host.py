@@ -165,6 +165,27 @@ def test_tp_slicing_rules(cfgmod, coracle, monkeypatch, world):
     assert np.allclose(acc, ref2, atol=1e-3)
 
 
+def test_custom_ops_trace_with_fake_tensors(cfgmod):
+    """Every kernel the model's forward reaches is an opaque custom op with a registered fake (meta) implementation,
+    so Dynamo can trace through the plugin under torch.compile without touching ctypes (reference ops.py:3-16,
+    ops.py:63-66 for shard_gemm; the int8 gather sits inside the compiled forward too)."""
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    with FakeTensorMode():
+        x = torch.empty((5, 256), dtype=torch.half)
+        tr = torch.empty((16, 24, 64), dtype=torch.int16)
+        suh, svh = torch.empty((256,), dtype=torch.half), torch.empty((384,), dtype=torch.half)
+        y = torch.ops.orcasaq2.shard_gemm(x, tr, suh, svh, 384, 4.0, False, False)
+        assert y.shape == (5, 384) and y.dtype == torch.half
+        yl = torch.ops.orcasaq2.layer_gemm(x, [tr, tr], [suh, suh], [svh, svh], [384, 384], [4.0, 4.0], [False] * 2, [False] * 2)
+        assert yl.shape == (5, 768) and yl.dtype == torch.half
+        q, s = torch.empty((300, 256), dtype=torch.int8), torch.empty((300,), dtype=torch.bfloat16)
+        ids = torch.empty((2, 7), dtype=torch.int64)
+        e = torch.ops.orcasaq2.int8_embed(q, s, ids)
+        assert e.shape == (2, 7, 256) and e.dtype == torch.bfloat16
+        lg = torch.ops.orcasaq2.int8_head(q, s, x)
+        assert lg.shape == (5, 300) and lg.dtype == torch.half
+
+
 def test_int8_embedding_table_api():
     from orcasaq2.patches.int8_embedding import Int8EmbeddingTable, apply
     q, s = R.make_int8_table(2, 8, 16)
