@@ -503,11 +503,46 @@ __device__ __forceinline__ void dense_item(const DenseParams &P, int L, int &px,
     }
 }
 
+// The same for the kernel that keeps tokens in the accumulator's lanes: a leftover tile is cut along its CHANNELS
+// (halves of 128: one rotation block), `n0` is the first channel and `n` the width of the item.
+__device__ __forceinline__ void dense_item_rot(const DenseParams &P, int L, int &tok0, int &n0, int &n) {
+    int px, ty;
+    if (L < P.full_items) {
+        dense_tile(P, L, px, ty);
+        n0 = px * kBN;
+        n = kBN;
+    } else {
+        const int t = L - P.full_items;
+        dense_tile(P, P.full_items + t / P.tail_f, px, ty);
+        n = kBN / P.tail_f;
+        n0 = px * kBN + (t % P.tail_f) * n;
+    }
+    tok0 = ty * kBN;
+}
+
+// 32 consecutive accumulator columns of this warp's 32 lanes (no wait: several loads may be in flight)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t *v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
 // Persistent: every CTA pair walks its share of the 256-channel x 256-token tiles.  Tensor memory holds two
 // accumulators (2 x 256 columns): while the epilogue warps drain one tile, the MMAs of the next tile fill the other.
+// ROT = false: the weight rows are the M operand (accumulator lanes = output channels, columns = tokens), the weight
+// comes with the output rotation folded in or a rotation pass follows.  ROT = true: the TOKENS are the M operand
+// (lanes = tokens, columns = output channels), so one thread holds a token's 128 consecutive channels: the epilogue
+// applies the output rotation in registers (7 x 64 butterflies in fp32) and the signs and scale, and writes the
+// final result; the weight is the plain transposed decode and `tail` is a map of the weight with narrower boxes.
+template <bool ROT>
 __global__ void __launch_bounds__(kDenseThreads, 1)
 gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-                       const __grid_constant__ CUtensorMap xmap_tail, const DenseParams P) {
+                       const __grid_constant__ CUtensorMap xmap_tail, const DenseParams P, const __half *__restrict__ svh) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char *smem_raw = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);   // swizzled tiles: 1024-byte alignment
     DenseBarriers &S = *reinterpret_cast<DenseBarriers *>(smem_raw + (size_t)kDenseStages * kDenseStageBytes);
@@ -554,11 +589,25 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
             asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(full0) : "r"(s32(&S.full[0])));
             Cursor c(0, kDenseStages);
             for (int L = pair; L < nitems && ok; L += P.npairs) {
-                int px, tok0, ntok;
-                dense_item(P, L, px, tok0, ntok);
-                const CUtensorMap *xm = ntok == kBN ? &xmap : &xmap_tail;          // box of ntok / 2 token rows
-                const int row_w = (2 * px + (int)crank) * kBM, row_x = tok0 + (int)crank * (ntok / 2);
-                const uint32_t bytes = 2 * (kABytes + (ntok / 2) * kBK * 2);
+                // M operand: 128 rows per CTA; N operand: this CTA's half of the item's n rows
+                const CUtensorMap *ma, *mb;
+                int row_a, row_b, n;
+                if constexpr (ROT) {
+                    int tok0, n0;
+                    dense_item_rot(P, L, tok0, n0, n);
+                    ma = &xmap;                                      // token rows out of range arrive as zeros
+                    mb = n == kBN ? &wmap : &xmap_tail;              // box of n / 2 weight rows
+                    row_a = tok0 + (int)crank * kBM;
+                    row_b = n0 + (int)crank * (n / 2);
+                } else {
+                    int px, tok0;
+                    dense_item(P, L, px, tok0, n);
+                    ma = &wmap;
+                    mb = n == kBN ? &xmap : &xmap_tail;              // box of n / 2 token rows
+                    row_a = (2 * px + (int)crank) * kBM;
+                    row_b = tok0 + (int)crank * (n / 2);
+                }
+                const uint32_t bytes = 2 * (kABytes + (n / 2) * kBK * 2);
                 for (int s = 0; s < nsteps && ok; ++s, c.advance(1)) {
                     if (c.wrapped) ok = mbar_wait(s32(&S.empty[c.idx]), c.phase ^ 1u, 20);
                     if (!ok) break;
@@ -566,9 +615,9 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
                     const uint32_t st = s32(smem_raw + (size_t)c.idx * kDenseStageBytes);
                     if (is_a) {
                         if (crank == 0) mbar_expect_tx(s32(&S.full[c.idx]), bytes);
-                        tma_2d_pair(st, &wmap, s * kBK, row_w, bar);
+                        tma_2d_pair(st, ma, s * kBK, row_a, bar);
                     } else {
-                        tma_2d_pair(st + kABytes, xm, s * kBK, row_x, bar);    // token rows out of range arrive as zeros
+                        tma_2d_pair(st + kABytes, mb, s * kBK, row_b, bar);
                     }
                 }
             }
@@ -609,6 +658,52 @@ gemm_dense_pair_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_co
         int i = 0;
         for (int L = pair; L < nitems && ok; L += P.npairs, ++i) {
             const int b = i & 1, use = i >> 1;
+            if constexpr (ROT) {
+                int tok0, n0, n;
+                dense_item_rot(P, L, tok0, n0, n);
+                const int tok = tok0 + (int)crank * kBM + 32 * quad + lane;
+                ok = mbar_wait(s32(&S.acc_full[b]), (uint32_t)use & 1u, 100);
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                if (col_part * 128 < n) {                           // a 128-channel item: the quadrant's first warp alone
+                    float f[128];
+                    const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)(b * kBN + col_part * 128);
+#pragma unroll
+                    for (int g = 0; g < 4; ++g) tmem_ld32(taddr + 32 * g, reinterpret_cast<uint32_t *>(f) + 32 * g);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int h = 1; h < 128; h <<= 1)
+#pragma unroll
+                        for (int e = 0; e < 128; ++e)
+                            if ((e & h) == 0) {
+                                const float u0 = f[e], u1 = f[e + h];
+                                f[e] = u0 + u1;
+                                f[e + h] = u0 - u1;
+                            }
+                    if (ok && tok < P.tokens) {
+                        const int ch0 = n0 + col_part * 128;
+                        const uint4 *sv = reinterpret_cast<const uint4 *>(svh + ch0);
+                        uint4 *dst = reinterpret_cast<uint4 *>(P.y + (size_t)tok * P.ldy + ch0);
+#pragma unroll
+                        for (int g = 0; g < 16; ++g) {
+                            const uint4 s8 = __ldg(sv + g);
+                            const __half2 *sh = reinterpret_cast<const __half2 *>(&s8);
+                            uint4 o;
+                            uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                const float2 sf = __half22float2(sh[e]);
+                                const __half2 hv = __floats2half2_rn(f[8 * g + 2 * e] * (kHadScale * sf.x), f[8 * g + 2 * e + 1] * (kHadScale * sf.y));
+                                ow[e] = *reinterpret_cast<const uint32_t *>(&hv);
+                            }
+                            dst[g] = o;
+                        }
+                    }
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(acc_empty0 + 8 * b) : "memory");
+                continue;
+            }
             int px, tok0, ntok;
             dense_item(P, L, px, tok0, ntok);
             const int oc_row = (2 * px + (int)crank) * kBM + 32 * quad + lane;
@@ -741,6 +836,169 @@ reconstruct_t_kernel(const uint32_t *__restrict__ trellis, const __half *__restr
         *reinterpret_cast<uint4 *>(wt + (size_t)(128 * blockIdx.x + 16 * warp + r) * ic + 64 * cy + seg * 8) = val;
     }
     __syncthreads();                                                // the block is re-staged by the next pass
+    }
+}
+
+// The same fold (Wt = svh * H128 Wt / sqrt(128) per 128-channel block), with the sign-matrix product on tcgen05:
+//     D[oc' (128 TMEM lanes)][ic (256 columns)] = H[oc'][oc] (A, generated once per CTA) x W[ic][oc]^T (B, K-major: the
+//     decoded weights staged in shared memory as rows of input channels, 128-byte swizzle, two K halves of 64)
+// Eight MMAs (M = 128, N = 256, K = 128) per 128 x 256 block: the product disappears behind the decode, and the
+// epilogue reads every output row's 256 consecutive input channels straight out of tensor memory.  CTA = 8 warps:
+// all decode and all read the accumulator back; one lane of warp 0 issues the MMAs.  Two CTAs share an SM (96 KB of
+// shared memory and 256 tensor-memory columns each).
+constexpr int kFoldN = 256;                          // input channels per pass
+constexpr int kFoldABytes = 2 * 128 * 128;           // H: two K halves of [128 rows][64]
+constexpr int kFoldBBytes = 2 * kFoldN * 128;        // W: two K halves of [256 rows][64]
+constexpr size_t kFoldSmem = kFoldABytes + kFoldBBytes + 1024 /*barrier, tmem base*/ + 1024 /*alignment*/;
+template <int K>
+__global__ void __launch_bounds__(256, 2)
+reconstruct_fold_kernel(const uint32_t *__restrict__ trellis, const __half *__restrict__ svh, __half *__restrict__ wt,
+                        int tiles_j, int ic) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char *smem_raw = smem_dyn + ((1024u - (s32(smem_dyn) & 1023u)) & 1023u);
+    unsigned char *smA = smem_raw, *smB = smem_raw + kFoldABytes;
+    uint64_t *bar = reinterpret_cast<uint64_t *>(smem_raw + kFoldABytes + kFoldBBytes);
+    uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(bar + 1);
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+
+    // A[r][p] = H[r][oc(p)] = (-1)^popcount(r & oc(p)) as fp16, K-major rows of 128 bytes per K half, 128-byte
+    // swizzle.  The K order p is free (A and B share it): it is chosen so that the eight output channels a lane
+    // decodes for one input channel are adjacent (one 16-byte store): p = 16 tile + 8 c2 + 4 i4 + 2 i3 + i0 holds
+    // channel 16 tile + 8 i4 + 4 i3 + 2 i0 + c2.
+    for (int i = tid; i < 128 * 128 / 2; i += 256) {
+        const int r = i >> 6, p = 2 * (i & 63);
+        const int o0 = (p & ~15) + 8 * ((p >> 2) & 1) + 4 * ((p >> 1) & 1) + ((p >> 3) & 1), o1 = o0 + 2;
+        const uint32_t lo = (__popc(r & o0) & 1) ? 0xBC00u : 0x3C00u, hi = (__popc(r & o1) & 1) ? 0xBC00u : 0x3C00u;
+        const int h = p >> 6, c = p & 63;
+        *reinterpret_cast<uint32_t *>(smA + h * 16384 + r * 128 + ((((c >> 3) ^ (r & 7))) << 4) + (c & 7) * 2) = lo | (hi << 16);
+    }
+    if (tid == 0) {
+        mbar_init(s32(bar), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(kFoldN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = *tmem_slot;
+    const float sc = kHadScale * __half2float(__ldg(svh + (size_t)blockIdx.x * 128 + 32 * (warp & 3) + lane));
+    uint32_t phase = 0;
+    bool ok = true;
+
+    // the packed words of a whole 256-channel chunk (four passes of four input tiles) are fetched ahead: the ones of
+    // the next chunk fly while this chunk's product and epilogue run (only 16 warps share an SM here, too few to hide
+    // the memory latency by themselves)
+    uint32_t wn[kFoldN / 64][K];
+    auto fetch = [&](int cy) {
+        const int u = lane >> 3, c = lane & 7;
+#pragma unroll
+        for (int pass = 0; pass < kFoldN / 64; ++pass) {
+            const int ti = cy * (kFoldN / 16) + pass * 4 + u;
+            const uint32_t *src = trellis + ((size_t)ti * tiles_j + blockIdx.x * 8 + warp) * (size_t)(8 * K) + c * K;
+#pragma unroll
+            for (int k = 0; k < K; ++k) wn[pass][k] = __ldg(src + k);
+        }
+    };
+    if ((int)blockIdx.y < ic / kFoldN) fetch(blockIdx.y);
+    for (int cy = blockIdx.y; cy < ic / kFoldN && ok; cy += gridDim.y) {
+        // ---- decode 128 output channels x 256 input channels: a warp takes output tile `warp` and, per pass, four
+        // input tiles; weight (input channel i, output channel o) goes to row p(i) of the B tile, where p is the K
+        // order of the rotated activations inside a 16-channel tile (channel 8b + 4h + q at 4q + 2b + h)
+        {
+            const int u = lane >> 3, c = lane & 7;
+#pragma unroll
+            for (int pass = 0; pass < kFoldN / 64; ++pass) {
+                uint32_t wd[K + 1];
+#pragma unroll
+                for (int k = 0; k < K; ++k) wd[k] = wn[pass][k];
+                wd[K] = __shfl_sync(0xffffffffu, wd[0], (lane & 24) | ((c + 1) & 7));
+                uint32_t z[32];
+                decode_chunk<K>(wd, z);
+                // weight i of chunk c: input channel 8 i2 + 4 i1 + (c & 3), output channel 4 (i >> 3) + 2 i0 + (c >> 2)
+#pragma unroll
+                for (int rb = 0; rb < 4; ++rb) {                     // rb = 2 i2 + i1
+                    const int row = pass * 64 + 16 * u + 4 * (c & 3) + rb;                                // B row (input channel)
+                    uint4 o;
+                    uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {                    // e = 2 i4 + i3
+                        const __half2 hv = __halves2half2(codeword_to_half(z[8 * e + 2 * rb]), codeword_to_half(z[8 * e + 2 * rb + 1]));
+                        ow[e] = *reinterpret_cast<const uint32_t *>(&hv);
+                    }
+                    const int chunk = 2 * (warp & 3) + (c >> 2);
+                    *reinterpret_cast<uint4 *>(smB + (warp >> 2) * (kFoldN * 128) + row * 128 + ((chunk ^ (row & 7)) << 4)) = o;
+                }
+            }
+        }
+        if (cy + (int)gridDim.y < ic / kFoldN) fetch(cy + gridDim.y);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // generic writes -> tensor-core reads
+        __syncthreads();
+        if (tid == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t idesc = umma_idesc(kFoldN);
+#pragma unroll
+            for (int k = 0; k < 8; ++k)
+                umma(tmem, umma_desc(s32(smA) + (k >> 2) * 16384 + (k & 3) * 32),
+                     umma_desc(s32(smB) + (k >> 2) * (kFoldN * 128) + (k & 3) * 32), idesc, k ? 1u : 0u);
+            umma_commit(s32(bar));
+        }
+        ok = mbar_wait(s32(bar), phase, 20);
+        phase ^= 1u;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        // ---- output rows: lane quadrant = 32 output channels, the two warps of a quadrant split the 256 columns.
+        // The rounded rows pass through the (now free) B tile, 512 bytes per row with the 16-byte pieces XOR-ed by
+        // the row number, so that both the per-row writes here and the per-row reads below are conflict-free and
+        // global memory sees whole 512-byte rows.
+        {
+            const int quad = warp & 3, half_cols = (warp >> 2) * (kFoldN / 2), R = 32 * quad + lane;
+#pragma unroll 1
+            for (int c0 = half_cols; c0 < half_cols + kFoldN / 2; c0 += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem + ((uint32_t)(32 * quad) << 16) + (uint32_t)c0;
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; j += 8) {
+                    uint4 o;
+                    uint32_t *ow = reinterpret_cast<uint32_t *>(&o);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const __half2 hv = __floats2half2_rn(__uint_as_float(v[j + 2 * e]) * sc, __uint_as_float(v[j + 2 * e + 1]) * sc);
+                        ow[e] = *reinterpret_cast<const uint32_t *>(&hv);
+                    }
+                    *reinterpret_cast<uint4 *>(smB + R * 512 + ((((c0 + j) >> 3) ^ lane) << 4)) = o;
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();
+        if (ok) {
+#pragma unroll 4
+            for (int rr = 0; rr < 16; ++rr) {
+                const int r = 16 * warp + rr;
+                const uint4 val = *reinterpret_cast<const uint4 *>(smB + r * 512 + ((lane ^ (r & 31)) << 4));
+                *reinterpret_cast<uint4 *>(wt + (size_t)(blockIdx.x * 128 + r) * ic + (size_t)cy * kFoldN + 8 * lane) = val;
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncthreads();                                             // tensor memory and the B tile are free again
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kFoldN) : "memory");
     }
 }
 
@@ -1105,7 +1363,24 @@ template <int K>
 static int launch_reconstruct_t(const void *trellis, const void *svh, void *wt, int ic, int oc, bool fold, cudaStream_t st) {
     const int tiles_j = oc / 16;
     dim3 grid(oc / 128, (ic / 64 + 3) / 4);                          // four passes per CTA: the sign fragments are reused
-    if (fold)
+    if (fold && ic % kFoldN == 0) {
+        if (cudaFuncSetAttribute(reconstruct_fold_kernel<K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kFoldSmem) != cudaSuccess) {
+            cudaGetLastError();
+            return EXL3_E_LAUNCH;
+        }
+        // CTAs loop over 256-channel chunks with stride gridDim.y: take the split with the fewest (waves x passes),
+        // counting a CTA's set-up (sign matrix, tensor-memory allocation) as a quarter of a pass
+        const int chunks = ic / kFoldN, bx = oc / 128, slots = 2 * 148;
+        int best_y = 1;
+        float best = 1e30f;
+        for (int y = 1; y <= chunks; ++y) {
+            const float cost = (float)((bx * y + slots - 1) / slots) * ((float)((chunks + y - 1) / y) + 0.25f);
+            if (cost < best) { best = cost; best_y = y; }
+        }
+        dim3 fgrid(bx, best_y);
+        reconstruct_fold_kernel<K><<<fgrid, 256, kFoldSmem, st>>>(static_cast<const uint32_t *>(trellis), static_cast<const __half *>(svh),
+                                                                   static_cast<__half *>(wt), tiles_j, ic);
+    } else if (fold)
         reconstruct_t_kernel<K, true><<<grid, 256, 0, st>>>(static_cast<const uint32_t *>(trellis), static_cast<const __half *>(svh),
                                                             static_cast<__half *>(wt), tiles_j, ic);
     else
@@ -1115,9 +1390,10 @@ static int launch_reconstruct_t(const void *trellis, const void *svh, void *wt, 
 }
 
 typedef int (*DenseTailMapFn)(void *ctx, int box_rows, CUtensorMap *out);
+template <bool ROT>
 static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseTailMapFn tail_map, void *tail_ctx,
-                        DenseParams P, cudaStream_t st) {
-    if (cudaFuncSetAttribute(gemm_dense_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem) != cudaSuccess) {
+                        DenseParams P, const __half *svh, cudaStream_t st) {
+    if (cudaFuncSetAttribute(gemm_dense_pair_kernel<ROT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDenseSmem) != cudaSuccess) {
         cudaGetLastError();
         return EXL3_E_LAUNCH;
     }
@@ -1133,13 +1409,13 @@ static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseT
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     // as many pairs as the device holds at once (cached per device), each walking its share of the tiles
-    static int pairs_on[64] = {};
+    static int pairs_on[64] = {};                                     // (one table per instantiation)
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     int fit = dev >= 0 && dev < 64 ? pairs_on[dev] : 0;
     if (fit == 0) {
         cfg.gridDim = dim3(2 * 1024);
-        if (cudaOccupancyMaxActiveClusters(&fit, gemm_dense_pair_kernel, &cfg) != cudaSuccess || fit < 1) {
+        if (cudaOccupancyMaxActiveClusters(&fit, gemm_dense_pair_kernel<ROT>, &cfg) != cudaSuccess || fit < 1) {
             cudaGetLastError();
             return EXL3_E_LAUNCH;
         }
@@ -1149,7 +1425,7 @@ static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseT
     P.npairs = ntiles < fit ? ntiles : fit;
     // the tiles left over after the last full round: cut them in 2 or 4 when the pieces still fit one round
     const int tail = ntiles % P.npairs;
-    P.tail_f = tail == 0 ? 1 : 4 * tail <= P.npairs ? 4 : 2 * tail <= P.npairs ? 2 : 1;
+    P.tail_f = tail == 0 ? 1 : (!ROT && 4 * tail <= P.npairs) ? 4 : 2 * tail <= P.npairs ? 2 : 1;   // ROT: whole rotation blocks
     P.full_items = ntiles - (P.tail_f > 1 ? tail : 0);
     P.items = P.full_items + (ntiles - P.full_items) * P.tail_f;
     CUtensorMap xtail = xmap;
@@ -1158,7 +1434,7 @@ static int launch_dense(const CUtensorMap &wmap, const CUtensorMap &xmap, DenseT
         if (rc != EXL3_OK) return rc;
     }
     cfg.gridDim = dim3((unsigned)(2 * P.npairs));
-    if (cudaLaunchKernelEx(&cfg, gemm_dense_pair_kernel, wmap, xmap, xtail, P) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
+    if (cudaLaunchKernelEx(&cfg, gemm_dense_pair_kernel<ROT>, wmap, xmap, xtail, P, svh) != cudaSuccess) { cudaGetLastError(); return EXL3_E_LAUNCH; }
     return launch_status();
 }
 } }
@@ -1264,14 +1540,16 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         return EXL3_OK;
     }
     if (use_dense(rows, ic, oc)) {
-        // ---- many rows: rotate the activations, rebuild the weight once (transposed, with the output rotation and
-        // signs folded in), dense tcgen05 GEMM on CTA pairs whose epilogue writes the final result
-        // Folding costs 0.83 us per 2^20 weights (128 x 128 sign-matrix products on the legacy tensor path: +74 us for
-        // 5120 x 17408); the separate output rotation costs 0.49 us per 2^20 outputs while the output stays in L2
-        // (17.6 us for 2048 x 17408) and 1.22 us beyond that (174 us for 8192 x 17408).  Fold when that is cheaper.
-        // A pitched output (a column block of a fused layer's result) cannot be rotated in place afterwards: fold.
+        // ---- many rows: rotate the activations, rebuild the weight once (transposed), dense tcgen05 GEMM on CTA pairs.
+        // The output rotation and signs: in the GEMM's epilogue (tokens in the accumulator's lanes, a thread rotates
+        // its token's 128-channel blocks in registers: no extra pass and no extra work on the weight), which needs
+        // 16-byte aligned output rows and signs.  Otherwise either folded into the rebuilt weight (0.29 us per 2^20
+        // weights on tcgen05, 0.89 on the legacy tensor path when the input dimension is not a multiple of 256) or
+        // as a pass over the output (0.49 us per 2^20 outputs while it stays in L2, 1.22 beyond), whichever is
+        // cheaper; a pitched output cannot be rotated in place afterwards and is always folded.
+        const bool rot = (reinterpret_cast<uintptr_t>(y) & 15) == 0 && (reinterpret_cast<uintptr_t>(svh) & 15) == 0 && ldy % 8 == 0;
         const double had_per = (double)rows * oc * 2 > 96.0 * 1048576.0 ? 1.22 : 0.49;
-        const bool fold = had_per * rows > 0.83 * ic || ldy != oc;
+        const bool fold = !rot && (had_per * rows > (ic % kFoldN == 0 ? 0.29 : 0.89) * ic || ldy != oc);
         if (residual) return EXL3_E_UNSUPPORTED;
         if (oc / 128 > 65535 || ic / 64 > 65535) return EXL3_E_SHAPE;
         __half *xh = static_cast<__half *>(scratch);
@@ -1320,7 +1598,9 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         D.nty = (rows + kBN - 1) / kBN;
         D.npairs = 0;
         if ((long long)D.npx * D.nty > 0x3fffffffLL) return EXL3_E_SHAPE;
+        // the narrower boxes of a cut tile: of the token rows, or (epilogue rotation) of the weight rows
         struct TailCtx { EncodeTiledFn enc; void *xh; cuuint64_t xdim[2]; cuuint64_t gstr[1]; } tctx = {enc, xh, {xdim[0], xdim[1]}, {gstr[0]}};
+        if (rot) { tctx.xh = wt; tctx.xdim[1] = wdim[1]; }
         auto tail_map = [](void *c, int box_rows, CUtensorMap *out) -> int {
             TailCtx *t = static_cast<TailCtx *>(c);
             const cuuint32_t tbox[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
@@ -1329,7 +1609,8 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
                           CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS
                        ? EXL3_OK : EXL3_E_LAUNCH;
         };
-        rc = launch_dense(wmap, xmap, tail_map, &tctx, D, st);
+        if (rot) return launch_dense<true>(wmap, xmap, tail_map, &tctx, D, static_cast<const __half *>(svh), st);
+        rc = launch_dense<false>(wmap, xmap, tail_map, &tctx, D, nullptr, st);
         if (rc != EXL3_OK || fold) return rc;
         return exl3_had_r_128(y, y, nullptr, svh, 1.0f, rows, oc, stream);
     }

@@ -88,6 +88,35 @@ def _dense_ref(ext, x, tr, suh, svh, K):
     return y
 
 
+@pytest.mark.parametrize("rows,ic,oc,K,layout", [
+    (1100, 512, 256, 3, "pitched"),        # rotation folded into the rebuilt weight by the tcgen05 kernel
+    (1100, 384, 256, 4, "pitched"),        # input dimension not a multiple of 256: folded on the legacy tensor path
+    (1100, 512, 512, 5, "offset"),         # contiguous rows: folding is cheaper than a pass over the output
+    (1024, 4096, 256, 2, "offset"),        # many input channels per row: plain weight, output rotated in place afterwards
+])
+def test_many_rows_output_not_16_byte_aligned(ext, rows, ic, oc, K, layout):
+    """The pair kernel rotates the output in its epilogue only when the output rows are 16-byte aligned; an output
+    that is only 8-byte aligned takes the older routes (rotation folded into the weight, or a pass over the result)."""
+    tr, suh, svh, x = R.make_layer(900 + rows + ic, ic, oc, K, rows)
+    xg, trg, sug, svg = x.half().cuda(), tr.cuda(), suh.cuda(), svh.cuda()
+    ref = _dense_ref(ext, xg, trg, sug, svg, K).float()
+    if layout == "pitched":
+        wide = torch.full((rows, oc + 12), 7.0, dtype=torch.half, device="cuda")
+        out = wide[:, 4:4 + oc]
+    else:
+        flat = torch.full((rows * oc + 8,), 7.0, dtype=torch.half, device="cuda")
+        out = flat[4:4 + rows * oc].view(rows, oc)
+    assert out.data_ptr() % 16 == 8
+    ext.gemm_tc(xg, trg, out, sug, svg)
+    torch.cuda.synchronize()
+    assert ext.gemm_tc_status() == 0
+    assert (out.float() - ref).abs().max() / ref.abs().max() < 5e-3
+    if layout == "pitched":
+        assert bool((wide[:, :4] == 7.0).all()) and bool((wide[:, 4 + oc:] == 7.0).all())
+    else:
+        assert bool((flat[:4] == 7.0).all()) and bool((flat[4 + rows * oc:] == 7.0).all())
+
+
 @pytest.mark.parametrize("rows,ic,oc,K", [(24, 1024, 512, 4), (128, 512, 256, 3), (300, 512, 384, 5), (600, 256, 128, 4)])
 def test_gemm_tc_fused_rmsnorm_residual_and_pitch(ext, rows, ic, oc, K):
     """RMSNorm in the activation pre-pass, residual add and a wider output matrix in the post-pass equal

@@ -50,8 +50,8 @@ def test_layer_gemm_fused(ops, coracle, rows):
 @pytest.mark.parametrize("rows", [1030, 4100])
 def test_many_rows_take_the_pair_kernel(ops, coracle, rows):
     """From 1024 rows with an even number of 128-channel output blocks: decode once + dense tcgen05 GEMM on CTA pairs,
-    as a single shard (few input channels: the output rotation is folded into the rebuilt weight) and as a
-    fused layer (every shard writes its column block of the result: pitched output, always folded)."""
+    as a single shard and as a fused layer (every shard writes its column block of the result: pitched output);
+    the GEMM's epilogue rotates and scales the output rows in registers."""
     ic, oc, K = 256, 512, 3
     tr, suh, svh, x = R.make_layer(rows, ic, oc, K, rows)
     y = torch.ops.orcasaq2.shard_gemm(x.cuda(), tr.cuda(), suh.cuda(), svh.cuda(), oc, float(K), False, False)
