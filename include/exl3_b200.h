@@ -131,10 +131,12 @@ int exl3_gemv(const void *x, const void *trellis, void *y, const void *suh, cons
  * accumulators in tensor memory).  Up to 1023 rows the trellis is decoded inside the kernel (into tensor
  * memory up to 128 rows, into shared-memory fp16 tiles above) and the decoded weight is never written to
  * global memory.  From 1024 rows (from 384 .. 640 rows for wide layers), when oc / 128 is even, the weight is rebuilt ONCE per call into the scratch
- * (transposed; where that is cheaper than rotating the output afterwards, or with a pitched output, the output rotation and svh are folded into it, which
- * changes the rounding of the result by about one fp16 ulp of the weights) and a dense GEMM runs on CTA pairs
- * (tcgen05.mma.cta_group::2): the reference's own many-row idea, orcasaq2/ops.py:50-59, with this library's
- * GEMM in the place of hgemm_recon.
+ * (transposed) and a dense GEMM runs on CTA pairs (tcgen05.mma.cta_group::2): the reference's own many-row idea,
+ * orcasaq2/ops.py:50-59, with this library's GEMM in the place of hgemm_recon.  That GEMM keeps the tokens in the
+ * accumulator's lanes, so its epilogue applies the output rotation and svh to the fp32 sums in registers and writes
+ * the final fp16 result (no pass over the output, one rounding); this needs y and svh 16-byte aligned and ldy a
+ * multiple of 8.  With an output that is only 8-byte aligned the rotation is folded into the rebuilt weight or runs
+ * as a pass over y, whichever is cheaper (folding changes the rounding by about one fp16 ulp of the weights).
  * x is fp16 (or bf16 when x_is_bf16; it is narrowed to fp16 as the reference does,
  * orcasaq2/config.py:233), y fp16, scratch a caller buffer of exl3_gemm_tc_scratch_bytes() bytes,
  * 256-byte aligned: the rotated activations (the reference's `xh`, orcasaq2/ops.py:53) and, when the

@@ -23,7 +23,7 @@
 // tensor memory and exits.
 //
 // Further down: the decode-once route for many rows (reconstruct_t_kernel + gemm_dense_pair_kernel, a persistent
-// dense GEMM on CTA pairs with tcgen05.mma.cta_group::2), and the host code that picks between the two routes and
+// dense GEMM on CTA pairs with tcgen05.mma.cta_group::2 whose epilogue applies the output rotation), and the host code that picks between the two routes and
 // the tensor-memory-operand kernel of exl3_gemm_ts.cuh.
 #include <cuda.h>
 #include <cuda_fp16.h>

@@ -9,8 +9,8 @@ Row-count dispatch (reference ops.py:25,46).  Up to 16 rows: the fused decode GE
 streaming of the packed trellis; a single shard moves to the tensor-memory kernel below from 9 rows).  From 17 rows: `exl3_gemm_tc`.  For few hundred rows that is
 one pass over the packed weights with no dense copy in memory -- up to 128 rows the decoded weights go from registers into tensor memory and are the A
 operand of tcgen05.mma; above that they are staged as swizzled shared-memory tiles.  From 1024 rows (from 384 .. 640 rows for wide layers, where it measured faster) the library decodes once (the reference's own idea
-for many rows, ops.py:50-59: rotate, rebuild the weight into scratch, dense GEMM, rotate back) and runs its own dense tcgen05 GEMM on CTA pairs, with the
-output rotation folded into the rebuilt weight where that is cheaper.  The reference's route with a library GEMM (`_dense_path`) remains for shapes the pair kernel
+for many rows, ops.py:50-59: rotate, rebuild the weight into scratch, dense GEMM, rotate back) and runs its own dense tcgen05 GEMM on CTA pairs, whose
+epilogue rotates and scales the output rows in registers (no separate pass).  The reference's route with a library GEMM (`_dense_path`) remains for shapes the pair kernel
 does not take (an odd number of 128-channel output blocks) and behind ORCA_EXL3_TC_MAX_ROWS.  GEMM_MAX_ROWS keeps the
 reference's name and default; it is the bound up to which the packed trellis is read directly
 when the tcgen05 path is switched off (ORCA_EXL3_TC=0).
