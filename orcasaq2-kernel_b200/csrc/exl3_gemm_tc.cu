@@ -1084,11 +1084,28 @@ xh_permute4_kernel(const void *__restrict__ x, const __half *__restrict__ suh, _
     const long long wid0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 4;
     if (wid0 >= nblocks) return;
     uint2 raw[4], sg[4];
+    // one division per warp (32-bit when the block count allows) instead of a 64-bit one per block
+    const unsigned bpr = (unsigned)blocks_per_row;
+    long long row0;
+    unsigned blk0;
+    if (nblocks <= 0x7fffffffLL) {
+        const unsigned r = (unsigned)wid0 / bpr;
+        row0 = r;
+        blk0 = (unsigned)wid0 - r * bpr;
+    } else {
+        row0 = wid0 / blocks_per_row;
+        blk0 = (unsigned)(wid0 - row0 * blocks_per_row);
+    }
+    float sgn[5];
+    fwht128_signs(lane, sgn);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-        const long long wid = wid0 + u < nblocks ? wid0 + u : wid0;
-        const int blk = (int)(wid % blocks_per_row);
-        const long long row = wid / blocks_per_row;
+        unsigned blk = blk0;
+        long long row = row0;
+        if (wid0 + u < nblocks) {
+            blk += u;
+            while (blk >= bpr) { blk -= bpr; ++row; }
+        }
         raw[u] = *reinterpret_cast<const uint2 *>(static_cast<const unsigned short *>(x) + (size_t)row * ldx + (size_t)blk * 128 + 4 * lane);
         sg[u] = *reinterpret_cast<const uint2 *>(suh + blk * 128 + 4 * lane);
     }
@@ -1107,7 +1124,7 @@ xh_permute4_kernel(const void *__restrict__ x, const __half *__restrict__ suh, _
         }
         const __half2 s01 = *reinterpret_cast<const __half2 *>(&sg[u].x), s23 = *reinterpret_cast<const __half2 *>(&sg[u].y);
         v[0] *= __low2float(s01); v[1] *= __high2float(s01); v[2] *= __low2float(s23); v[3] *= __high2float(s23);
-        fwht128_warp(v, lane);
+        fwht128_warp_signed(v, sgn);
         __half *dst = xh + (size_t)(wid0 + u) * 128 + 16 * (lane >> 2) + (lane & 3);
 #pragma unroll
         for (int j = 0; j < 4; ++j) dst[4 * j] = __float2half_rn(v[j] * kHadScale);

@@ -13,6 +13,8 @@ __device__ __forceinline__ void unpack4(const uint2 &r, float (&v)[4]) {
     v[0] = __low2float(a); v[1] = __high2float(a); v[2] = __low2float(b); v[3] = __high2float(b);
 }
 
+// PRE / POST: whether the scale vectors exist (a missing one costs no loads, conversions or multiplies)
+template <bool PRE, bool POST>
 __global__ void __launch_bounds__(kHadWarps * 32)
 had_r_128_kernel(const __half *__restrict__ in, __half *__restrict__ out, const __half *__restrict__ pre,
                  const __half *__restrict__ post, float scale, long long nblocks, int blocks_per_row) {
@@ -23,29 +25,46 @@ had_r_128_kernel(const __half *__restrict__ in, __half *__restrict__ out, const 
     // in flight.  (One block per warp: 2.8 TB/s on B200; four: see the profile notes.)  In place is fine: a warp
     // reads all of its blocks before it writes any of them.
     uint2 raw[kHadUnroll], pr[kHadUnroll], po[kHadUnroll];
-    const uint2 ones = make_uint2(0x3C003C00u, 0x3C003C00u);
+    // one division per warp (32-bit when the block count allows): 64-bit remainders per block were a visible share
+    // of this kernel's instructions
+    const unsigned bpr = (unsigned)blocks_per_row;
+    const unsigned blk0 = nblocks <= 0x7fffffffLL ? (unsigned)wid0 % bpr : (unsigned)(wid0 % blocks_per_row);
+    float sgn[5];
+    fwht128_signs(lane, sgn);
 #pragma unroll
     for (int u = 0; u < kHadUnroll; ++u) {
         const long long wid = wid0 + u;
         const bool live = wid < nblocks;
-        const int col = (int)((live ? wid : wid0) % blocks_per_row) * 128 + 4 * lane;
+        unsigned b = blk0 + u;
+        while (b >= bpr) b -= bpr;
+        const int col = (int)b * 128 + 4 * lane;
         raw[u] = live ? *reinterpret_cast<const uint2 *>(in + (size_t)wid * 128 + 4 * lane) : make_uint2(0u, 0u);
-        pr[u] = pre ? *reinterpret_cast<const uint2 *>(pre + col) : ones;
-        po[u] = post ? *reinterpret_cast<const uint2 *>(post + col) : ones;
+        if (PRE) pr[u] = *reinterpret_cast<const uint2 *>(pre + col);
+        if (POST) po[u] = *reinterpret_cast<const uint2 *>(post + col);
     }
     const float s = kHadScale * scale;
 #pragma unroll
     for (int u = 0; u < kHadUnroll; ++u) {
         if (wid0 + u >= nblocks) break;
-        float v[4], p[4], q[4];
+        float v[4];
         unpack4(raw[u], v);
-        unpack4(pr[u], p);
-        unpack4(po[u], q);
+        if (PRE) {
+            float p[4];
+            unpack4(pr[u], p);
 #pragma unroll
-        for (int k = 0; k < 4; ++k) v[k] *= p[k];
-        fwht128_warp(v, lane);
-        const __half2 o01 = __floats2half2_rn(v[0] * s * q[0], v[1] * s * q[1]);
-        const __half2 o23 = __floats2half2_rn(v[2] * s * q[2], v[3] * s * q[3]);
+            for (int k = 0; k < 4; ++k) v[k] *= p[k];
+        }
+        fwht128_warp_signed(v, sgn);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) v[k] *= s;
+        if (POST) {
+            float q[4];
+            unpack4(po[u], q);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) v[k] *= q[k];
+        }
+        const __half2 o01 = __floats2half2_rn(v[0], v[1]);
+        const __half2 o23 = __floats2half2_rn(v[2], v[3]);
         uint2 o;
         o.x = *reinterpret_cast<const uint32_t *>(&o01);
         o.y = *reinterpret_cast<const uint32_t *>(&o23);
@@ -67,8 +86,13 @@ extern "C" int exl3_had_r_128(const void *in, void *out, const void *pre, const 
     const long long nblocks = (long long)rows * bpr;
     const long long grid = (nblocks + kHadWarps * kHadUnroll - 1) / (kHadWarps * kHadUnroll);
     if (grid > 0x7fffffffLL) return EXL3_E_SHAPE;
-    had_r_128_kernel<<<(unsigned)grid, kHadWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<const __half *>(in), static_cast<__half *>(out), static_cast<const __half *>(pre),
-        static_cast<const __half *>(post), scale, nblocks, bpr);
+    const __half *i16 = static_cast<const __half *>(in), *pre16 = static_cast<const __half *>(pre), *post16 = static_cast<const __half *>(post);
+    __half *o16 = static_cast<__half *>(out);
+    const cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const unsigned g = (unsigned)grid, t = kHadWarps * 32;
+    if (pre && post) had_r_128_kernel<true, true><<<g, t, 0, st>>>(i16, o16, pre16, post16, scale, nblocks, bpr);
+    else if (pre) had_r_128_kernel<true, false><<<g, t, 0, st>>>(i16, o16, pre16, post16, scale, nblocks, bpr);
+    else if (post) had_r_128_kernel<false, true><<<g, t, 0, st>>>(i16, o16, pre16, post16, scale, nblocks, bpr);
+    else had_r_128_kernel<false, false><<<g, t, 0, st>>>(i16, o16, pre16, post16, scale, nblocks, bpr);
     return launch_status();
 }

@@ -28,4 +28,28 @@ __device__ __forceinline__ void fwht128_warp(float (&v)[4], int lane) {
     }
 }
 
+// The same butterflies for kernels that do little else: the lane's sign of every shuffle stage is computed once
+// (sgn[i] = -1 when bit i of the lane is set), which makes a stage one shuffle and one fused multiply-add per value.
+// Bitwise the same results: a product with +-1 is exact.
+__device__ __forceinline__ void fwht128_signs(int lane, float (&sgn)[5]) {
+#pragma unroll
+    for (int i = 0; i < 5; ++i) sgn[i] = ((lane >> i) & 1) ? -1.f : 1.f;
+}
+__device__ __forceinline__ void fwht128_warp_signed(float (&v)[4], const float (&sgn)[5]) {
+    {
+        const float a0 = v[0] + v[1], a1 = v[0] - v[1], a2 = v[2] + v[3], a3 = v[2] - v[3];
+        v[0] = a0 + a2;
+        v[1] = a1 + a3;
+        v[2] = a0 - a2;
+        v[3] = a1 - a3;
+    }
+#pragma unroll
+    for (int i = 0; i < 5; ++i)
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[k], 1 << i);
+            v[k] = fmaf(v[k], sgn[i], other);
+        }
+}
+
 }  // namespace exl3
