@@ -56,15 +56,23 @@ def test_reconstruct_rejects(ext):
 
 
 @pytest.mark.parametrize("rows,n", [(1, 128), (3, 384), (17, 5120), (200, 1024)])
-@pytest.mark.parametrize("mode", ["plain", "pre", "post", "both_inplace"])
+@pytest.mark.parametrize("mode", ["plain", "pre", "post", "both_inplace", "both_8_byte_aligned"])
 def test_had_r_128(ext, coracle, rows, n, mode):
     g = torch.Generator().manual_seed(rows * 7 + n)
     x = torch.randn((rows, n), generator=g).half()
-    pre = (torch.rand((n,), generator=g) * 2 - 1).half() if mode in ("pre", "both_inplace") else None
-    post = (torch.rand((n,), generator=g) * 2 - 1).half() if mode in ("post", "both_inplace") else None
-    scale = 0.75 if mode == "both_inplace" else 1.0
+    both = mode in ("both_inplace", "both_8_byte_aligned")
+    pre = (torch.rand((n,), generator=g) * 2 - 1).half() if mode == "pre" or both else None
+    post = (torch.rand((n,), generator=g) * 2 - 1).half() if mode == "post" or both else None
+    scale = 0.75 if both else 1.0
     xg = x.cuda()
     out = xg if mode == "both_inplace" else torch.empty_like(xg)
+    if mode == "both_8_byte_aligned":     # 16-byte aligned tensors take the kernel with 32 bytes per lane, these the 8-byte one
+        flat_in = torch.empty(rows * n + 4, dtype=torch.half, device="cuda")
+        flat_out = torch.empty(rows * n + 4, dtype=torch.half, device="cuda")
+        xg = flat_in[4:].view(rows, n)
+        xg.copy_(x)
+        out = flat_out[4:].view(rows, n)
+        assert xg.data_ptr() % 16 == 8 and out.data_ptr() % 16 == 8
     ext.had_r_128(xg, out, None if pre is None else pre.cuda(), None if post is None else post.cuda(), scale)
     ref = coracle.had_r_128(x.numpy(), None if pre is None else pre.numpy(),
                             None if post is None else post.numpy(), scale).astype(np.float32)
