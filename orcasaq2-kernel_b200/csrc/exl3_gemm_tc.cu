@@ -1131,6 +1131,93 @@ xh_permute4_kernel(const void *__restrict__ x, const __half *__restrict__ suh, _
     }
 }
 
+// The plain pre-pass with sixteen values per lane (eight lanes per 128-block, four blocks per warp): four butterfly
+// stages in registers, three across lanes (12 shuffles per block instead of 20), and a lane's sixteen channels are
+// exactly one 16-channel tile, so the permuted K order is a reordering of its own registers and the lane stores 32
+// contiguous bytes.  Same stage order and rounding as xh_permute4_kernel.  Needs 16-byte aligned rows.
+template <bool BF16>
+__global__ void __launch_bounds__(256)
+xh_permute16_kernel(const void *__restrict__ x, const __half *__restrict__ suh, __half *__restrict__ xh,
+                    long long nblocks, int blocks_per_row, int ldx) {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const int lane = threadIdx.x & 31, sub = lane & 7;
+    const long long wid0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * 4;
+    if (wid0 >= nblocks) return;
+    const long long wid = wid0 + (lane >> 3);
+    const bool live = wid < nblocks;
+    long long row = 0;
+    unsigned blk = 0;
+    if (live) {
+        if (nblocks <= 0x7fffffffLL) {
+            const unsigned r = (unsigned)wid / (unsigned)blocks_per_row;
+            row = r;
+            blk = (unsigned)wid - r * (unsigned)blocks_per_row;
+        } else {
+            row = wid / blocks_per_row;
+            blk = (unsigned)(wid - row * blocks_per_row);
+        }
+    }
+    uint4 r[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)}, sg[2] = {r[0], r[0]};
+    if (live) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(static_cast<const unsigned short *>(x) + (size_t)row * ldx + (size_t)blk * 128 + 16 * sub);
+        const uint4 *ss = reinterpret_cast<const uint4 *>(suh + (size_t)blk * 128 + 16 * sub);
+        r[0] = src[0]; r[1] = src[1];
+        sg[0] = ss[0]; sg[1] = ss[1];
+    }
+    float v[16];
+    {
+        const uint32_t *w = reinterpret_cast<const uint32_t *>(r);
+        const __half2 *sh = reinterpret_cast<const __half2 *>(sg);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            float lo, hi;
+            if (BF16) {
+                lo = __half2float(__float2half_rn(__uint_as_float(w[i] << 16)));
+                hi = __half2float(__float2half_rn(__uint_as_float(w[i] & 0xFFFF0000u)));
+            } else {
+                const __half2 hv = *reinterpret_cast<const __half2 *>(&w[i]);
+                lo = __low2float(hv);
+                hi = __high2float(hv);
+            }
+            v[2 * i] = lo * __low2float(sh[i]);
+            v[2 * i + 1] = hi * __high2float(sh[i]);
+        }
+    }
+#pragma unroll
+    for (int h = 1; h < 16; h <<= 1)
+#pragma unroll
+        for (int e = 0; e < 16; ++e)
+            if ((e & h) == 0) {
+                const float a = v[e], b = v[e + h];
+                v[e] = a + b;
+                v[e + h] = a - b;
+            }
+#pragma unroll
+    for (int i = 0; i < 3; ++i) {
+        const float sgn = ((lane >> i) & 1) ? -1.f : 1.f;
+#pragma unroll
+        for (int k = 0; k < 16; ++k) {
+            const float other = __shfl_xor_sync(0xffffffffu, v[k], 1 << i);
+            v[k] = fmaf(v[k], sgn, other);
+        }
+    }
+    if (live) {
+        // position p = 4q + 2b + h of the tile holds channel 8b + 4h + q
+        uint4 o[2];
+        uint32_t *ow = reinterpret_cast<uint32_t *>(o);
+#pragma unroll
+        for (int p = 0; p < 16; p += 2) {
+            const int c0 = 8 * ((p >> 1) & 1) + (p >> 2), c1 = c0 + 4;      // p even: h = 0; p + 1: h = 1
+            const __half2 hv = __halves2half2(__float2half_rn(v[c0] * kHadScale), __float2half_rn(v[c1] * kHadScale));
+            ow[p >> 1] = *reinterpret_cast<const uint32_t *>(&hv);
+        }
+        uint4 *dst = reinterpret_cast<uint4 *>(xh + (size_t)wid * 128 + 16 * sub);
+        dst[0] = o[0];
+        dst[1] = o[1];
+    }
+}
+
 // Pre-pass: Xh = H128(x * suh) as fp16, with the K order permuted inside every 16-channel tile
 // (channel 8b + 4h + q is stored at 4q + 2b + h) to match the A tiles written by the decode warps.
 // x may be fp16 or bf16 (the reference casts activations to fp16 first: config.py:233).
@@ -1617,7 +1704,13 @@ extern "C" int exl3_gemm_tc_ex(const void *x, const void *trellis, void *y, cons
         __half *wt = reinterpret_cast<__half *>(static_cast<unsigned char *>(scratch) + xh_bytes(rows, ic));
         const long long nblocks = (long long)rows * (ic / 128);
         const unsigned g1 = (unsigned)((nblocks + 7) / 8);
-        if (F.in_mode == 0) {
+        if (F.in_mode == 0 && (reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(suh) & 15) == 0 && F.ldx % 8 == 0) {
+            const unsigned g4 = (unsigned)((nblocks + 31) / 32);
+            if (x_is_bf16)
+                xh_permute16_kernel<true><<<g4, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F.ldx);
+            else
+                xh_permute16_kernel<false><<<g4, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F.ldx);
+        } else if (F.in_mode == 0) {
             const unsigned g4 = (unsigned)((nblocks + 31) / 32);
             if (x_is_bf16)
                 xh_permute4_kernel<true><<<g4, 256, 0, st>>>(x, static_cast<const __half *>(suh), xh, nblocks, ic / 128, F.ldx);

@@ -100,6 +100,11 @@ def test_many_rows_output_not_16_byte_aligned(ext, rows, ic, oc, K, layout):
     tr, suh, svh, x = R.make_layer(900 + rows + ic, ic, oc, K, rows)
     xg, trg, sug, svg = x.half().cuda(), tr.cuda(), suh.cuda(), svh.cuda()
     ref = _dense_ref(ext, xg, trg, sug, svg, K).float()
+    if layout == "offset":                 # activations that are only 8-byte aligned too: the pre-pass with 8 bytes per lane
+        xflat = torch.empty(rows * ic + 4, dtype=torch.half, device="cuda")
+        xflat[4:].view(rows, ic).copy_(xg)
+        xg = xflat[4:].view(rows, ic)
+        assert xg.data_ptr() % 16 == 8
     if layout == "pitched":
         wide = torch.full((rows, oc + 12), 7.0, dtype=torch.half, device="cuda")
         out = wide[:, 4:4 + oc]
