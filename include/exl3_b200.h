@@ -59,6 +59,8 @@ int exl3_reconstruct(void *w, const void *trellis, int ic, int oc, int k_times_2
  * out = H128(in * pre) * post * scale, blockwise over the last dimension n (a multiple of
  * 128), rows x n fp16, one rounding.  pre / post are fp16 [n] or NULL; in == out is allowed.
  * Replaces ext.had_r_128(in, out, pre, post, scale): orcasaq2/ops.py:54,59.
+ * Pointers must be 8-byte aligned; when all of them are 16-byte aligned a kernel with 32 bytes per lane runs
+ * (same results, 5.3 against 4.6 TB/s on B200 for 8192 x 17408).
  */
 int exl3_had_r_128(const void *in, void *out, const void *pre, const void *post, float scale,
                    int rows, int n, void *stream);
